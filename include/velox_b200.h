@@ -1,0 +1,202 @@
+/*
+ * velox_b200.h -- C ABI of libvelox_b200, the sm_100a decode-step library for Velox.
+ *
+ * What this replaces.  Velox's compiler (src/codegen.rs) writes, per model, a .cu file with every
+ * kernel as text plus the per-model launch sequence, exported as
+ *     extern "C" void velox_<Model>_{prefill,decode}_cuda(VeloxCudaArena*, uint32_t token_in,
+ *                                   size_t step, uint64_t active_mask, cudaStream_t)
+ *     extern "C" void velox_<Model>_{prefill,decode}_graph_step_cuda(VeloxCudaArena*, uint64_t, cudaStream_t)
+ * (src/codegen.rs:2803-2811, :3243-3253), and its host runner (src/runners/velox_cuda_runner.cu)
+ * allocates the arenas, streams weights in, captures the decode step in a CUDA graph and replays it.
+ * With this library the emitted file shrinks to a model description plus one call per fused IR
+ * instruction (src/ir.rs:52-300), and the runner calls the engine entry points below.
+ *
+ * Conventions.  Plain C types only; every call returns an int32 status (VB_OK or a negative
+ * VB_ERR_*) and never throws, aborts or exits; `stream` arguments are a cudaStream_t passed as
+ * void* (NULL = the legacy default stream).  Device pointers are plain addresses.  A context is
+ * used from one host thread at a time; tensor parallelism is one context per GPU / process.
+ * After vb_decode_graph_build, vb_decode_run neither allocates nor synchronises, and the decode
+ * step reads its position and input token from device memory, so one captured graph serves every
+ * position (the property the reference gets from VeloxDecodeState, src/codegen.rs:1040-1050).
+ */
+#ifndef VELOX_B200_H
+#define VELOX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VB_OK 0
+#define VB_ERR_INVALID (-1)     /* bad argument / shape / format                           */
+#define VB_ERR_CUDA (-2)        /* a CUDA runtime call failed (see vb_last_error)           */
+#define VB_ERR_UNSUPPORTED (-3) /* valid request this build does not cover                  */
+#define VB_ERR_OOM (-4)         /* device or KV-pool allocation failed                      */
+#define VB_ERR_STATE (-5)       /* call order (e.g. decode before all weights are loaded)   */
+#define VB_ERR_TIMEOUT (-6)     /* a bounded device-side wait ran out                       */
+#define VB_ERR_COMM (-7)        /* tensor-parallel communicator failure                     */
+
+/* Weight storage formats.  VB_FMT_Q4G64REF is the reference's own `--quantize q4_0` format
+ * (src/codegen.rs:2337-2369); Q4G32 / I8PC are the symmetric formats of the benchmark configs. */
+enum {
+    VB_FMT_F32 = 0, VB_FMT_F16 = 1, VB_FMT_BF16 = 2,
+    VB_FMT_Q4G32 = 3,    /* int4, groups of 32 along `in`, fp16 scale: (n-8)*scale              */
+    VB_FMT_Q4G64REF = 4, /* int4, groups of 64, half2(scale,min): fmaf(n,scale,min)             */
+    VB_FMT_I8PC = 5      /* int8, fp16 scale per output row: q*scale                            */
+};
+
+/* Tensor roles = the weight names of the .vlx models (examples/llama3_8b.vlx, qwen2_5_7b.vlx). */
+enum {
+    VB_ROLE_EMBED = 0,      /* [vocab][d]          */
+    VB_ROLE_ATTN_NORM = 1,  /* [d]        per layer */
+    VB_ROLE_WQ = 2,         /* [Hq*D][d]           */
+    VB_ROLE_WK = 3,         /* [Hkv*D][d]          */
+    VB_ROLE_WV = 4,         /* [Hkv*D][d]          */
+    VB_ROLE_WO = 5,         /* [d][Hq*D]           */
+    VB_ROLE_MLP_NORM = 6,   /* [d]                 */
+    VB_ROLE_WGATE = 7,      /* [ffn][d]            */
+    VB_ROLE_WUP = 8,        /* [ffn][d]            */
+    VB_ROLE_WDOWN = 9,      /* [d][ffn]            */
+    VB_ROLE_FINAL_NORM = 10,/* [d]                 */
+    VB_ROLE_LM_HEAD = 11,   /* [vocab][d]          */
+    VB_ROLE_BQ = 12, VB_ROLE_BK = 13, VB_ROLE_BV = 14, /* QKV bias, [rows]                     */
+    VB_ROLE_MLA_NORM = 15, VB_ROLE_MLA_WDKV = 16, VB_ROLE_MLA_WABSQ = 17, VB_ROLE_MLA_WABSO = 18,
+    VB_ROLE_COUNT = 19
+};
+
+enum { VB_LOC_HOST = 0, VB_LOC_DEVICE = 1 };
+enum { VB_ATTN_GQA = 0, VB_ATTN_MLA_REF = 1 };
+
+/* Model description: the VELOX_MODEL_* constants the compiler emits (src/codegen.rs:101-113) plus
+ * the serving parameters the runner chooses.  Replaces VeloxCudaArena/TransformerConfig
+ * (src/codegen.rs:1032-1043, src/runtime.rs:1160-1171). */
+typedef struct vb_model_desc {
+    uint32_t struct_bytes;    /* sizeof(vb_model_desc), for forward compatibility              */
+    uint32_t vocab, d_model, n_layers, n_q_heads, n_kv_heads, head_dim, ffn_dim;
+    uint32_t max_seq_len;     /* tokens per sequence the KV reservation may reach               */
+    uint32_t max_batch;       /* sequences decoded per step (>=1)                               */
+    float    rms_eps, rope_theta;
+    uint32_t weight_fmt;      /* storage of the linear layers (VB_FMT_*)                        */
+    uint32_t head_fmt;        /* storage of lm_head                                             */
+    uint32_t embed_fmt;       /* storage of the embedding table (F32/F16/BF16/Q4G64REF)          */
+    uint32_t qkv_bias;        /* 1: q=(x.Wq)+b_q ... before RoPE                                 */
+    uint32_t tied_lm_head;    /* 1: lm_head reads the embedding table                           */
+    uint32_t kv_block_tokens; /* paged-KV block size (16)                                       */
+    uint32_t kv_blocks_total; /* pool size in blocks; 0 = max_batch*ceil(max_seq_len/block)      */
+    uint32_t attn_kind;       /* VB_ATTN_*                                                      */
+    uint32_t mla_latent;      /* latent width of the reference absorbed-MLA block               */
+    uint32_t tp_rank, tp_size;/* tensor-parallel coordinates (tp_size 1 = single GPU)           */
+    uint32_t reserved[8];
+} vb_model_desc;
+
+typedef struct vb_ctx vb_ctx;
+
+/* ---- library ------------------------------------------------------------------------------ */
+int32_t     vb_version(void);
+const char* vb_last_error(void);           /* message of the last failing call on this thread  */
+int32_t     vb_device_count(int32_t* out);
+
+/* ---- engine: what velox_cuda_runner.cu:417-487 does around the emitted model --------------- */
+/* Allocates weight arena, paged KV pool, activation buffers and the mapped token ring, once. */
+int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out);
+int32_t vb_destroy(vb_ctx* ctx);
+/* Load one tensor given as [rows][cols] row-major in `src_fmt` (F32/F16/BF16) from host or device
+ * memory; it is converted on the GPU to the context's storage format (quantized when that is an
+ * int format), as stream_tensor_converted does (velox_cuda_runner.cu:154-199).  With tp_size>1 the
+ * caller passes the FULL tensor and the context keeps its own shard. */
+int32_t vb_load_tensor(vb_ctx* ctx, int32_t role, int32_t layer, const void* src, int32_t src_fmt,
+                       int32_t src_loc, uint64_t rows, uint64_t cols);
+/* Load a tensor that already is in the context's storage format (canonical layout, see DESIGN). */
+int32_t vb_load_tensor_packed(vb_ctx* ctx, int32_t role, int32_t layer, const void* data,
+                              const void* scales, int32_t src_loc, uint64_t rows, uint64_t cols);
+/* Synthetic weights: value i = mean + std * N_i(seed, stream), generated on the GPU and converted. */
+int32_t vb_load_tensor_synthetic(vb_ctx* ctx, int32_t role, int32_t layer, uint64_t seed, uint64_t stream,
+                                 float mean, float std, uint64_t rows, uint64_t cols);
+/* Copy a stored tensor back in canonical layout (host buffers; sizes in bytes are checked). */
+int32_t vb_export_tensor(vb_ctx* ctx, int32_t role, int32_t layer, void* data, uint64_t data_bytes,
+                         void* scales, uint64_t scales_bytes);
+int32_t vb_weight_bytes(vb_ctx* ctx, uint64_t* total_bytes);
+
+/* Sequences.  A slot is one of max_batch sequences; reserve() assigns KV blocks for `n_tokens`
+ * positions up front so that no decode step ever allocates. */
+int32_t vb_seq_reserve(vb_ctx* ctx, int32_t slot, uint32_t n_tokens);
+int32_t vb_seq_release(vb_ctx* ctx, int32_t slot);
+int32_t vb_seq_set(vb_ctx* ctx, int32_t slot, uint32_t token, uint32_t pos, uint32_t active);
+
+/* Prefill: runs the prompt of `slot` (positions 0..n-1), leaves the first generated token and
+ * position n in the slot's device state (velox_cuda_runner.cu:494-520). */
+int32_t vb_prefill(vb_ctx* ctx, int32_t slot, const uint32_t* tokens, uint32_t n_tokens);
+/* One decode step for every active slot, launched eagerly on the context's stream
+ * (velox_<Model>_decode_cuda, src/codegen.rs:3243-3253). */
+int32_t vb_decode_step(vb_ctx* ctx);
+/* Capture one decode step into a CUDA graph (velox_cuda_runner.cu:471-487). */
+int32_t vb_decode_graph_build(vb_ctx* ctx);
+/* Replay `n_steps` decode steps back to back with no host synchronisation in between
+ * (velox_cuda_runner.cu:537-546).  If elapsed_ms != NULL the call brackets the replays with CUDA
+ * events on the context's stream, waits for the end and returns the device time. */
+int32_t vb_decode_run(vb_ctx* ctx, uint32_t n_steps, float* elapsed_ms);
+int32_t vb_sync(vb_ctx* ctx);
+/* Tokens generated for `slot`: ring entries of positions [first_pos, first_pos+n). */
+int32_t vb_read_tokens(vb_ctx* ctx, int32_t slot, uint32_t first_pos, uint32_t n, uint32_t* out);
+int32_t vb_read_logits(vb_ctx* ctx, int32_t slot, float* out, uint64_t n_floats);
+int32_t vb_read_hidden(vb_ctx* ctx, int32_t slot, float* out, uint64_t n_floats);
+int32_t vb_read_state(vb_ctx* ctx, int32_t slot, uint32_t* token, uint32_t* pos);
+/* Kernels launched through this context since creation (graph replays count their nodes). */
+int32_t vb_launch_count(vb_ctx* ctx, uint64_t* out);
+/* Algorithmic HBM bytes of one decode step at the slots' current positions (weights once + KV). */
+int32_t vb_step_bytes(vb_ctx* ctx, uint64_t* weight_bytes, uint64_t* kv_bytes);
+/* Tuning knobs (name/value), e.g. "gemv_path"; returns VB_ERR_INVALID for unknown names. */
+int32_t vb_set_option(vb_ctx* ctx, const char* name, int64_t value);
+
+/* Tensor parallel set-up (tp_size>1): every rank calls vb_tp_unique_id on rank 0's buffer contents
+ * (128 bytes, exchanged by the host through its own channel) and then vb_tp_init. */
+int32_t vb_tp_unique_id(void* id128);
+int32_t vb_tp_init(vb_ctx* ctx, const void* id128);
+
+/* ---- per-op entry points: one per fused IR instruction (src/ir.rs:52-300) ------------------- */
+/* All pointers are device pointers; activations are fp32 as in the reference. */
+/* Embed (src/runners/tinystories_smollm.cu:87): dst[b][d] = table[tokens[b]][:]. */
+int32_t vb_op_embed(float* dst, const uint32_t* tokens, const void* table, const void* scales, int32_t fmt,
+                    uint32_t d_model, uint32_t vocab, uint32_t batch, void* stream);
+/* RmsNorm (src/runtime.rs:588-601). `w_fmt` F32 or F16. */
+int32_t vb_op_rmsnorm(float* dst, const float* x, const void* w, int32_t w_fmt, uint32_t dim, uint32_t batch,
+                      float eps, void* stream);
+/* Matmul (src/runtime.rs:702-740): dst[b][o] = sum_k x[b][k] * W[o][k], W in canonical layout. */
+int32_t vb_op_matmul(float* dst, const float* x, const void* w, const void* scales, int32_t fmt,
+                     uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* RoPE, rotate-half convention (src/runtime.rs:745-768), in place on t[n_heads][head_dim]. */
+int32_t vb_op_rope(float* t, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta, void* stream);
+/* Decode attention over a contiguous fp32 cache laid out as the reference's
+ * (src/runtime.rs:772-831): k/v [seq][n_kv*head_dim], q/out [n_q*head_dim]; split-K flash-decode. */
+int32_t vb_op_gqa_attention(float* out, const float* q, const float* k_cache, const float* v_cache,
+                            uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t pos,
+                            void* scratch, uint64_t scratch_bytes, void* stream);
+/* SampleArgmax (src/runtime.rs:1078-1088): first index of the maximum; NaN never wins. */
+int32_t vb_op_sample_argmax(uint32_t* out_token, const float* logits, uint32_t n, void* scratch,
+                            uint64_t scratch_bytes, void* stream);
+/* FusedMlaAbsorbedAttn (src/runtime.rs:944-1044): one layer's latent pool [max_seq][latent], fp32. */
+int32_t vb_op_mla_absorbed(float* dst, const float* x, const float* w_norm, const float* w_dkv,
+                           const float* w_absq, const float* w_abso, float* latent_pool, uint32_t step,
+                           uint32_t hidden, uint32_t latent, uint32_t max_seq, float eps,
+                           void* scratch, uint64_t scratch_bytes, void* stream);
+/* Load-time conversions (velox_cuda_quantize_q4_group64_kernel, src/codegen.rs:2337-2369, and the
+ * symmetric formats).  `src` fp32 [rows][cols] on the device. */
+int32_t vb_op_quantize(void* data, void* scales, const float* src, int32_t fmt, uint64_t rows, uint64_t cols, void* stream);
+int32_t vb_op_dequantize(float* dst, const void* data, const void* scales, int32_t fmt, uint64_t rows, uint64_t cols, void* stream);
+int32_t vb_op_fill_normal(float* dst, uint64_t n, uint64_t seed, uint64_t stream_id, float mean, float std, void* stream);
+/* Bytes of scratch the ops above want for a given problem (upper bound). */
+uint64_t vb_op_scratch_bytes(uint32_t n_q_heads, uint32_t head_dim, uint32_t max_seq, uint32_t vocab);
+
+/* ---- device memory helpers for hosts without a CUDA binding (tests, FFI shims) ------------- */
+int32_t vb_dev_alloc(void** out, uint64_t bytes);
+int32_t vb_dev_free(void* p);
+int32_t vb_dev_upload(void* dst_dev, const void* src_host, uint64_t bytes);
+int32_t vb_dev_download(void* dst_host, const void* src_dev, uint64_t bytes);
+int32_t vb_dev_sync(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VELOX_B200_H */

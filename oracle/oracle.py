@@ -1,0 +1,236 @@
+"""ctypes binding of the CPU checker (TEST INFRASTRUCTURE ONLY).
+
+Loads ``libvelox_oracle.so`` (the restatement of the reference's CPU runtime, velox_oracle.c) and,
+when it was built, ``_ref/libvelox_ref_smollm.so`` (the reference's own emitted C99 model).  Only the
+tests, the smoke check and the benchmark's CPU-baseline leg import this module; the product package
+never does.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+
+FMT_F32, FMT_F16, FMT_BF16, FMT_Q4G32, FMT_Q4G64REF, FMT_I8PC = range(6)
+(ROLE_EMBED, ROLE_ATTN_NORM, ROLE_WQ, ROLE_WK, ROLE_WV, ROLE_WO, ROLE_MLP_NORM, ROLE_WGATE, ROLE_WUP,
+ ROLE_WDOWN, ROLE_FINAL_NORM, ROLE_LM_HEAD, ROLE_BQ, ROLE_BK, ROLE_BV, ROLE_MLA_NORM, ROLE_MLA_WDKV,
+ ROLE_MLA_WABSQ, ROLE_MLA_WABSO) = range(19)
+
+
+class VoConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("vocab", "d_model", "n_layers", "n_q_heads", "n_kv_heads",
+                                           "head_dim", "ffn_dim", "max_seq_len")] + \
+               [("rms_eps", C.c_float), ("rope_theta", C.c_float),
+                ("qkv_bias", C.c_uint32), ("n_seqs", C.c_uint32), ("mla_latent", C.c_uint32)]
+
+
+def build(force: bool = False) -> None:
+    """Compile the checker with the Makefile beside this file (gcc, a few seconds)."""
+    if force or not os.path.exists(os.path.join(_HERE, "libvelox_oracle.so")):
+        subprocess.check_call(["make", "-C", _HERE, "libvelox_oracle.so"], stdout=subprocess.DEVNULL)
+    if force or not os.path.exists(os.path.join(_HERE, "_ref", "libvelox_ref_smollm.so")):
+        subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
+
+
+_lib = None
+_ref = None
+
+
+def _p(a, t=C.c_void_p):
+    return a.ctypes.data_as(t) if a is not None else None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(os.path.join(_HERE, "libvelox_oracle.so"))
+        L.vo_engine_create.restype = C.c_void_p
+        L.vo_engine_create.argtypes = [C.POINTER(VoConfig)]
+        L.vo_engine_destroy.argtypes = [C.c_void_p]
+        L.vo_engine_set_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.vo_engine_forward_step.restype = C.c_uint32
+        L.vo_engine_forward_step.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
+        L.vo_engine_logits.restype = C.POINTER(C.c_float)
+        L.vo_engine_logits.argtypes = [C.c_void_p]
+        L.vo_engine_hidden.restype = C.POINTER(C.c_float)
+        L.vo_engine_hidden.argtypes = [C.c_void_p]
+        L.vo_engine_generate_greedy.restype = C.c_size_t
+        L.vo_engine_generate_greedy.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p]
+        L.vo_fill_normal.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_float, C.c_float]
+        L.vo_fill_tokens.argtypes = [C.c_void_p, C.c_size_t, C.c_uint64, C.c_uint64, C.c_uint32]
+        L.vo_hash64.restype = C.c_uint64
+        L.vo_hash64.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64]
+        L.vo_f32_to_f16.restype = C.c_uint16
+        L.vo_f32_to_f16.argtypes = [C.c_float]
+        L.vo_f16_to_f32.restype = C.c_float
+        L.vo_f16_to_f32.argtypes = [C.c_uint16]
+        for q in ("q4g32", "q4g64ref", "i8pc"):
+            getattr(L, "vo_quantize_" + q).argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
+            getattr(L, "vo_dequant_" + q).argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
+        L.vo_rmsnorm_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_float]
+        L.vo_matmul_transposed_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]
+        L.vo_matvec_fmt.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_size_t, C.c_size_t]
+        L.vo_rope_rotate_half_f32.argtypes = [C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float]
+        L.vo_gqa_attention_step_f32.argtypes = [C.c_void_p] * 5 + [C.c_size_t] * 4
+        L.vo_swiglu_mlp_residual_f32.argtypes = [C.c_void_p] * 8 + [C.c_size_t] * 2
+        L.vo_sample_argmax_f32.restype = C.c_uint32
+        L.vo_sample_argmax_f32.argtypes = [C.c_void_p, C.c_size_t]
+        L.vo_mla_absorbed_step_f32.argtypes = [C.c_void_p] * 7 + [C.c_size_t] * 4 + [C.c_float]
+        L.vo_num_threads.restype = C.c_int
+        _lib = L
+    return _lib
+
+
+def ref_lib():
+    """The reference's own emitted C99 model (None when it was not built)."""
+    global _ref
+    if _ref is None:
+        build()
+        path = os.path.join(_HERE, "_ref", "libvelox_ref_smollm.so")
+        if not os.path.exists(path):
+            return None
+        R = C.CDLL(path)
+        R.refsm_create.restype = C.c_void_p
+        R.refsm_destroy.argtypes = [C.c_void_p]
+        R.refsm_weight_ptr.restype = C.POINTER(C.c_float)
+        R.refsm_weight_ptr.argtypes = [C.c_void_p, C.c_int]
+        R.refsm_prefill.restype = C.c_uint32
+        R.refsm_prefill.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]
+        R.refsm_decode.restype = C.c_uint32
+        R.refsm_decode.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64]
+        R.refsm_logits.restype = C.POINTER(C.c_float)
+        R.refsm_logits.argtypes = [C.c_void_p]
+        R.refsm_reset_kv.argtypes = [C.c_void_p]
+        R.refsm_generate.restype = C.c_uint64
+        R.refsm_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p]
+        R.refsm_rmsnorm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_float]
+        R.refsm_matmul_vec.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
+        R.refsm_rope.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float]
+        R.refsm_gqa.argtypes = [C.c_void_p] * 5 + [C.c_uint64] * 4
+        R.refsm_argmax.restype = C.c_uint32
+        R.refsm_argmax.argtypes = [C.c_void_p, C.c_uint64]
+        R.refsm_mla.argtypes = [C.c_void_p] * 7 + [C.c_uint64, C.c_uint64, C.c_float]
+        R.refsm_dim.restype = C.c_uint64
+        R.refsm_dim.argtypes = [C.c_int]
+        R.refsm_num_threads.restype = C.c_int
+        _ref = R
+    return _ref
+
+
+# ---------------------------------------------------------------------------------------------
+# numpy-facing helpers
+# ---------------------------------------------------------------------------------------------
+def fill_normal(n: int, seed: int, stream: int, std: float = 0.02, mean: float = 0.0) -> np.ndarray:
+    out = np.empty(n, dtype=np.float32)
+    lib().vo_fill_normal(_p(out), n, seed, stream, mean, std)
+    return out
+
+
+def fill_tokens(n: int, seed: int, stream: int, vocab: int) -> np.ndarray:
+    out = np.empty(n, dtype=np.uint32)
+    lib().vo_fill_tokens(_p(out), n, seed, stream, vocab)
+    return out
+
+
+def quantize(w: np.ndarray, fmt: int):
+    """fp32 [rows, cols] -> (data, scales) in storage format `fmt` (scales None for plain formats)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    rows, cols = w.shape
+    L = lib()
+    if fmt == FMT_F32:
+        return w, None
+    if fmt == FMT_F16:
+        return w.astype(np.float16).view(np.uint16), None
+    if fmt == FMT_BF16:
+        u = w.view(np.uint32).astype(np.uint64)
+        lsb = (u >> 16) & 1
+        return ((u + 0x7FFF + lsb) >> 16).astype(np.uint16), None
+    if fmt == FMT_Q4G32:
+        packed = np.empty((rows, cols // 8), dtype=np.uint32)
+        scales = np.empty((rows, cols // 32), dtype=np.uint16)
+        L.vo_quantize_q4g32(_p(packed), _p(scales), _p(w), rows, cols)
+        return packed, scales
+    if fmt == FMT_Q4G64REF:
+        packed = np.empty((rows, cols // 8), dtype=np.uint32)
+        scales = np.empty((rows, cols // 64, 2), dtype=np.uint16)
+        L.vo_quantize_q4g64ref(_p(packed), _p(scales), _p(w), rows, cols)
+        return packed, scales
+    if fmt == FMT_I8PC:
+        q = np.empty((rows, cols), dtype=np.int8)
+        scales = np.empty(rows, dtype=np.uint16)
+        L.vo_quantize_i8pc(_p(q), _p(scales), _p(w), rows, cols)
+        return q, scales
+    raise ValueError(fmt)
+
+
+def dequantize(data: np.ndarray, scales, fmt: int, rows: int, cols: int) -> np.ndarray:
+    L = lib()
+    out = np.empty((rows, cols), dtype=np.float32)
+    if fmt == FMT_F32:
+        return np.asarray(data, dtype=np.float32).reshape(rows, cols)
+    if fmt == FMT_F16:
+        return data.view(np.float16).astype(np.float32).reshape(rows, cols)
+    if fmt == FMT_BF16:
+        return (data.astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    fn = {FMT_Q4G32: L.vo_dequant_q4g32, FMT_Q4G64REF: L.vo_dequant_q4g64ref, FMT_I8PC: L.vo_dequant_i8pc}[fmt]
+    fn(_p(out), _p(data), _p(scales), rows, cols)
+    return out
+
+
+def matvec(x: np.ndarray, data: np.ndarray, scales, fmt: int, in_dim: int, out_dim: int) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(out_dim, dtype=np.float32)
+    lib().vo_matvec_fmt(_p(out), _p(x), _p(data), _p(scales), fmt, in_dim, out_dim)
+    return out
+
+
+class Engine:
+    """Mirror of VeloxStaticExecutionEngine (src/runtime.rs:1229-1502) over the C restatement."""
+
+    def __init__(self, **cfg):
+        self.cfg = VoConfig(**cfg)
+        self._keep = []
+        self.h = lib().vo_engine_create(C.byref(self.cfg))
+        if not self.h:
+            raise MemoryError("vo_engine_create")
+
+    def set_tensor(self, role: int, layer: int, data: np.ndarray, scales=None, fmt: int = FMT_F32):
+        data = np.ascontiguousarray(data)
+        scales = np.ascontiguousarray(scales) if scales is not None else None
+        self._keep += [data, scales]
+        rc = lib().vo_engine_set_tensor(self.h, role, layer, _p(data), _p(scales), fmt)
+        if rc != 0:
+            raise ValueError((role, layer))
+
+    def forward_step(self, token: int, pos: int, seq: int = 0) -> int:
+        return int(lib().vo_engine_forward_step(self.h, seq, int(token), int(pos)))
+
+    @property
+    def logits(self) -> np.ndarray:
+        return np.ctypeslib.as_array(lib().vo_engine_logits(self.h), shape=(self.cfg.vocab,)).copy()
+
+    @property
+    def hidden(self) -> np.ndarray:
+        return np.ctypeslib.as_array(lib().vo_engine_hidden(self.h), shape=(self.cfg.d_model,)).copy()
+
+    def generate_greedy(self, prompt, n_new: int, seq: int = 0) -> np.ndarray:
+        prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+        out = np.zeros(n_new, dtype=np.uint32)
+        lib().vo_engine_generate_greedy(self.h, seq, _p(prompt), len(prompt), n_new, _p(out))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().vo_engine_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,79 @@
+// Host-side launchers shared between the translation units of libvelox_b200.
+#pragma once
+
+#include "vb_internal.cuh"
+
+namespace vb {
+
+const char* last_error();
+// Opt every kernel into the dynamic shared memory it may ask for (once per device, before any capture).
+cudaError_t kernels_init();
+cudaError_t gemv_init();
+cudaError_t attn_init();
+
+// vb_basic.cu
+cudaError_t fill_normal(const LaunchCfg& lc, float* dst, uint64_t n, uint64_t seed, uint64_t stream_id, float mean, float std);
+cudaError_t quantize(const LaunchCfg& lc, void* data, void* scales, const float* src, int32_t fmt, uint64_t rows, uint64_t cols);
+cudaError_t dequantize(const LaunchCfg& lc, float* dst, const void* data, const void* scales, int32_t fmt, uint64_t rows, uint64_t cols);
+cudaError_t embed(const LaunchCfg& lc, float* dst, const uint32_t* tokens, const SeqState* state, const void* table,
+                  const void* scales, int fmt, uint32_t d, uint32_t vocab, uint32_t batch);
+cudaError_t rmsnorm(const LaunchCfg& lc, float* dst, const float* x, const void* w, int w_fmt, uint32_t dim, uint32_t batch, float eps);
+cudaError_t rope(const LaunchCfg& lc, float* t, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta);
+cudaError_t bias_rope_kv_append(const LaunchCfg& lc, float* q_out, const float* qkv, const SeqState* state, const void* bq,
+                                const void* bk, const void* bv, int bias_fmt, __half* kv_layer, const int32_t* block_table,
+                                uint32_t max_blocks, uint32_t Hq, uint32_t Hkv, uint32_t D, uint32_t block_tokens, float theta,
+                                uint32_t batch);
+cudaError_t argmax(const LaunchCfg& lc, uint32_t* out_token, const float* logits, uint32_t n, uint32_t batch, float* cand_v,
+                   uint32_t* cand_i, SeqState* state, uint32_t* ring, uint32_t ring_slots);
+uint32_t argmax_chunks(uint32_t n);
+
+// vb_gemv.cu
+// Epilogues of the matrix-vector kernels.
+enum GemvEpilogue {
+    EPI_STORE = 0,     // dst[b][o] = acc
+    EPI_RESIDUAL = 1,  // dst[b][o] += acc                      (O-proj / down-proj + residual)
+    EPI_SWIGLU = 2     // dst[b][o] = silu(acc_gate) * acc_up   (two matrices, same row index)
+};
+struct GemvArgs {
+    float* dst = nullptr;            // [batch][dst_stride]
+    const float* x = nullptr;        // [batch][in_dim] fp32
+    WMat w;                          // [out_dim][in_dim]
+    WMat w2;                         // second matrix for EPI_SWIGLU
+    const void* norm_w = nullptr;    // != null: x is RMS-normalised with these weights first
+    int norm_fmt = VB_FMT_F32;
+    float eps = 0.0f;
+    const SeqState* state = nullptr; // != null: inactive slots are skipped
+    uint32_t batch = 1;
+    uint32_t dst_stride = 0;         // elements between batch rows of dst (0 = out_dim)
+    uint32_t dst_offset = 0;         // column offset inside dst
+    int epilogue = EPI_STORE;
+};
+cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
+
+// vb_attn.cu
+struct AttnArgs {
+    float* out = nullptr;          // [batch][Hq*D]
+    const float* q = nullptr;      // [batch][Hq*D] (RoPE applied)
+    const void* k = nullptr;       // contiguous: [seq][Hkv*D]; paged: the layer's pool
+    const void* v = nullptr;       // contiguous only
+    int kv_fp16 = 0;               // element type of the cache
+    const int32_t* block_table = nullptr;  // != null: paged
+    uint32_t max_blocks = 0, block_tokens = 16;
+    const SeqState* state = nullptr;  // paged: seq_len = state[b].pos + 1
+    uint32_t pos = 0;                 // contiguous: attends [0..pos]
+    uint32_t Hq = 0, Hkv = 0, D = 0, batch = 1;
+    uint32_t max_splits = 1;
+    float* scratch = nullptr;      // [batch][Hq][max_splits][D+2]
+};
+uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits);
+uint32_t attn_pick_splits(uint32_t max_seq);
+cudaError_t attention(const LaunchCfg& lc, const AttnArgs& a);
+cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, size_t kv_batch_stride);
+
+// vb_mla.cu
+cudaError_t mla_absorbed(const LaunchCfg& lc, float* dst, const float* x, const float* w_norm, const float* w_dkv,
+                         const float* w_absq, const float* w_abso, float* pool, uint32_t step, uint32_t hidden,
+                         uint32_t latent, uint32_t max_seq, float eps, float* scratch);
+uint64_t mla_scratch_floats(uint32_t hidden, uint32_t latent);
+
+}  // namespace vb
