@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of libvelox_b200 (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Workload at N=1: Llama-3-8B-shape decoder, int4 group-32 weights + fp16 scales, fp16 embeddings, batch 1,
+512-token prompt, greedy decode (seed-generated synthetic weights and token ids; no checkpoint offline).
+A "step" is one decode step (one token).  `value` is decode tok/s with everything resident in HBM, timed by
+CUDA events on the library's stream around K CUDA-graph replays; `e2e` is the same metric when every step
+is driven from the host through the C ABI (token and position sent in, sampled token read back).
+N>1 runs N independent replicas (the 8B model fits one GPU): weak scaling, no data-path collective.
+
+--impl reference times the CPU restatement of the reference runtime (oracle/, OpenMP on all host cores) on
+a bounded sample of the same workload; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tok_per_s"
+UNIT = "tok/s"
+SEED = 20250101
+PROMPT_LEN = 512
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def workload_spec(name: str):
+    from velox_b200.modelspec import LLAMA3_8B_INT4
+    if name == "llama3-8b-int4-bs1":
+        return LLAMA3_8B_INT4, 1
+    if name == "llama3-8b-int4-bs1-4layers":  # quick functional check of the bench itself
+        return LLAMA3_8B_INT4.scaled(name="llama3-8b-int4g32-4layers", n_layers=4), 1
+    raise SystemExit("unknown workload %r" % name)
+
+
+def cpu_sample(spec, n_layers_sample: int, n_steps: int, warm: int):
+    """Times the CPU checker on `n_layers_sample` layers + head of the workload; returns per-token seconds
+    extrapolated to the full depth (weight streaming is linear in the layer count)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as H
+    from oracle import oracle as O
+    sub = spec.scaled(n_layers=n_layers_sample)
+    eng, _ = H.build_oracle(sub, SEED, max_seq_len=warm + n_steps + 1)
+    toks = H.prompt_tokens(spec, SEED, warm + n_steps)
+    for i in range(warm):
+        eng.forward_step(int(toks[i]), i)
+    per_step = []
+    head_t = None
+    for i in range(warm, warm + n_steps):
+        t0 = time.perf_counter()
+        eng.forward_step(int(toks[i]), i)
+        per_step.append(time.perf_counter() - t0)
+    # separate the head (independent of depth) from the per-layer cost with a 1-layer engine
+    one = spec.scaled(n_layers=1)
+    e1, _ = H.build_oracle(one, SEED, max_seq_len=4)
+    e1.forward_step(int(toks[0]), 0)
+    t0 = time.perf_counter()
+    e1.forward_step(int(toks[1]), 1)
+    t1 = time.perf_counter() - t0
+    t_s = float(np.median(per_step))
+    per_layer = max(1e-9, (t_s - t1) / max(1, n_layers_sample - 1)) if n_layers_sample > 1 else t_s
+    head_t = max(0.0, t1 - per_layer)
+    full = head_t + per_layer * spec.n_layers
+    return full, per_step, O.lib().vo_num_threads()
+
+
+def run_reference(args, spec, batch, rank, world):
+    if rank != 0:
+        return
+    budget_s = 150.0
+    n = args.steps + args.warmup
+    # pick how many layers one "step" covers so that the whole run fits the budget (calibrated on 2 layers)
+    full, _, cores = cpu_sample(spec, 2, 1, 1)
+    per_layer = full / spec.n_layers
+    layers = int(max(2, min(spec.n_layers, budget_s / max(1e-6, n * per_layer))))
+    t_wall = time.perf_counter()
+    full, per_step, cores = cpu_sample(spec, layers, args.steps, args.warmup)
+    value = 1.0 / full
+    sample = ("each step = one decode token through %d of %d layers + lm_head on the CPU restatement of "
+              "src/runtime.rs, extrapolated linearly to full depth; positions %d..%d" %
+              (layers, spec.n_layers, args.warmup, args.warmup + args.steps - 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": 1e3 * full, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload, "model": spec.name, "batch": batch,
+                                                        "prompt_len": PROMPT_LEN},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": time.perf_counter() - t_wall,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3-8b-int4-bs1")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemv-path", type=int, default=1)
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    spec, batch = workload_spec(args.workload)
+
+    if args.impl == "reference":
+        run_reference(args, spec, batch, rank, world)
+        return
+
+    import torch  # plumbing only: process group, barrier, max over ranks
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from velox_b200.engine import Engine
+    max_seq = args.prompt_len + args.warmup + 2 * args.steps + 16
+    eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank)
+    eng.set_option("gemv_path", args.gemv_path)
+    if args.no_pdl:
+        eng.set_option("pdl", 0)
+    t0 = time.perf_counter()
+    eng.load_synthetic(SEED)
+    load_s = time.perf_counter() - t0
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import helpers as H
+    prompt = H.prompt_tokens(spec, SEED, args.prompt_len)
+    eng.reserve(0, max_seq)
+    t0 = time.perf_counter()
+    eng.prefill(prompt, 0)
+    eng.sync()
+    ttft_s = time.perf_counter() - t0
+    eng.build_graph()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize() if torch.cuda.is_available() else None
+        eng.sync()
+
+    # ---- device-resident timing: K graph replays between CUDA events on the library's stream ----------
+    sampler = ClockSampler(local_rank)
+    sampler.start()          # nvidia-smi needs a moment to start: sample from the warm-up on, all under load
+    eng.decode(args.warmup)
+    eng.sync()
+    wbytes, kv0 = eng.step_bytes()
+    barrier()
+    l0 = eng.launch_count()
+    ms = eng.decode(args.steps, timed=True)
+    launches = eng.launch_count() - l0
+    barrier()
+    _, kv1 = eng.step_bytes()
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * batch * 1e3 / ms_per_step
+
+    # ---- end to end: every step driven from the host through the C ABI ----------------------------------
+    tok, pos = eng.state(0)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = eng.forward_step(tok, pos, 0)   # sends (token,pos), replays one step, reads the token back
+        pos += 1
+    e2e_s = time.perf_counter() - t0
+    if sampler.rows == []:
+        # very short runs: keep the GPU busy until the sampler has something to report
+        t_end = time.perf_counter() + 1.0
+        while not sampler.rows and time.perf_counter() < t_end:
+            eng.decode(8)
+            eng.sync()
+    clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = world * batch * args.steps / e2e_s
+
+    peak, peak_kind = load_peaks()
+    step_bytes = wbytes + (kv0 + kv1) // 2  # mean context over the timed region
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len,
+                   "weights": "int4 g32 + fp16 scales, fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
+                   "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),
+                   "gemv_path": args.gemv_path, "replicas": world},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     "kernel": "decode step (one CUDA-graph launch = one token)", "bytes_per_launch": step_bytes},
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "ttft_ms": 1e3 * ttft_s, "load_s": load_s,
+    }
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        full, per_step, cores = cpu_sample(spec, 2, 2, 1)
+        line["cpu_baseline"] = {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "2 decode tokens through 2 of %d layers + lm_head on the CPU restatement, "
+                                          "extrapolated linearly to full depth" % spec.n_layers}
+    eng.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

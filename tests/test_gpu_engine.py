@@ -1,0 +1,167 @@
+"""End-to-end parity of the decode engine (C ABI) against the CPU checker on the same seed-generated
+weights: stored tensors bit-exact, logits within 2e-2 max-abs, greedy tokens identical for 32 steps."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import helpers as H
+from velox_b200 import lib as L
+from velox_b200.modelspec import ModelSpec, SMOLLM_135M, LLAMA3_8B_INT4, QWEN25_7B_INT8
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2  # the tolerance the task states for fp16/bf16 compute with fp32 accumulation
+
+SMALL_SPECS = [
+    H.TINY,
+    SMOLLM_135M.scaled(name="smollm-narrow", n_layers=3, vocab=2048),
+    LLAMA3_8B_INT4.scaled(name="llama-int4-small", d_model=512, n_layers=3, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1408, vocab=4096),
+    LLAMA3_8B_INT4.scaled(name="llama-int4-2layer-fullwidth", n_layers=2, vocab=8192),
+    QWEN25_7B_INT8.scaled(name="qwen-int8-small", d_model=448, n_layers=2, n_q_heads=7, n_kv_heads=1, head_dim=64, ffn_dim=1184, vocab=3008),
+    LLAMA3_8B_INT4.scaled(name="llama-q4ref-small", d_model=512, n_layers=2, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1408, vocab=4096,
+                          weight_fmt=L.FMT_Q4G64REF, head_fmt=L.FMT_Q4G64REF, embed_fmt=L.FMT_Q4G64REF, tied_lm_head=True),
+    LLAMA3_8B_INT4.scaled(name="llama-bf16-small", d_model=256, n_layers=2, n_q_heads=4, n_kv_heads=4, head_dim=64, ffn_dim=512, vocab=1024,
+                          weight_fmt=L.FMT_BF16, head_fmt=L.FMT_BF16, embed_fmt=L.FMT_BF16),
+]
+
+
+def run_parity(spec: ModelSpec, seed: int, n_prompt: int, n_new: int, path: int, check_stored: bool = True):
+    max_seq = n_prompt + n_new + 1
+    ora, stored = H.build_oracle(spec, seed, max_seq)
+    eng = H.build_engine(spec, seed, max_seq)
+    eng.set_option("gemv_path", path)
+    if check_stored:
+        for (role, layer), (data, scales, fmt, rows, cols) in stored.items():
+            if role == L.ROLE_LM_HEAD and spec.tied_lm_head:
+                continue
+            got_d, got_s = eng.export_tensor(role, layer, rows, cols)
+            assert np.array_equal(got_d.reshape(-1).view(np.uint8), np.ascontiguousarray(data).reshape(-1).view(np.uint8)), (role, layer)
+            if scales is not None:
+                assert np.array_equal(got_s.reshape(-1), scales.reshape(-1)), (role, layer)
+    prompt = H.prompt_tokens(spec, seed, n_prompt)
+    want = ora.generate_greedy(prompt, n_new)
+    want_logits = ora.logits
+    got = eng.generate_greedy(prompt, n_new)
+    got_logits = eng.logits()
+    err = float(np.max(np.abs(got_logits - want_logits)))
+    assert err <= LOGIT_TOL, "logits max-abs %g" % err
+    assert np.array_equal(got, want), "greedy tokens differ: %s vs %s" % (got, want)
+    assert int(np.argmax(got_logits)) == int(np.argmax(want_logits))
+    eng.close()
+    return err
+
+
+@pytest.mark.parametrize("spec", SMALL_SPECS, ids=lambda s: s.name)
+@pytest.mark.parametrize("path", [0, 1])
+def test_small_models_match_checker(spec, path):
+    run_parity(spec, seed=77, n_prompt=9, n_new=32, path=path)
+
+
+def test_smollm_135m_full_model_matches_reference_fixture():
+    """BASELINE config 1 shape, full depth, against the committed output of the reference's emitted C99."""
+    g = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "smollm_ref_golden.json")))
+    eng = H.build_engine(SMOLLM_135M, g["seed"], 64)
+    n_new = len(g["tokens"])
+    got = eng.generate_greedy(np.array(g["prompt"], dtype=np.uint32), n_new)
+    assert [int(t) for t in got] == g["tokens"]
+    lg = eng.logits()
+    last = g["steps"][-1]
+    for tid, val in zip(last["top5_ids"], last["top5_logits"]):
+        assert abs(float(lg[tid]) - val) <= LOGIT_TOL
+    assert int(np.argmax(lg)) == last["top5_ids"][0]
+    eng.close()
+
+
+def test_smollm_135m_prompt128_32_steps():
+    """BASELINE config 1: 128-token prompt, first 32 greedy tokens and final logits against the checker."""
+    err = run_parity(SMOLLM_135M, seed=2024, n_prompt=128, n_new=32, path=1, check_stored=False)
+    assert err <= LOGIT_TOL
+
+
+def test_eager_graph_and_stepwise_agree():
+    """Graph replay, eager launches and host-driven forward_step produce identical tokens and logits."""
+    spec = SMALL_SPECS[2]
+    prompt = H.prompt_tokens(spec, 5, 7)
+    outs = []
+    for mode in ("graph", "eager", "step"):
+        eng = H.build_engine(spec, 5, 64)
+        if mode == "step":
+            eng.reserve(0, 40)
+            tok, toks = 0, []
+            for p, t in enumerate(prompt):
+                tok = eng.forward_step(int(t), p)
+            toks.append(tok)
+            for s in range(1, 12):
+                tok = eng.forward_step(tok, len(prompt) + s - 1)
+                toks.append(tok)
+            outs.append((np.array(toks, dtype=np.uint32), eng.logits()))
+        else:
+            outs.append((eng.generate_greedy(prompt, 12, use_graph=(mode == "graph")), eng.logits()))
+        eng.close()
+    for t, lg in outs[1:]:
+        assert np.array_equal(t, outs[0][0])
+        assert np.array_equal(lg, outs[0][1])
+
+
+def test_batched_variable_length_sequences():
+    """Several slots with different prompt lengths decode together; each matches its own CPU run."""
+    spec = SMALL_SPECS[4]
+    seed, n_new = 31, 10
+    lens = [5, 23, 16, 1]
+    max_seq = max(lens) + n_new + 1
+    ora, _ = H.build_oracle(spec, seed, max_seq, n_seqs=len(lens))
+    eng = H.build_engine(spec, seed, max_seq, max_batch=len(lens) + 1)  # one slot stays inactive
+    prompts = [H.prompt_tokens(spec, seed, n, stream=(1 << 20) + i) for i, n in enumerate(lens)]
+    for i, p in enumerate(prompts):
+        eng.reserve(i, len(p) + n_new)
+        eng.prefill(p, i)
+    eng.build_graph()
+    eng.decode(n_new - 1)
+    for i, p in enumerate(prompts):
+        want = ora.generate_greedy(p, n_new, seq=i)
+        got = eng.read_tokens(i, len(p) - 1, n_new)
+        assert np.array_equal(got, want), i
+        assert float(np.max(np.abs(eng.logits(i) - ora.logits))) <= LOGIT_TOL
+    eng.close()
+
+
+def test_engine_argument_errors():
+    spec = H.TINY
+    eng = H.build_engine(spec, 1, 32)
+    with pytest.raises(L.VeloxError):
+        eng.reserve(0, 33)                      # beyond max_seq_len
+    with pytest.raises(L.VeloxError):
+        eng.reserve(3, 4)                       # slot out of range
+    eng.reserve(0, 16)
+    with pytest.raises(L.VeloxError):
+        eng.prefill(np.zeros(17, dtype=np.uint32))   # beyond the reservation
+    with pytest.raises(L.VeloxError):
+        eng.prefill(np.array([spec.vocab], dtype=np.uint32))  # token out of range
+    with pytest.raises(L.VeloxError):
+        eng.prefill(np.zeros(0, dtype=np.uint32))    # empty prompt
+    with pytest.raises(L.VeloxError):
+        eng.set_state(0, 0, 16)                 # position outside the reservation
+    with pytest.raises(L.VeloxError):
+        eng.set_option("no_such_option", 1)
+    from velox_b200.engine import Engine
+    e2 = Engine(spec, 32)
+    with pytest.raises(L.VeloxError) as ei:
+        e2.decode(1)                            # weights not loaded
+    assert ei.value.code == L.ERR_STATE
+    e2.close()
+    eng.close()
+
+
+def test_kv_pool_exhaustion_and_reuse():
+    spec = H.TINY
+    from velox_b200.engine import Engine
+    eng = Engine(spec, max_seq_len=64, max_batch=2, kv_blocks_total=5)
+    eng.reserve(0, 64)           # 4 blocks
+    with pytest.raises(L.VeloxError) as ei:
+        eng.reserve(1, 48)       # 3 more: pool has 1
+    assert ei.value.code == L.ERR_OOM
+    eng.release(0)
+    eng.reserve(1, 48)
+    eng.close()

@@ -1,12 +1,17 @@
-// Decode attention: flash-decode split-K over the KV length with grouped queries.
+// Decode attention: flash-decode split-K over the KV length with grouped queries, one kernel.
 //
-// Pass 1 (k_attn_split): grid (kv_head x q-head chunk, split, sequence).  A block owns one KV head, the
-// (up to 8) query heads that share it and one slice of the context; its 4 warps walk the slice token by
-// token, every K/V row is read once and used for all the query heads of the group, and each warp keeps an
-// online-softmax state (m, l, acc) per query head.  The block's partial (m, l, unnormalised acc) goes to
-// scratch.  Pass 2 (k_attn_combine) merges the splits.  The reference computes the same quantity with a
-// two-pass softmax on the CPU (src/runtime.rs:772-831) and a sequential online softmax on the GPU
-// (src/runners/tinystories_smollm.cu:321-393); its split-K test is
+// Grid (kv_head x q-head chunk, split, sequence).  A block owns one KV head, the (up to 8) query heads that
+// share it and one slice of the context (a whole number of 16-token KV blocks).  Each of its 4 warps takes 4
+// or 8 tokens at a time: all their K and V rows are requested before anything is computed (the kernel is
+// latency-bound at decode sizes), every row is used for all query heads of the group, the per-lane partial
+// dot products are reduced with a transposing butterfly (one value per lane instead of one reduction per
+// value), and each warp keeps an online-softmax state (m, l, acc) per query head.  The block's partial goes
+// to scratch; the LAST block of a (sequence, head group) to finish -- found with a fence and an atomic
+// counter that it also resets, so the kernel can be replayed from a CUDA graph -- merges the splits.  The
+// merge order is fixed, so results do not depend on which block came last.
+//
+// The reference computes the same quantity with a two-pass softmax on the CPU (src/runtime.rs:772-831) and a
+// sequential online softmax on the GPU (src/runners/tinystories_smollm.cu:321-393); its split-K test is
 // tests/empirical_challenge_phase2/test2_split_k_flashdecoding_parity.cu.
 //
 // The cache is either the reference's contiguous fp32 layout [t][Hkv*D] or this library's paged fp16 pool,
@@ -17,6 +22,7 @@
 namespace vb {
 
 constexpr int ATTN_WARPS = 4;
+constexpr int ATTN_MAX_SPLITS = 64;
 
 struct AttnKArgs {
     AttnArgs a;
@@ -24,7 +30,9 @@ struct AttnKArgs {
     uint32_t G;          // query heads per KV head
     uint32_t g_chunks;   // ceil(G / GM), GM = query heads a block handles at once
     uint32_t n_splits;
+    uint32_t tokens_per_split;
     size_t kv_batch_stride;  // contiguous: elements between sequences
+    uint32_t* counters;      // [batch][Hkv * g_chunks], zero between launches
 };
 
 template <typename KVT, int EPL>
@@ -64,12 +72,37 @@ __device__ __forceinline__ void load_row(const KVT* __restrict__ p, uint32_t lan
     }
 }
 
+// Sums NV per-lane values over the warp; afterwards v[0] of lane L is the total of value (L % NV).
+template <int NV>
+__device__ __forceinline__ void warp_transpose_reduce(float v[NV], uint32_t lane) {
+#pragma unroll
+    for (int off = 16; off >= NV; off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) v[i] += __shfl_xor_sync(0xFFFFFFFFu, v[i], off);
+    }
+#pragma unroll
+    for (int off = (NV > 16 ? 16 : NV / 2), n = NV; off >= 1; off >>= 1, n >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float mine = upper ? v[i + n / 2] : v[i];
+            const float other = upper ? v[i] : v[i + n / 2];
+            v[i] = mine + __shfl_xor_sync(0xFFFFFFFFu, other, off);
+        }
+    }
+}
+
 template <typename KVT, int EPL, int GM>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     const AttnArgs& a = ka.a;
     constexpr int D = EPL * 32;
+    constexpr int TCH = (EPL >= 8) ? 2 : ((GM >= 8) ? 4 : 8);  // tokens a warp handles at once
+    constexpr int NV = TCH * GM;                              // partial dot products per lane (<= 32)
+    static_assert(NV <= 32 && (NV & (NV - 1)) == 0, "values per lane must be a power of two <= 32");
     __shared__ float q_s[GM][D];
+    __shared__ float sc_s[ATTN_WARPS][32];
     __shared__ float part_ml[ATTN_WARPS][GM][2];
+    __shared__ uint32_t is_last_s;
     extern __shared__ __align__(16) float part_acc[];  // [ATTN_WARPS][GM][D]
 
     pdl_wait();
@@ -82,66 +115,95 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     if (a.state && !a.state[b].active) return;
     const uint32_t seq_len = (a.state ? a.state[b].pos : a.pos) + 1;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t t_lo = min(seq_len, split * ka.tokens_per_split), t_hi = min(seq_len, t_lo + ka.tokens_per_split);
 
-    // slice of the context owned by this split (whole KV blocks)
-    uint32_t per = (seq_len + ka.n_splits - 1) / ka.n_splits;
-    per = ((per + a.block_tokens - 1) / a.block_tokens) * a.block_tokens;
-    const uint32_t t_lo = min(seq_len, split * per), t_hi = min(seq_len, t_lo + per);
-
-    const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
-    for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) q_s[i / D][i % D] = qb[i];
-    __syncthreads();
-
-    float m[GM], l[GM], acc[GM][EPL], qr[GM][EPL];
+    float m[GM], l[GM], acc[GM][EPL];
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
         m[g] = -INFINITY; l[g] = 0.0f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) { acc[g][e] = 0.0f; qr[g][e] = (g < (int)ng) ? q_s[g][lane * EPL + e] : 0.0f; }
+        for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
     }
 
-    for (uint32_t t = t_lo + warp; t < t_hi; t += ATTN_WARPS) {
-        const KVT *kp, *vp;
-        if (a.block_table) {
-            const int32_t blk = a.block_table[(size_t)b * a.max_blocks + t / a.block_tokens];
-            const size_t base = (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D + (size_t)(t % a.block_tokens) * D;
-            kp = reinterpret_cast<const KVT*>(a.k) + base;
-            vp = kp + (size_t)a.Hkv * a.block_tokens * D;
-        } else {
-            const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)t * a.Hkv * D + (size_t)kvh * D;
-            kp = reinterpret_cast<const KVT*>(a.k) + off;
-            vp = reinterpret_cast<const KVT*>(a.v) + off;
-        }
-        float kr[EPL], vr[EPL];
-        load_row<KVT, EPL>(kp, lane, kr);
-        load_row<KVT, EPL>(vp, lane, vr);
+    if (t_lo < t_hi) {
+        const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
+        for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) q_s[i / D][i % D] = (i < ng * D) ? qb[i] : 0.0f;
+        __syncthreads();
+        float qr[GM][EPL];
 #pragma unroll
-        for (int g = 0; g < GM; ++g) {
-            if (g < (int)ng) {
-                float dot = 0.0f;
+        for (int g = 0; g < GM; ++g)
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) dot = fmaf(qr[g][e], kr[e], dot);
-                dot = warp_sum(dot);
-                const float s = dot * ka.scale;
-                const float new_m = fmaxf(m[g], s);
-                const float alpha = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - new_m);
-                const float beta = __expf(s - new_m);
-                l[g] = l[g] * alpha + beta;
-                m[g] = new_m;
+            for (int e = 0; e < EPL; ++e) qr[g][e] = q_s[g][lane * EPL + e];
+
+        for (uint32_t t0 = t_lo + warp * TCH; t0 < t_hi; t0 += ATTN_WARPS * TCH) {
+            float kr[TCH][EPL], vr[TCH][EPL];
 #pragma unroll
-                for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(acc[g][e], alpha, beta * vr[e]);
+            for (int i = 0; i < TCH; ++i) {
+                const uint32_t tt = min(t0 + i, t_hi - 1);  // out-of-range tokens re-read the last row, masked below
+                const KVT *kp, *vp;
+                if (a.block_table) {
+                    const int32_t blk = a.block_table[(size_t)b * a.max_blocks + tt / a.block_tokens];
+                    const size_t base = (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D + (size_t)(tt % a.block_tokens) * D;
+                    kp = reinterpret_cast<const KVT*>(a.k) + base;
+                    vp = kp + (size_t)a.Hkv * a.block_tokens * D;
+                } else {
+                    const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
+                    kp = reinterpret_cast<const KVT*>(a.k) + off;
+                    vp = reinterpret_cast<const KVT*>(a.v) + off;
+                }
+                load_row<KVT, EPL>(kp, lane, kr[i]);
+                load_row<KVT, EPL>(vp, lane, vr[i]);
+            }
+            // partial dot products, value index = g * TCH + i
+            float pv[NV];
+#pragma unroll
+            for (int g = 0; g < GM; ++g)
+#pragma unroll
+                for (int i = 0; i < TCH; ++i) {
+                    float d = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) d = fmaf(qr[g][e], kr[i][e], d);
+                    pv[g * TCH + i] = d;
+                }
+            warp_transpose_reduce<NV>(pv, lane);
+            __syncwarp();
+            if (lane < NV) {
+                const uint32_t i = lane % TCH;
+                sc_s[warp][lane] = (t0 + i < t_hi) ? pv[0] * ka.scale : -INFINITY;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < GM; ++g) {
+                float s[TCH];
+                float cmax = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < TCH; ++i) { s[i] = sc_s[warp][g * TCH + i]; cmax = fmaxf(cmax, s[i]); }
+                const float new_m = fmaxf(m[g], cmax);
+                if (new_m != -INFINITY) {
+                    const float alpha = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - new_m);
+                    float p[TCH], psum = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < TCH; ++i) { p[i] = __expf(s[i] - new_m); psum += p[i]; }
+                    l[g] = fmaf(l[g], alpha, psum);
+                    m[g] = new_m;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) {
+                        float v = acc[g][e] * alpha;
+#pragma unroll
+                        for (int i = 0; i < TCH; ++i) v = fmaf(p[i], vr[i][e], v);
+                        acc[g][e] = v;
+                    }
+                }
             }
         }
     }
 
-    // merge the 4 warps
+    // ---- merge the 4 warps, write this split's partial -----------------------------------------------------
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
-        if (g < (int)ng) {
-            if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
+        if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
-        }
+        for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
     }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) {
@@ -162,38 +224,52 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         ps[2 + d] = A;
         if (d == 0) { ps[0] = M; ps[1] = L; }
     }
-}
 
-// grid (Hq, batch), D threads
-__global__ void k_attn_combine(AttnKArgs ka, uint32_t D) {
-    const AttnArgs& a = ka.a;
-    pdl_wait();
-    pdl_launch_dependents();
-    const uint32_t h = blockIdx.x, b = blockIdx.y;
-    if (a.state && !a.state[b].active) return;
-    const float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits) * (D + 2);
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < ka.n_splits; ++s) M = fmaxf(M, ps[(size_t)s * (D + 2)]);
-    for (uint32_t d = threadIdx.x; d < D; d += blockDim.x) {
+    // ---- the last block of this (sequence, head group) merges all splits --------------------------------------
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t* ctr = ka.counters + (size_t)b * gridDim.x + blockIdx.x;
+        const uint32_t prev = atomicAdd(ctr, 1u);
+        const uint32_t last = (prev == ka.n_splits - 1) ? 1u : 0u;
+        if (last) *ctr = 0u;  // ready for the next launch / graph replay
+        is_last_s = last;
+    }
+    __syncthreads();
+    if (!is_last_s) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) {
+        const uint32_t g = i / D, d = i % D;
+        const uint32_t h = kvh * ka.G + g0 + g;
+        const float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits) * (D + 2);
+        float M = -INFINITY;
+        for (uint32_t s = 0; s < ka.n_splits; ++s) M = fmaxf(M, __ldcg(ps + (size_t)s * (D + 2)));
         float L = 0.0f, A = 0.0f;
         for (uint32_t s = 0; s < ka.n_splits; ++s) {
-            const float ms = ps[(size_t)s * (D + 2)];
-            const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
-            L = fmaf(ps[(size_t)s * (D + 2) + 1], f, L);
-            A = fmaf(ps[(size_t)s * (D + 2) + 2 + d], f, A);
+            const float ms = __ldcg(ps + (size_t)s * (D + 2));
+            if (ms == -INFINITY) continue;
+            const float f = __expf(ms - M);
+            L = fmaf(__ldcg(ps + (size_t)s * (D + 2) + 1), f, L);
+            A = fmaf(__ldcg(ps + (size_t)s * (D + 2) + 2 + d), f, A);
         }
         a.out[(size_t)b * a.Hq * D + (size_t)h * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
     }
 }
 
+// scratch: partials [batch][Hq][n_splits][D+2] floats, then counters [batch][Hq] u32 (upper bound)
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits) {
-    return (uint64_t)batch * Hq * max_splits * (D + 2);
+    return (uint64_t)batch * Hq * max_splits * (D + 2) + (uint64_t)batch * Hq + 16;
+}
+// tokens per split: whole KV blocks, at least 32, at most ATTN_MAX_SPLITS splits over max_seq
+uint32_t attn_tokens_per_split(uint32_t max_seq) {
+    uint32_t tps = (max_seq + ATTN_MAX_SPLITS - 1) / ATTN_MAX_SPLITS;
+    tps = ((tps + 15) / 16) * 16;
+    return tps < 32 ? 32 : tps;
 }
 uint32_t attn_pick_splits(uint32_t max_seq) {
-    uint32_t s = (max_seq + 255) / 256;
-    if (s < 1) s = 1;
-    if (s > 32) s = 32;
-    return s;
+    const uint32_t tps = attn_tokens_per_split(max_seq ? max_seq : 1);
+    const uint32_t s = ((max_seq ? max_seq : 1) + tps - 1) / tps;
+    return s < 1 ? 1 : s;
 }
 
 template <typename KVT, int EPL, int GM>
@@ -210,6 +286,7 @@ static cudaError_t launch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
         return launch_split_g<KVT, EPL, 1>(lc, ka);  // wide heads: one query head per block keeps registers in bounds
     } else {
         if (ka.G == 1) return launch_split_g<KVT, EPL, 1>(lc, ka);
+        if (ka.G == 2) return launch_split_g<KVT, EPL, 2>(lc, ka);
         if (ka.G <= 4) return launch_split_g<KVT, EPL, 4>(lc, ka);
         return launch_split_g<KVT, EPL, 8>(lc, ka);
     }
@@ -230,13 +307,14 @@ static cudaError_t dispatch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
 template <typename KVT, int EPL, int GM>
 static cudaError_t opt_in_one() {
     const size_t smem = (size_t)ATTN_WARPS * GM * EPL * 32 * sizeof(float);
-    if (smem <= 32 * 1024) return cudaSuccess;
+    if (smem <= 16 * 1024) return cudaSuccess;
     return cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 template <typename KVT>
 static cudaError_t opt_in_all() {
     cudaError_t e;
     if ((e = opt_in_one<KVT, 4, 8>()) != cudaSuccess) return e;
+    if ((e = opt_in_one<KVT, 4, 4>()) != cudaSuccess) return e;
     if ((e = opt_in_one<KVT, 8, 1>()) != cudaSuccess) return e;
     return opt_in_one<KVT, 16, 1>();
 }
@@ -248,17 +326,17 @@ cudaError_t attn_init() {
 
 cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, size_t kv_batch_stride) {
     if (a.batch == 0 || a.Hq == 0) return cudaSuccess;
-    if (a.Hkv == 0 || a.Hq % a.Hkv != 0) return cudaErrorInvalidValue;
+    if (a.Hkv == 0 || a.Hq % a.Hkv != 0 || a.max_splits == 0 || a.tokens_per_split == 0) return cudaErrorInvalidValue;
     AttnKArgs ka;
     ka.a = a;
     ka.scale = (scale != 0.0f) ? scale : 1.0f / sqrtf((float)a.D);
     ka.G = a.Hq / a.Hkv;
     ka.g_chunks = 1;
-    ka.n_splits = a.max_splits ? a.max_splits : 1;
+    ka.n_splits = a.max_splits;
+    ka.tokens_per_split = a.tokens_per_split;
     ka.kv_batch_stride = kv_batch_stride;
-    cudaError_t e = a.kv_fp16 ? dispatch_split<__half>(lc, ka) : dispatch_split<float>(lc, ka);
-    if (e != cudaSuccess) return e;
-    return launch(lc, k_attn_combine, dim3(a.Hq, a.batch), dim3(a.D < 128 ? a.D : 128), 0, ka, a.D);
+    ka.counters = reinterpret_cast<uint32_t*>(a.scratch + (uint64_t)a.batch * a.Hq * a.max_splits * (a.D + 2));
+    return a.kv_fp16 ? dispatch_split<__half>(lc, ka) : dispatch_split<float>(lc, ka);
 }
 
 cudaError_t attention(const LaunchCfg& lc, const AttnArgs& a) { return attention_ex(lc, a, 0.0f, 0); }
@@ -278,18 +356,23 @@ extern "C" int32_t vb_op_gqa_attention(float* out, const float* q, const float* 
     a.out = out; a.q = q; a.k = k_cache; a.v = v_cache; a.kv_fp16 = 0;
     a.pos = pos; a.Hq = n_q; a.Hkv = n_kv; a.D = head_dim; a.batch = 1;
     a.max_splits = attn_pick_splits(pos + 1);
+    a.tokens_per_split = attn_tokens_per_split(pos + 1);
     a.scratch = (float*)scratch;
-    VB_REQUIRE(scratch_bytes >= attn_scratch_floats(n_q, head_dim, 1, a.max_splits) * 4,
-               "vb_op_gqa_attention: scratch too small (%llu bytes)", (unsigned long long)scratch_bytes);
+    const uint64_t need = attn_scratch_floats(n_q, head_dim, 1, a.max_splits) * 4;
+    VB_REQUIRE(scratch_bytes >= need, "vb_op_gqa_attention: scratch too small (%llu bytes, %llu needed)",
+               (unsigned long long)scratch_bytes, (unsigned long long)need);
     LaunchCfg lc; lc.stream = (cudaStream_t)stream;
     VB_CUDA(kernels_init());
+    // the split counters must start at zero; a caller's scratch is not
+    VB_CUDA(cudaMemsetAsync((float*)scratch + (uint64_t)n_q * a.max_splits * (head_dim + 2), 0, (size_t)n_q * 4 + 64, lc.stream));
     VB_CUDA(attention(lc, a));
     return VB_OK;
 }
 
 extern "C" uint64_t vb_op_scratch_bytes(uint32_t n_q_heads, uint32_t head_dim, uint32_t max_seq, uint32_t vocab) {
-    uint64_t a = attn_scratch_floats(n_q_heads ? n_q_heads : 1, head_dim, 1, attn_pick_splits(max_seq)) * 4;
+    const uint32_t hq = n_q_heads ? n_q_heads : 1, d = head_dim ? head_dim : 1;
+    uint64_t a = attn_scratch_floats(hq, d, 1, attn_pick_splits(max_seq)) * 4;
     uint64_t b = (uint64_t)argmax_chunks(vocab ? vocab : 1) * 8;
-    uint64_t m = (uint64_t)(head_dim > 0 ? head_dim : 1) * 16;  // q_abs + bookkeeping of the MLA op
+    uint64_t m = mla_scratch_floats(0, d) * 4;
     return a + b + m + 4096;
 }

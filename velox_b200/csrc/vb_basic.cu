@@ -316,13 +316,21 @@ cudaError_t rmsnorm(const LaunchCfg& lc, float* dst, const float* x, const void*
     return launch(lc, k_rmsnorm, dim3(batch), dim3(256), 0, dst, x, w, w_fmt, dim, eps);
 }
 
+// 1/theta^(2j/D) as the reference computes it in fp32 (src/runtime.rs:758).  The host libm's powf is correctly
+// rounded; evaluating pow in double and rounding once gives the same fp32 value, whereas the device powf may
+// be 2 ulp off, which at position 2047 already moves the angle by 1e-4 rad.
+__device__ __forceinline__ float rope_inv_freq(float theta, uint32_t j, uint32_t head_dim) {
+    const float expo = (float)(2 * j) / (float)head_dim;
+    return 1.0f / (float)pow((double)theta, (double)expo);
+}
+
 // ---- RoPE (stand-alone op) ----------------------------------------------------------------------------------
 __global__ void k_rope(float* __restrict__ t, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta) {
     const uint32_t half = head_dim / 2;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_heads * half) return;
     const uint32_t h = i / half, j = i % half;
-    const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)head_dim);
+    const float freq = rope_inv_freq(theta, j, head_dim);
     const float angle = (float)pos * freq;
     float s, c;
     sincosf(angle, &s, &c);
@@ -360,7 +368,7 @@ __global__ void k_bias_rope_kv_append(float* __restrict__ q_out, const float* __
     // pool layout per layer: [block][K|V][kv_head][block_tokens][D]
     if (i < n_rot) {
         const uint32_t h = i / half, j = i % half;
-        const float freq = 1.0f / powf(theta, (float)(2 * j) / (float)D);
+        const float freq = rope_inv_freq(theta, j, D);
         const float angle = (float)pos * freq;
         float s, c;
         sincosf(angle, &s, &c);

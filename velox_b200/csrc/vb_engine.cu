@@ -32,7 +32,7 @@ struct vb_ctx {
     bool use_pdl = true;
 
     // derived
-    uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1;
+    uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1, tokens_per_split = 32;
 
     // weight arena (execution order, 256-byte aligned slabs)
     uint8_t* arena = nullptr;
@@ -105,7 +105,7 @@ bool role_shape(const vb_ctx* c, int role, uint32_t* rows, uint32_t* cols, int32
 int32_t plan_arena(vb_ctx* c) {
     uint64_t off = 0;
     // pass 1: compute offsets; pass 2 (after allocation) turns them into pointers
-    struct Slot { int role, layer; uint64_t data, scales; };
+    struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales; bool has_tiled; };
     std::vector<Slot> slots;
     auto add_group = [&](std::initializer_list<int> roles, int layer) {
         // data of all members first (contiguous rows), then their scales (contiguous too)
@@ -115,16 +115,33 @@ int32_t plan_arena(vb_ctx* c) {
             if (!role_shape(c, role, &rows, &cols, &fmt)) continue;
             Tensor& t = c->tensor(role, layer);
             t.m.fmt = fmt; t.m.rows = rows; t.m.cols = cols;
-            g.push_back({role, layer, off, 0});
+            g.push_back({role, layer, off, 0, 0, 0, false});
             off += wmat_data_bytes(fmt, rows, cols);
         }
         off = align256(off);
+        bool tile_all = !g.empty();
         for (Slot& s : g) {
             Tensor& t = c->tensor(s.role, s.layer);
             s.scales = off;
             off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+            if (t.m.fmt != VB_FMT_Q4G32 || !tile_q4_supported(t.m.rows, t.m.cols)) tile_all = false;
         }
         off = align256(off);
+        if (tile_all) {
+            // tile-major copies for the tuned kernel, members adjacent again (fused QKV = one tiled matrix)
+            for (Slot& s : g) {
+                Tensor& t = c->tensor(s.role, s.layer);
+                s.has_tiled = true; s.tiled = off;
+                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols);
+            }
+            off = align256(off);
+            for (Slot& s : g) {
+                Tensor& t = c->tensor(s.role, s.layer);
+                s.tiled_scales = off;
+                off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+            }
+            off = align256(off);
+        }
         for (Slot& s : g) slots.push_back(s);
     };
     for (uint32_t l = 0; l < c->d.n_layers; ++l) {
@@ -147,6 +164,7 @@ int32_t plan_arena(vb_ctx* c) {
         Tensor& t = c->tensor(s.role, s.layer);
         t.m.data = c->arena + s.data;
         t.m.scales = wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols) ? c->arena + s.scales : nullptr;
+        if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; }
     }
     if (c->d.tied_lm_head) {
         Tensor& h = c->tensor(VB_ROLE_LM_HEAD, 0);
@@ -225,7 +243,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         a.out = c->attn_out; a.q = c->q; a.k = kv_layer; a.kv_fp16 = 1;
         a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
         a.state = state; a.Hq = d.n_q_heads; a.Hkv = d.n_kv_heads; a.D = d.head_dim; a.batch = B;
-        a.max_splits = c->n_splits; a.scratch = c->attn_scratch;
+        a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
@@ -300,6 +318,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     c->max_blocks = (d.max_seq_len + d.kv_block_tokens - 1) / d.kv_block_tokens;
     c->n_blocks = d.kv_blocks_total ? d.kv_blocks_total : d.max_batch * c->max_blocks;
     c->n_splits = attn_pick_splits(d.max_seq_len);
+    c->tokens_per_split = attn_tokens_per_split(d.max_seq_len);
     c->t.resize((size_t)VB_ROLE_COUNT * d.n_layers);
     int32_t rc = VB_OK;
     cudaError_t e;
@@ -334,6 +353,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     VB_CREATE_TRY(dev_alloc(&c->act, B * d.ffn_dim));
     VB_CREATE_TRY(dev_alloc(&c->logits, B * d.vocab));
     VB_CREATE_TRY(dev_alloc(&c->attn_scratch, attn_scratch_floats(d.n_q_heads, d.head_dim, d.max_batch, c->n_splits)));
+    VB_CREATE_CUDA(cudaMemsetAsync(c->attn_scratch, 0, attn_scratch_floats(d.n_q_heads, d.head_dim, d.max_batch, c->n_splits) * 4, c->stream));
     VB_CREATE_TRY(dev_alloc(&c->cand_v, B * argmax_chunks(d.vocab)));
     VB_CREATE_TRY(dev_alloc(&c->cand_i, B * argmax_chunks(d.vocab)));
     VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
@@ -376,6 +396,15 @@ static int32_t load_common(vb_ctx* c, int32_t role, int32_t layer, uint64_t rows
     return VB_OK;
 }
 
+static int32_t finish_load(vb_ctx* c, Tensor* t) {
+    if (!t->m.tiled) return VB_OK;
+    LaunchCfg lc = lcfg(c, false);
+    lc.counter = nullptr;
+    VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), t->m.data, t->m.scales, t->m.rows, t->m.cols));
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    return VB_OK;
+}
+
 static void mark_loaded(vb_ctx* c, int32_t role, Tensor* t) {
     t->loaded = true;
     if (role == VB_ROLE_EMBED && c->d.tied_lm_head) c->tensor(VB_ROLE_LM_HEAD, 0) = *t;  // tied: the head reads the table
@@ -412,6 +441,7 @@ int32_t vb_load_tensor(vb_ctx* c, int32_t role, int32_t layer, const void* src, 
     if (raw) cudaFree(raw);
     if (f32) cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor", __FILE__, __LINE__);
+    if ((rc = finish_load(c, t)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -427,6 +457,7 @@ int32_t vb_load_tensor_packed(vb_ctx* c, int32_t role, int32_t layer, const void
     VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.data), data, db, kind, c->stream));
     if (sb) VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.scales), scales, sb, kind, c->stream));
     VB_CUDA(cudaStreamSynchronize(c->stream));
+    if ((rc = finish_load(c, t)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -447,6 +478,7 @@ int32_t vb_load_tensor_synthetic(vb_ctx* c, int32_t role, int32_t layer, uint64_
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor_synthetic", __FILE__, __LINE__);
+    if ((rc = finish_load(c, t)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }

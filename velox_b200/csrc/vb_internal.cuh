@@ -41,6 +41,9 @@ struct WMat {
     const void* scales = nullptr;
     int32_t fmt = VB_FMT_F32;
     uint32_t rows = 0, cols = 0;
+    // optional tile-major copy for the tuned int4 kernel (see vb_gemv_fast.cu); null when absent
+    const void* tiled = nullptr;
+    const void* tiled_scales = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {

@@ -50,6 +50,11 @@ struct GemvArgs {
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
 
+// vb_gemv_fast.cu
+bool tile_q4_supported(uint32_t rows, uint32_t K);
+cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const void* canon, const void* canon_scales,
+                    uint32_t rows, uint32_t K);
+
 // vb_attn.cu
 struct AttnArgs {
     float* out = nullptr;          // [batch][Hq*D]
@@ -62,11 +67,13 @@ struct AttnArgs {
     const SeqState* state = nullptr;  // paged: seq_len = state[b].pos + 1
     uint32_t pos = 0;                 // contiguous: attends [0..pos]
     uint32_t Hq = 0, Hkv = 0, D = 0, batch = 1;
-    uint32_t max_splits = 1;
-    float* scratch = nullptr;      // [batch][Hq][max_splits][D+2]
+    uint32_t max_splits = 1;       // grid size along the context (fixed per context so that graphs replay)
+    uint32_t tokens_per_split = 32; // multiple of block_tokens
+    float* scratch = nullptr;      // attn_scratch_floats(): partials, then the split counters (zero before the first launch)
 };
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits);
 uint32_t attn_pick_splits(uint32_t max_seq);
+uint32_t attn_tokens_per_split(uint32_t max_seq);
 cudaError_t attention(const LaunchCfg& lc, const AttnArgs& a);
 cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, size_t kv_batch_stride);
 

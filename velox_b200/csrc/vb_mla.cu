@@ -13,7 +13,7 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
 // scratch: q_abs [latent] | ctx [latent] | attention partials
 uint64_t mla_scratch_floats(uint32_t hidden, uint32_t latent) {
     (void)hidden;
-    return 2ULL * latent + attn_scratch_floats(1, latent, 1, 32) + 64;
+    return 2ULL * latent + attn_scratch_floats(1, latent, 1, 64) + 64;
 }
 
 cudaError_t mla_absorbed(const LaunchCfg& lc, float* dst, const float* x, const float* w_norm, const float* w_dkv,
@@ -35,7 +35,10 @@ cudaError_t mla_absorbed(const LaunchCfg& lc, float* dst, const float* x, const 
     a.out = ctx; a.q = q_abs; a.k = pool; a.v = pool; a.kv_fp16 = 0; a.pos = safe_step;
     a.Hq = 1; a.Hkv = 1; a.D = latent; a.batch = 1; a.block_tokens = 16;
     a.max_splits = attn_pick_splits(safe_step + 1);
+    a.tokens_per_split = attn_tokens_per_split(safe_step + 1);
     a.scratch = part;
+    // split counters start at zero
+    if ((e = cudaMemsetAsync(part + (size_t)a.max_splits * (latent + 2), 0, 64, lc.stream)) != cudaSuccess) return e;
     const float scale = (latent >= 128) ? (1.0f / sqrtf(128.0f)) : (1.0f / sqrtf((float)latent));
     if ((e = attention_ex(lc, a, scale, 0)) != cudaSuccess) return e;
     if (dst != x) {

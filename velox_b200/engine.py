@@ -128,7 +128,7 @@ class Engine:
     def forward_step(self, token: int, pos: int, slot: int = 0) -> int:
         """src/runtime.rs:1328: one token at `pos`; returns the greedy next token."""
         self.set_state(slot, token, pos, True)
-        L.check(self._lib.vb_decode_step(self.h))
+        L.check(self._lib.vb_decode_run(self.h, 1, None))  # replays the captured graph when there is one
         return int(self.read_tokens(slot, pos, 1)[0])
 
     def prefill(self, prompt, slot: int = 0):
