@@ -72,6 +72,11 @@ __device__ __forceinline__ void load_row(const KVT* __restrict__ p, uint32_t lan
     }
 }
 
+__device__ __forceinline__ float bias_at(const void* w, int fmt, uint32_t i) {
+    return fmt == VB_FMT_F16 ? __half2float(((const __half*)w)[i])
+         : fmt == VB_FMT_BF16 ? __bfloat162float(((const __nv_bfloat16*)w)[i]) : ((const float*)w)[i];
+}
+
 // Sums NV per-lane values over the warp; afterwards v[0] of lane L is the total of value (L % NV).
 template <int NV>
 __device__ __forceinline__ void warp_transpose_reduce(float v[NV], uint32_t lane) {
@@ -126,9 +131,49 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     }
 
     if (t_lo < t_hi) {
-        const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
-        for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) q_s[i / D][i % D] = (i < ng * D) ? qb[i] : 0.0f;
-        __syncthreads();
+        if (a.qkv_raw) {
+            // fused bias + RoPE on the raw projections; the block whose slice holds `pos` appends K and V
+            const uint32_t pos = seq_len - 1, half = D / 2;
+            const float* raw = a.qkv_raw + (size_t)b * (a.Hq + 2 * a.Hkv) * D;
+            for (uint32_t i = threadIdx.x; i < GM * half; i += blockDim.x) {
+                const uint32_t g = i / half, j = i % half;
+                float r1 = 0.0f, r2 = 0.0f;
+                if (g < ng) {
+                    const uint32_t h = kvh * ka.G + g0 + g;
+                    float x1 = raw[(size_t)h * D + j], x2 = raw[(size_t)h * D + j + half];
+                    if (a.bq) { x1 += bias_at(a.bq, a.bias_fmt, h * D + j); x2 += bias_at(a.bq, a.bias_fmt, h * D + j + half); }
+                    float sn, cs;
+                    sincosf((float)pos * a.rope_inv_freq[j], &sn, &cs);
+                    r1 = x1 * cs - x2 * sn;
+                    r2 = x2 * cs + x1 * sn;
+                }
+                q_s[g][j] = r1;
+                q_s[g][j + half] = r2;
+            }
+            if (t_lo <= pos && pos < t_hi && gc == 0) {
+                const int32_t blk = a.block_table[(size_t)b * a.max_blocks + pos / a.block_tokens];
+                __half* kd = reinterpret_cast<__half*>(const_cast<void*>(a.k)) +
+                             (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D + (size_t)(pos % a.block_tokens) * D;
+                __half* vd = kd + (size_t)a.Hkv * a.block_tokens * D;
+                const float* kr_raw = raw + (size_t)a.Hq * D + (size_t)kvh * D;
+                const float* vr_raw = raw + (size_t)(a.Hq + a.Hkv) * D + (size_t)kvh * D;
+                for (uint32_t j = threadIdx.x; j < half; j += blockDim.x) {
+                    float x1 = kr_raw[j], x2 = kr_raw[j + half], v1 = vr_raw[j], v2 = vr_raw[j + half];
+                    if (a.bk) { x1 += bias_at(a.bk, a.bias_fmt, kvh * D + j); x2 += bias_at(a.bk, a.bias_fmt, kvh * D + j + half); }
+                    if (a.bv) { v1 += bias_at(a.bv, a.bias_fmt, kvh * D + j); v2 += bias_at(a.bv, a.bias_fmt, kvh * D + j + half); }
+                    float sn, cs;
+                    sincosf((float)pos * a.rope_inv_freq[j], &sn, &cs);
+                    kd[j] = __float2half_rn(x1 * cs - x2 * sn);
+                    kd[j + half] = __float2half_rn(x2 * cs + x1 * sn);
+                    vd[j] = __float2half_rn(v1);
+                    vd[j + half] = __float2half_rn(v2);
+                }
+            }
+        } else {
+            const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
+            for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) q_s[i / D][i % D] = (i < ng * D) ? qb[i] : 0.0f;
+        }
+        __syncthreads();  // q_s complete; the appended K/V row (written by this block) is visible to it
         float qr[GM][EPL];
 #pragma unroll
         for (int g = 0; g < GM; ++g)
@@ -238,19 +283,29 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     __syncthreads();
     if (!is_last_s) return;
     __threadfence();
+    // every split's (m, l) first, all loads in flight at once; then the weighted sum with the loads unrolled
+    float* ml = part_acc;  // [GM][n_splits][2], reuses the merge buffer (n_splits <= 64)
+    for (uint32_t i = threadIdx.x; i < ng * ka.n_splits; i += blockDim.x) {
+        const uint32_t g = i / ka.n_splits, sidx = i % ka.n_splits;
+        const float* ps = a.scratch + (((size_t)b * a.Hq + kvh * ka.G + g0 + g) * ka.n_splits + sidx) * (D + 2);
+        ml[2 * i] = __ldcg(ps);
+        ml[2 * i + 1] = __ldcg(ps + 1);
+    }
+    __syncthreads();
     for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) {
         const uint32_t g = i / D, d = i % D;
         const uint32_t h = kvh * ka.G + g0 + g;
-        const float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits) * (D + 2);
+        const float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits) * (D + 2) + 2 + d;
+        const float* mlg = ml + (size_t)g * ka.n_splits * 2;
         float M = -INFINITY;
-        for (uint32_t s = 0; s < ka.n_splits; ++s) M = fmaxf(M, __ldcg(ps + (size_t)s * (D + 2)));
+        for (uint32_t sidx = 0; sidx < ka.n_splits; ++sidx) M = fmaxf(M, mlg[2 * sidx]);
         float L = 0.0f, A = 0.0f;
-        for (uint32_t s = 0; s < ka.n_splits; ++s) {
-            const float ms = __ldcg(ps + (size_t)s * (D + 2));
-            if (ms == -INFINITY) continue;
-            const float f = __expf(ms - M);
-            L = fmaf(__ldcg(ps + (size_t)s * (D + 2) + 1), f, L);
-            A = fmaf(__ldcg(ps + (size_t)s * (D + 2) + 2 + d), f, A);
+#pragma unroll 8
+        for (uint32_t sidx = 0; sidx < ka.n_splits; ++sidx) {
+            const float ms = mlg[2 * sidx];
+            const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
+            L = fmaf(mlg[2 * sidx + 1], f, L);
+            A = fmaf(__ldcg(ps + (size_t)sidx * (D + 2)), f, A);
         }
         a.out[(size_t)b * a.Hq * D + (size_t)h * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
     }

@@ -2,6 +2,9 @@
 // the activation buffers, the device-resident per-sequence state and the mapped token ring -- the role of
 // the reference's host runner (src/runners/velox_cuda_runner.cu:417-487) plus the launch sequence its
 // compiler emits per model (src/runners/tinystories_smollm.cu:2388-3249).
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <new>
@@ -30,6 +33,8 @@ struct vb_ctx {
     uint64_t launches = 0;
     int gemv_path = 1;
     bool use_pdl = true;
+    bool fuse_append = true;
+    float* rope_inv_freq = nullptr;  // [head_dim/2]
 
     // derived
     uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1, tokens_per_split = 32;
@@ -107,6 +112,7 @@ int32_t plan_arena(vb_ctx* c) {
     // pass 1: compute offsets; pass 2 (after allocation) turns them into pointers
     struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales; bool has_tiled; };
     std::vector<Slot> slots;
+    std::vector<uint64_t> swiglu_off;
     auto add_group = [&](std::initializer_list<int> roles, int layer) {
         // data of all members first (contiguous rows), then their scales (contiguous too)
         std::vector<Slot> g;
@@ -131,14 +137,8 @@ int32_t plan_arena(vb_ctx* c) {
             // tile-major copies for the tuned kernel, members adjacent again (fused QKV = one tiled matrix)
             for (Slot& s : g) {
                 Tensor& t = c->tensor(s.role, s.layer);
-                s.has_tiled = true; s.tiled = off;
-                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols);
-            }
-            off = align256(off);
-            for (Slot& s : g) {
-                Tensor& t = c->tensor(s.role, s.layer);
-                s.tiled_scales = off;
-                off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+                s.has_tiled = true; s.tiled = off; s.tiled_scales = off;  // scales are interleaved block by block
+                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
             }
             off = align256(off);
         }
@@ -152,6 +152,17 @@ int32_t plan_arena(vb_ctx* c) {
         add_group({VB_ROLE_MLP_NORM}, (int)l);
         add_group({VB_ROLE_WGATE}, (int)l);
         add_group({VB_ROLE_WUP}, (int)l);
+        {
+            // gate and up interleaved 8 rows by 8 rows for the fused SwiGLU kernel
+            Tensor& tg = c->tensor(VB_ROLE_WGATE, (int)l);
+            if (tg.m.fmt == VB_FMT_Q4G32 && tg.m.rows % 8 == 0 && tg.m.cols % 128 == 0) {
+                swiglu_off.push_back(off);
+                off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
+                off = align256(off);
+            } else {
+                swiglu_off.push_back(~0ULL);
+            }
+        }
         add_group({VB_ROLE_WDOWN}, (int)l);
     }
     add_group({VB_ROLE_FINAL_NORM}, 0);
@@ -166,6 +177,8 @@ int32_t plan_arena(vb_ctx* c) {
         t.m.scales = wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols) ? c->arena + s.scales : nullptr;
         if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; }
     }
+    for (uint32_t l = 0; l < c->d.n_layers; ++l)
+        if (swiglu_off[l] != ~0ULL) c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
     if (c->d.tied_lm_head) {
         Tensor& h = c->tensor(VB_ROLE_LM_HEAD, 0);
         h = c->tensor(VB_ROLE_EMBED, 0);
@@ -236,11 +249,14 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
             bq = c->tensor(VB_ROLE_BQ, L).m.data; bk = c->tensor(VB_ROLE_BK, L).m.data; bv = c->tensor(VB_ROLE_BV, L).m.data;
             bf = c->tensor(VB_ROLE_BQ, L).m.fmt;
         }
-        VB_TRY(bias_rope_kv_append(lcfg(c, true), c->q, c->qkv, state, bq, bk, bv, bf, kv_layer, c->block_table_dev,
-                                   c->max_blocks, d.n_q_heads, d.n_kv_heads, d.head_dim, d.kv_block_tokens, d.rope_theta, B));
-        // split-K attention over the paged cache
+        const bool fused_append = (d.n_q_heads / d.n_kv_heads) <= 8 && c->fuse_append;
+        if (!fused_append)
+            VB_TRY(bias_rope_kv_append(lcfg(c, true), c->q, c->qkv, state, bq, bk, bv, bf, kv_layer, c->block_table_dev,
+                                       c->max_blocks, d.n_q_heads, d.n_kv_heads, d.head_dim, d.kv_block_tokens, d.rope_theta, B));
+        // split-K attention over the paged cache (with the bias + RoPE + KV append fused in when possible)
         AttnArgs a;
         a.out = c->attn_out; a.q = c->q; a.k = kv_layer; a.kv_fp16 = 1;
+        if (fused_append) { a.qkv_raw = c->qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; }
         a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
         a.state = state; a.Hq = d.n_q_heads; a.Hkv = d.n_kv_heads; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
@@ -356,6 +372,14 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     VB_CREATE_CUDA(cudaMemsetAsync(c->attn_scratch, 0, attn_scratch_floats(d.n_q_heads, d.head_dim, d.max_batch, c->n_splits) * 4, c->stream));
     VB_CREATE_TRY(dev_alloc(&c->cand_v, B * argmax_chunks(d.vocab)));
     VB_CREATE_TRY(dev_alloc(&c->cand_i, B * argmax_chunks(d.vocab)));
+    {
+        // RoPE frequencies exactly as the reference computes them on the host (src/runtime.rs:758)
+        std::vector<float> f(d.head_dim / 2);
+        for (uint32_t j = 0; j < d.head_dim / 2; ++j) f[j] = 1.0f / powf(d.rope_theta, (float)(2 * j) / (float)d.head_dim);
+        VB_CREATE_TRY(dev_alloc(&c->rope_inv_freq, f.size()));
+        VB_CREATE_CUDA(cudaMemcpyAsync(c->rope_inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice, c->stream));
+        VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
+    }
     VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
 #undef VB_CREATE_TRY
 #undef VB_CREATE_CUDA
@@ -370,7 +394,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
     if (c->graph) cudaGraphDestroy(c->graph);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
-                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i};
+                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -396,11 +420,15 @@ static int32_t load_common(vb_ctx* c, int32_t role, int32_t layer, uint64_t rows
     return VB_OK;
 }
 
-static int32_t finish_load(vb_ctx* c, Tensor* t) {
+static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer) {
     if (!t->m.tiled) return VB_OK;
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
     VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), t->m.data, t->m.scales, t->m.rows, t->m.cols));
+    if (role == VB_ROLE_WGATE || role == VB_ROLE_WUP) {
+        const void* il = c->tensor(VB_ROLE_WGATE, layer).m.tiled_swiglu;
+        if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), t->m.data, t->m.scales, t->m.rows, t->m.cols, role == VB_ROLE_WUP ? 1 : 0));
+    }
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;
 }
@@ -441,7 +469,7 @@ int32_t vb_load_tensor(vb_ctx* c, int32_t role, int32_t layer, const void* src, 
     if (raw) cudaFree(raw);
     if (f32) cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor", __FILE__, __LINE__);
-    if ((rc = finish_load(c, t)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -457,7 +485,7 @@ int32_t vb_load_tensor_packed(vb_ctx* c, int32_t role, int32_t layer, const void
     VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.data), data, db, kind, c->stream));
     if (sb) VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.scales), scales, sb, kind, c->stream));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    if ((rc = finish_load(c, t)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -478,7 +506,7 @@ int32_t vb_load_tensor_synthetic(vb_ctx* c, int32_t role, int32_t layer, uint64_
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor_synthetic", __FILE__, __LINE__);
-    if ((rc = finish_load(c, t)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -599,11 +627,17 @@ int32_t vb_decode_graph_build(vb_ctx* c) {
         cudaError_t e3 = cudaSuccess;
         if (e == cudaSuccess && e2 == cudaSuccess) {
             e3 = cudaGraphInstantiate(&c->graph_exec, g, 0);
-            if (e3 == cudaSuccess) { c->graph = g; return VB_OK; }
+            if (e3 == cudaSuccess) {
+                c->graph = g;
+                if (getenv("VELOX_B200_DEBUG")) fprintf(stderr, "[velox_b200] decode graph: %llu kernel nodes, pdl=%d\n", (unsigned long long)c->graph_nodes, (int)c->use_pdl);
+                return VB_OK;
+            }
         }
         if (g) cudaGraphDestroy(g);
         c->graph_exec = nullptr;
         (void)cudaGetLastError();
+        if (getenv("VELOX_B200_DEBUG")) fprintf(stderr, "[velox_b200] graph capture attempt %d failed: %s / %s / %s\n", attempt,
+                                                cudaGetErrorString(e), cudaGetErrorString(e2), cudaGetErrorString(e3));
         if (attempt == 0 && c->use_pdl) { c->use_pdl = false; continue; }  // capture without programmatic edges
         return cuda_fail(e != cudaSuccess ? e : (e2 != cudaSuccess ? e2 : e3), "capture(decode step)", __FILE__, __LINE__);
     }
@@ -631,11 +665,26 @@ int32_t vb_decode_run(vb_ctx* c, uint32_t n_steps, float* elapsed_ms) {
     return VB_OK;
 }
 
+// Reads (and clears) the device error word that bounded device-side waits set when they expire.
+static int32_t check_device_error(vb_ctx* c) {
+    uint32_t* w = nullptr;
+    VB_CUDA(fast_error_word(&w));
+    uint32_t v = 0;
+    VB_CUDA(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
+    if (v != 0) {
+        cudaMemset(w, 0, 4);
+        set_error("a bounded device-side wait expired (code 0x%x): results of the last launches are invalid", v);
+        return VB_ERR_TIMEOUT;
+    }
+    (void)c;
+    return VB_OK;
+}
+
 int32_t vb_sync(vb_ctx* c) {
     VB_REQUIRE(c != nullptr, "vb_sync: null context");
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    return VB_OK;
+    return check_device_error(c);
 }
 
 int32_t vb_read_tokens(vb_ctx* c, int32_t slot, uint32_t first_pos, uint32_t n, uint32_t* out) {
@@ -644,6 +693,7 @@ int32_t vb_read_tokens(vb_ctx* c, int32_t slot, uint32_t first_pos, uint32_t n, 
     VB_REQUIRE(n <= RING_SLOTS, "vb_read_tokens: at most %u tokens stay in the ring", RING_SLOTS);
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaStreamSynchronize(c->stream));
+    { int32_t rc = check_device_error(c); if (rc != VB_OK) return rc; }
     for (uint32_t i = 0; i < n; ++i) out[i] = c->ring_host[(size_t)slot * RING_SLOTS + ((first_pos + i) % RING_SLOTS)];
     return VB_OK;
 }
@@ -715,6 +765,8 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     if (!strcmp(name, "gemv_path")) { c->gemv_path = (int)value; return VB_OK; }
     if (!strcmp(name, "pdl")) { c->use_pdl = value != 0; return VB_OK; }
+    if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
+    if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
     set_error("vb_set_option: unknown option '%s'", name);
     return VB_ERR_INVALID;
 }

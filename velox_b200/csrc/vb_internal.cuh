@@ -44,6 +44,8 @@ struct WMat {
     // optional tile-major copy for the tuned int4 kernel (see vb_gemv_fast.cu); null when absent
     const void* tiled = nullptr;
     const void* tiled_scales = nullptr;
+    // gate matrices only: gate and up interleaved 8 rows by 8 rows in one tile-major matrix of 2*rows rows
+    const void* tiled_swiglu = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {

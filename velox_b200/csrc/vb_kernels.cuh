@@ -52,13 +52,23 @@ cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
 
 // vb_gemv_fast.cu
 bool tile_q4_supported(uint32_t rows, uint32_t K);
+cudaError_t tile_q4_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K,
+                           int which);
+extern bool fast_use_tma;
+cudaError_t fast_error_word(uint32_t** out);
 cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const void* canon, const void* canon_scales,
                     uint32_t rows, uint32_t K);
 
 // vb_attn.cu
 struct AttnArgs {
     float* out = nullptr;          // [batch][Hq*D]
-    const float* q = nullptr;      // [batch][Hq*D] (RoPE applied)
+    const float* q = nullptr;      // [batch][Hq*D] (RoPE applied); unused when qkv_raw is given
+    // fused mode (paged fp16 cache, Hq/Hkv <= 8): raw projections [batch][(Hq+2Hkv)*D]; the kernel adds the
+    // biases, applies RoPE at the sequence's position and appends K/V to the cache before attending
+    const float* qkv_raw = nullptr;
+    const void *bq = nullptr, *bk = nullptr, *bv = nullptr;
+    int bias_fmt = VB_FMT_F32;
+    const float* rope_inv_freq = nullptr;  // [D/2], 1/theta^(2j/D)
     const void* k = nullptr;       // contiguous: [seq][Hkv*D]; paged: the layer's pool
     const void* v = nullptr;       // contiguous only
     int kv_fp16 = 0;               // element type of the cache
