@@ -110,9 +110,9 @@ bool role_shape(const vb_ctx* c, int role, uint32_t* rows, uint32_t* cols, int32
 int32_t plan_arena(vb_ctx* c) {
     uint64_t off = 0;
     // pass 1: compute offsets; pass 2 (after allocation) turns them into pointers
-    struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales; bool has_tiled; };
+    struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales, v3; bool has_tiled; };
     std::vector<Slot> slots;
-    std::vector<uint64_t> swiglu_off;
+    std::vector<uint64_t> swiglu_off, swiglu_v3_off;
     auto add_group = [&](std::initializer_list<int> roles, int layer) {
         // data of all members first (contiguous rows), then their scales (contiguous too)
         std::vector<Slot> g;
@@ -121,7 +121,7 @@ int32_t plan_arena(vb_ctx* c) {
             if (!role_shape(c, role, &rows, &cols, &fmt)) continue;
             Tensor& t = c->tensor(role, layer);
             t.m.fmt = fmt; t.m.rows = rows; t.m.cols = cols;
-            g.push_back({role, layer, off, 0, 0, 0, false});
+            g.push_back({role, layer, off, 0, 0, 0, 0, false});
             off += wmat_data_bytes(fmt, rows, cols);
         }
         off = align256(off);
@@ -138,6 +138,12 @@ int32_t plan_arena(vb_ctx* c) {
             for (Slot& s : g) {
                 Tensor& t = c->tensor(s.role, s.layer);
                 s.has_tiled = true; s.tiled = off; s.tiled_scales = off;  // scales are interleaved block by block
+                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+            }
+            off = align256(off);
+            for (Slot& s : g) {  // and the integer tensor-core layout
+                Tensor& t = c->tensor(s.role, s.layer);
+                s.v3 = off;
                 off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
             }
             off = align256(off);
@@ -159,8 +165,12 @@ int32_t plan_arena(vb_ctx* c) {
                 swiglu_off.push_back(off);
                 off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
                 off = align256(off);
+                swiglu_v3_off.push_back(off);
+                off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
+                off = align256(off);
             } else {
                 swiglu_off.push_back(~0ULL);
+                swiglu_v3_off.push_back(~0ULL);
             }
         }
         add_group({VB_ROLE_WDOWN}, (int)l);
@@ -175,10 +185,13 @@ int32_t plan_arena(vb_ctx* c) {
         Tensor& t = c->tensor(s.role, s.layer);
         t.m.data = c->arena + s.data;
         t.m.scales = wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols) ? c->arena + s.scales : nullptr;
-        if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; }
+        if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; t.m.v3 = c->arena + s.v3; }
     }
     for (uint32_t l = 0; l < c->d.n_layers; ++l)
-        if (swiglu_off[l] != ~0ULL) c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
+        if (swiglu_off[l] != ~0ULL) {
+            c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
+            c->tensor(VB_ROLE_WGATE, (int)l).m.v3_swiglu = c->arena + swiglu_v3_off[l];
+        }
     if (c->d.tied_lm_head) {
         Tensor& h = c->tensor(VB_ROLE_LM_HEAD, 0);
         h = c->tensor(VB_ROLE_EMBED, 0);
@@ -425,9 +438,13 @@ static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer) {
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
     VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), t->m.data, t->m.scales, t->m.rows, t->m.cols));
+    VB_CUDA(tile_q4_v3(lc, const_cast<void*>(t->m.v3), t->m.data, t->m.scales, t->m.rows, t->m.cols));
     if (role == VB_ROLE_WGATE || role == VB_ROLE_WUP) {
+        const int which = role == VB_ROLE_WUP ? 1 : 0;
         const void* il = c->tensor(VB_ROLE_WGATE, layer).m.tiled_swiglu;
-        if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), t->m.data, t->m.scales, t->m.rows, t->m.cols, role == VB_ROLE_WUP ? 1 : 0));
+        if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), t->m.data, t->m.scales, t->m.rows, t->m.cols, which));
+        const void* il3 = c->tensor(VB_ROLE_WGATE, layer).m.v3_swiglu;
+        if (il3) VB_CUDA(tile_q4_v3_swiglu(lc, const_cast<void*>(il3), t->m.data, t->m.scales, t->m.rows, t->m.cols, which));
     }
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;
@@ -766,6 +783,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "gemv_path")) { c->gemv_path = (int)value; return VB_OK; }
     if (!strcmp(name, "pdl")) { c->use_pdl = value != 0; return VB_OK; }
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
+    if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
     set_error("vb_set_option: unknown option '%s'", name);
     return VB_ERR_INVALID;

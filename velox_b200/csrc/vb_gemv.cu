@@ -123,6 +123,7 @@ cudaError_t gemv_init() {
 #define VB_OPT_IN(F) if ((e = cudaFuncSetAttribute(k_gemv_exact<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMV_EXACT_MAX_SMEM)) != cudaSuccess) return e
     VB_OPT_IN(VB_FMT_F32); VB_OPT_IN(VB_FMT_F16); VB_OPT_IN(VB_FMT_BF16); VB_OPT_IN(VB_FMT_Q4G32); VB_OPT_IN(VB_FMT_Q4G64REF); VB_OPT_IN(VB_FMT_I8PC);
 #undef VB_OPT_IN
+    if ((e = gemv_imma_init()) != cudaSuccess) return e;
     return gemv_fast_init();
 }
 
@@ -136,7 +137,9 @@ cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path) {
     if (a.batch == 0 || a.w.rows == 0) return cudaSuccess;
     if (path != 0) {
         bool handled = false;
-        cudaError_t e = gemv_fast(lc, a, &handled);
+        cudaError_t e = gemv_imma(lc, a, &handled);
+        if (handled || e != cudaSuccess) return e;
+        e = gemv_fast(lc, a, &handled);
         if (handled || e != cudaSuccess) return e;
     }
     switch (a.w.fmt) {

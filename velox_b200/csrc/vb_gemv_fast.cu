@@ -33,6 +33,7 @@
 // own dependents and only then wait for the producer kernel's x.
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
+#include "vb_tma.cuh"
 
 namespace vb {
 
@@ -360,37 +361,6 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_gemv_q4_mma(FastArgs a) {
 }
 
 // ---- batch-1 kernel: TMA ring + warp specialization ---------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok;
-}
-// Bounded wait (~1 s of SM clocks).  Returns false when it gave up; the caller records the failure and goes on.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > 2000000000LL) return false;
-    }
-}
-__device__ __forceinline__ void tma_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(FAST_THREADS) : "memory"); }
 
 constexpr uint32_t ERR_WAIT_FULL = 0x51u, ERR_WAIT_EMPTY = 0x52u;

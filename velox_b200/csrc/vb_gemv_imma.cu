@@ -1,0 +1,373 @@
+// Batch-1 matrix-vector kernel for symmetric int4 group-32 weights on the integer tensor-core path.
+//
+// Why integers.  At HBM speed a B200 SM receives ~45 int4 weights per clock.  Turning nibbles into fp16
+// costs one logic instruction per two weights on the half-rate integer/logic pipe, which measured as the
+// binding limit of the fp16-mma kernel (that pipe ~47 % busy at ~33 % of DRAM bandwidth).  Here a nibble
+// only has to become a byte: one AND per FOUR weights (`w & 0x0F0F0F0F`, and the same of `w >> 4`), and
+// mma.sync.m16n8k32.s8 multiplies the bytes 0..15 directly.
+//
+// Activations.  x is staged in shared memory as 15-bit fixed point per quantization group of 32:
+// X = rint(x * p_g), p_g the power of two that brings the group's largest magnitude into [8192, 16384),
+// split into two signed bytes X = 256*H + L (L in [-128,127]).  One m16n8k32 covers exactly one group of 32
+// along K for 16 rows, with H and L in two of the eight B columns; four consecutive groups use the four
+// column pairs of the same accumulator, so after the four mma of a 16x128 block lane (g,t) holds, for rows
+// g and g+8, the exact integers sum(q*H) and sum(q*L) of group t.  The zero point is removed with the
+// group's sum(X):  sum((q-8)*X) = 256*C_H + C_L - 8*SX, an exact int32 (< 2^24), converted once and scaled
+// by fp32(scale[row][group]) / p_g.  Nothing is rounded between x's 15-bit quantization and the final fp32
+// accumulation.
+//
+// Storage ("v3" tile-major blocks of 1152 bytes, block order [row tile][k tile]): lane L = 4g+t finds at
+// byte 16*L the four words (groups 0..3) of row g and at 512+16*L those of row g+8; in a word, byte b holds
+// element 4t+b of the group in its low nibble and element 16+4t+b in its high nibble -- the A fragment of
+// m16n8k32 after the two ANDs.  At byte 1024 + 4*L: half2(scale[row g][group t], scale[row g+8][group t]).
+//
+// Data movement and overlap are those of the pipelined fp16 kernel: persistent blocks, a producer warp
+// streaming row tiles through a shared-memory ring with cp.async.bulk + mbarriers (started before the
+// grid-dependency wait), eight consumer warps, bounded waits that report through a device error word.
+#include "vb_internal.cuh"
+#include "vb_kernels.cuh"
+#include "vb_tma.cuh"
+
+namespace vb {
+
+constexpr int IM_WARPS = 8;
+constexpr int IM_CONSUMERS = IM_WARPS * 32;
+constexpr int IM_THREADS = IM_CONSUMERS + 32;
+constexpr int IM_BLK_BYTES = 1152;
+constexpr int IM_SB = 8;  // blocks per stage
+constexpr int IM_STAGE_BYTES = IM_SB * IM_BLK_BYTES;
+constexpr int IM_MAX_STAGES = 8;
+constexpr int IM_MAX_SMEM = 112 * 1024;
+constexpr uint32_t IM_ERR_FULL = 0x61u, IM_ERR_EMPTY = 0x62u;
+
+struct ImmaArgs {
+    const unsigned char* w;  // v3 tile-major blocks
+    uint32_t rows, K;        // rows of the (possibly gate/up-interleaved) matrix
+    const float* x;
+    float* dst;
+    const void* norm_w; int norm_fmt; float eps;
+    const SeqState* state;
+    uint32_t dst_offset;
+    int epilogue;            // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU (interleaved 8+8 tiles)
+    uint32_t* err;
+    uint32_t n_stages;
+};
+
+__device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
+                                           const int c[4]) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+
+__device__ __forceinline__ void im_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(IM_CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ float im_norm_w(const void* w, int fmt, uint32_t i) {
+    return fmt == VB_FMT_F16 ? __half2float(((const __half*)w)[i])
+         : fmt == VB_FMT_BF16 ? __bfloat162float(((const __nv_bfloat16*)w)[i]) : ((const float*)w)[i];
+}
+
+// One chunk of 8 consecutive elements of x (already multiplied by the RMSNorm factors) -> the staged form.
+// The four lanes that share a group of 32 agree on its power-of-two scale through shuffles, so all 32
+// lanes of a warp must call this together (`valid` masks the stores).
+__device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, int* __restrict__ sx, float* __restrict__ invp,
+                                               const float v[8], uint32_t c, bool valid) {
+    float gmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, fabsf(v[i]));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
+    gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
+    float p = 1.0f;  // power of two with gmax * p in [8192, 16384); 1 for an all-zero or non-finite group
+    if (gmax > 0.0f && gmax < 3.0e38f) p = exp2f((float)(13 - ilogbf(gmax)));
+    int X[8], s = 0;
+    uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        X[i] = __float2int_rn(v[i] * p);
+        X[i] = max(-16383, min(16383, X[i]));
+        s += X[i];
+        const int H = (X[i] + 128) >> 8, L = X[i] - (H << 8);
+        hw[i >> 2] |= (uint32_t)(H & 0xFF) << (8 * (i & 3));
+        lw[i >> 2] |= (uint32_t)(L & 0xFF) << (8 * (i & 3));
+    }
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+    s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+    if (valid) {
+        // group layout: 32 H bytes then 32 L bytes
+        unsigned char* gb = xq + (size_t)(c >> 2) * 64 + (c & 3) * 8;
+        *reinterpret_cast<uint2*>(gb) = make_uint2(hw[0], hw[1]);
+        *reinterpret_cast<uint2*>(gb + 32) = make_uint2(lw[0], lw[1]);
+        if ((c & 3) == 0) { sx[c >> 2] = s; invp[c >> 2] = 1.0f / p; }
+    }
+}
+
+// grid: min(row tiles, 2 per SM) persistent blocks of 8 consumer warps + 1 producer warp
+__global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16, NS = a.n_stages;
+    const uint32_t n_chunks = (KT + IM_SB - 1) / IM_SB;
+    unsigned char* ring = smem_raw;                                              // [NS][IM_STAGE_BYTES]
+    unsigned char* xq = ring + (size_t)NS * IM_STAGE_BYTES;                      // [K/32][64]
+    int* sx = reinterpret_cast<int*>(xq + (size_t)K * 2);                        // [K/32]
+    float* invp = reinterpret_cast<float*>(sx + K / 32);                         // [K/32]
+    float* red = invp + K / 32;                                                  // [2][IM_WARPS][16]
+    __shared__ __align__(8) unsigned long long bar_full[IM_MAX_STAGES], bar_empty[IM_MAX_STAGES];
+    __shared__ float ssq[IM_WARPS];
+
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < NS; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), IM_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == IM_WARPS) {
+        // ---- producer: weights do not depend on the previous kernel, so no grid-dependency wait here ----------
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t it = 0;
+            for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                const unsigned char* wt = a.w + (size_t)tile * KT * IM_BLK_BYTES;
+                for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                    if (ok && !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u)) { ok = false; atomicExch(a.err, IM_ERR_EMPTY); }
+                    const uint32_t nblk = min((uint32_t)IM_SB, KT - c * IM_SB);
+                    const uint32_t bytes = nblk * IM_BLK_BYTES;
+                    mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
+                    tma_load_1d(smem_u32(ring + (size_t)s * IM_STAGE_BYTES), wt + (size_t)c * IM_SB * IM_BLK_BYTES, bytes,
+                                smem_u32(&bar_full[s]));
+                }
+            }
+        }
+        return;
+    }
+
+    // ---- consumers ----------------------------------------------------------------------------------------------
+    pdl_wait();
+    const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
+
+    // x -> shared memory.  Rows of up to 4096 elements make one trip through registers.
+    {
+        const float* x = a.x;
+        const bool in_regs = K <= 4096;
+        float xr[2][8];
+        float ss = 0.0f;
+        if (active && a.norm_w) {
+            if (in_regs) {
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    const uint32_t c = threadIdx.x + i * IM_CONSUMERS;
+                    if (c < K / 8) {
+                        const float4 v0 = *reinterpret_cast<const float4*>(x + c * 8), v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                        xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
+                        xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ss = fmaf(xr[i][e], xr[i][e], ss);
+                    }
+                }
+            } else {
+                for (uint32_t k = threadIdx.x * 4; k < K; k += IM_CONSUMERS * 4) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + k);
+                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) ssq[warp] = ss;
+        }
+        im_consumer_sync();
+        float inv = 1.0f;
+        if (a.norm_w && active) {
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < IM_WARPS; ++w) tot += ssq[w];
+            inv = 1.0f / sqrtf(tot / (float)K + a.eps);
+        }
+        for (uint32_t c0 = 0; c0 < K / 8; c0 += IM_CONSUMERS) {
+            const uint32_t c = c0 + threadIdx.x;
+            const bool valid = active && c < K / 8;  // groups of 4 lanes are valid together
+            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            if (valid) {
+                if (in_regs && a.norm_w) {
+                    const int i = (int)(c0 / IM_CONSUMERS);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = i == 0 ? xr[0][e] : xr[1][e];
+                } else {
+                    const float4 v0 = *reinterpret_cast<const float4*>(x + c * 8), v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
+                    v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
+                }
+                if (a.norm_w) {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
+                }
+            }
+            im_stage_chunk(xq, sx, invp, v, c, valid);
+        }
+        im_consumer_sync();
+    }
+
+    // residual rows fetched early so that the epilogue does not wait on them
+    bool ok = true;
+    uint32_t it = 0, parity = 0;
+    const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
+    const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 4 * t;
+    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, parity ^= 1) {
+        float resid = 0.0f;
+        if (a.epilogue == EPI_RESIDUAL && threadIdx.x < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + threadIdx.x];
+        float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
+        for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
+            const uint32_t s = it % NS, ph = (it / NS) & 1u;
+            if (ok && !mbar_wait(smem_u32(&bar_full[s]), ph)) { ok = false; atomicExch(a.err, IM_ERR_FULL); }
+            const uint32_t kk = c * IM_SB + warp;
+            if (kk < KT && active) {
+                const unsigned char* blk = ring + (size_t)s * IM_STAGE_BYTES + (size_t)warp * IM_BLK_BYTES;
+                const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
+                const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
+                const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
+                // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
+                const uint32_t bx0 = *reinterpret_cast<const uint32_t*>(xq_lane + (size_t)kk * 256);
+                const uint32_t bx1 = *reinterpret_cast<const uint32_t*>(xq_lane + (size_t)kk * 256 + 16);
+                const int sxt = sx[kk * 4 + t];
+                const float ip = invp[kk * 4 + t];
+                const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
+                const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
+                int d[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t m = 0x0F0F0F0Fu;
+                    const uint32_t b0 = (gj == (uint32_t)j) ? bx0 : 0u, b1 = (gj == (uint32_t)j) ? bx1 : 0u;
+                    imma_16832(d, war[j] & m, wbr[j] & m, (war[j] >> 4) & m, (wbr[j] >> 4) & m, b0, b1, d);
+                }
+                // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
+                const int r0 = d[0] * 256 + d[1] - 8 * sxt;
+                const int r1 = d[2] * 256 + d[3] - 8 * sxt;
+                const float2 s2 = __half22float2(sc);
+                acc0 = fmaf((float)r0 * ip, s2.x, acc0);
+                acc1 = fmaf((float)r1 * ip, s2.y, acc1);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+        }
+        // the four lanes of a row hold different groups: add them, then reduce the 8 warps through shared memory
+        acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
+        acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
+        float* rbuf = red + (size_t)parity * (IM_WARPS * 16);  // double-buffered by tile parity: one barrier per tile
+        if (t == 0) { rbuf[warp * 16 + g] = acc0; rbuf[warp * 16 + g + 8] = acc1; }
+        im_consumer_sync();
+        if (threadIdx.x < 16 && active) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < IM_WARPS; ++w) v += rbuf[w * 16 + threadIdx.x];
+            if (a.epilogue == EPI_SWIGLU) {
+                // tile = 8 gate rows (mma rows 0..7) over the same 8 up rows (mma rows 8..15)
+                const float up = __shfl_down_sync(0x0000FFFFu, v, 8);
+                if (threadIdx.x < 8) a.dst[a.dst_offset + tile * 8 + threadIdx.x] = (v / (1.0f + expf(-v))) * up;
+            } else if (a.epilogue == EPI_RESIDUAL) {
+                a.dst[a.dst_offset + tile * 16 + threadIdx.x] = resid + v;
+            } else {
+                a.dst[a.dst_offset + tile * 16 + threadIdx.x] = v;
+            }
+        }
+    }
+}
+
+// ---- canonical -> v3 repack (load time) ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t canon_nibble(const uint32_t* __restrict__ canon, uint64_t row, uint32_t K, uint32_t e) {
+    const uint32_t w = canon[row * (K / 8) + (e >> 3)], r = e & 7;
+    return (w >> (((r & 1) ? 16 : 0) + (r >> 1) * 4)) & 15u;
+}
+// one thread per output word; fills `half` (0: mma rows 0..7, 1: rows 8..15) of every block:
+// source row = rt * rows_per_tile + row_off + g
+__global__ void k_tile_q4_v3_words(uint32_t* __restrict__ out, const uint32_t* __restrict__ canon, uint32_t n_tiles, uint32_t K,
+                                   uint32_t rows_per_tile, uint32_t row_off, uint32_t half) {
+    const uint32_t KT = K / 128;
+    const uint64_t n = (uint64_t)n_tiles * KT * 128;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t j = i & 3, L = (i >> 2) & 31;
+        const uint64_t blk = i >> 7;
+        const uint32_t kt = blk % KT, rt = blk / KT, g = L >> 2, t = L & 3;
+        const uint64_t row = (uint64_t)rt * rows_per_tile + row_off + g;
+        const uint32_t e0 = kt * 128 + j * 32;
+        uint32_t w = 0;
+#pragma unroll
+        for (uint32_t b = 0; b < 4; ++b) {
+            w |= canon_nibble(canon, row, K, e0 + 4 * t + b) << (8 * b);
+            w |= canon_nibble(canon, row, K, e0 + 16 + 4 * t + b) << (8 * b + 4);
+        }
+        out[blk * (IM_BLK_BYTES / 4) + half * 128 + (i & 127)] = w;
+    }
+}
+__global__ void k_tile_q4_v3_scales(__half* __restrict__ out, const __half* __restrict__ canon, uint32_t n_tiles, uint32_t K,
+                                    uint32_t rows_per_tile, uint32_t row_off, uint32_t half) {
+    const uint32_t KT = K / 128;
+    const uint64_t n = (uint64_t)n_tiles * KT * 32;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t t = i & 3, g = (i >> 2) & 7;
+        const uint64_t blk = i >> 5;
+        const uint32_t kt = blk % KT, rt = blk / KT;
+        const uint64_t row = (uint64_t)rt * rows_per_tile + row_off + g;
+        out[blk * (IM_BLK_BYTES / 2) + 512 + (g * 4 + t) * 2 + half] = canon[row * (K / 32) + kt * 4 + t];
+    }
+}
+
+static cudaError_t tile_v3_half(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t n_tiles,
+                                uint32_t K, uint32_t rows_per_tile, uint32_t row_off, uint32_t half) {
+    const uint64_t nw = (uint64_t)n_tiles * (K / 128) * 128;
+    unsigned blocks = (unsigned)((nw + 255) / 256 > 148 * 32 ? 148 * 32 : (nw + 255) / 256);
+    cudaError_t e = launch(lc, k_tile_q4_v3_words, dim3(blocks), dim3(256), 0, (uint32_t*)tiled, (const uint32_t*)canon, n_tiles, K,
+                           rows_per_tile, row_off, half);
+    if (e != cudaSuccess) return e;
+    const uint64_t ns = (uint64_t)n_tiles * (K / 128) * 32;
+    blocks = (unsigned)((ns + 255) / 256 > 148 * 32 ? 148 * 32 : (ns + 255) / 256);
+    return launch(lc, k_tile_q4_v3_scales, dim3(blocks), dim3(256), 0, (__half*)tiled, (const __half*)canon_scales, n_tiles, K,
+                  rows_per_tile, row_off, half);
+}
+
+cudaError_t tile_q4_v3(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K) {
+    cudaError_t e = tile_v3_half(lc, tiled, canon, canon_scales, rows / 16, K, 16, 0, 0);
+    if (e != cudaSuccess) return e;
+    return tile_v3_half(lc, tiled, canon, canon_scales, rows / 16, K, 16, 8, 1);
+}
+// gate (which = 0) or up (which = 1) into the interleaved SwiGLU matrix: tile i = gate rows 8i..8i+7 | up rows 8i..8i+7
+cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K,
+                              int which) {
+    return tile_v3_half(lc, tiled, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
+}
+
+cudaError_t gemv_imma_init() {
+    return cudaFuncSetAttribute(k_gemv_q4_imma, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+}
+
+bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
+
+cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
+    *handled = false;
+    if (!imma_enabled || a.batch != 1 || a.w.fmt != VB_FMT_Q4G32) return cudaSuccess;
+    const bool swiglu = a.epilogue == EPI_SWIGLU;
+    const void* w = swiglu ? a.w.v3_swiglu : a.w.v3;
+    if (!w || a.w.cols % 128 != 0) return cudaSuccess;
+    if (swiglu && (a.w2.rows != a.w.rows || a.w2.cols != a.w.cols)) return cudaSuccess;
+    const uint32_t rows = swiglu ? 2 * a.w.rows : a.w.rows;
+    if (rows % 16 != 0) return cudaSuccess;
+    const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + 2 * (size_t)IM_WARPS * 16 * 4 + 256;
+    if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
+    size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
+    if (ns > IM_MAX_STAGES) ns = IM_MAX_STAGES;
+    ImmaArgs f;
+    f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
+    f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
+    f.dst_offset = a.dst_offset; f.epilogue = a.epilogue; f.n_stages = (uint32_t)ns;
+    cudaError_t e = fast_error_word(&f.err);
+    if (e != cudaSuccess) return e;
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    const uint32_t n_tiles = rows / 16;
+    *handled = true;
+    return launch(lc, k_gemv_q4_imma, dim3(n_tiles < 2u * n_sm ? n_tiles : 2u * n_sm), dim3(IM_THREADS), fixed + ns * IM_STAGE_BYTES, f);
+}
+
+}  // namespace vb

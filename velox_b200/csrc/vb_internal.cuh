@@ -46,6 +46,9 @@ struct WMat {
     const void* tiled_scales = nullptr;
     // gate matrices only: gate and up interleaved 8 rows by 8 rows in one tile-major matrix of 2*rows rows
     const void* tiled_swiglu = nullptr;
+    // the same two copies in the byte-per-nibble-pair block layout of the integer tensor-core kernel (vb_gemv_imma.cu)
+    const void* v3 = nullptr;
+    const void* v3_swiglu = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {

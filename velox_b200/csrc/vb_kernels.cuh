@@ -59,6 +59,14 @@ cudaError_t fast_error_word(uint32_t** out);
 cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const void* canon, const void* canon_scales,
                     uint32_t rows, uint32_t K);
 
+// vb_gemv_imma.cu
+cudaError_t gemv_imma_init();
+cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled);
+cudaError_t tile_q4_v3(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K);
+cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K,
+                              int which);
+extern bool imma_enabled;
+
 // vb_attn.cu
 struct AttnArgs {
     float* out = nullptr;          // [batch][Hq*D]
