@@ -147,6 +147,12 @@ int32_t vb_read_state(vb_ctx* ctx, int32_t slot, uint32_t* token, uint32_t* pos)
 int32_t vb_launch_count(vb_ctx* ctx, uint64_t* out);
 /* Algorithmic HBM bytes of one decode step at the slots' current positions (weights once + KV). */
 int32_t vb_step_bytes(vb_ctx* ctx, uint64_t* weight_bytes, uint64_t* kv_bytes);
+/* Device-timestamp trace of the last decode step (enable with vb_set_option(ctx, "trace", 1) before building
+ * the graph).  One record of three global-timer values in ns per traced kernel, in launch order: entry of its
+ * first block, that block past the grid-dependency wait, latest exit over all blocks.  The reference times
+ * with host timers and cudaEvent pairs around whole phases (velox_cuda_runner.cu:39-49, :494-563); this is
+ * the per-kernel view of the same thing.  Reading clears the records. */
+int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t* n_records);
 /* Tuning knobs (name/value), e.g. "gemv_path"; returns VB_ERR_INVALID for unknown names. */
 int32_t vb_set_option(vb_ctx* ctx, const char* name, int64_t value);
 

@@ -110,8 +110,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     __shared__ uint32_t is_last_s;
     extern __shared__ __align__(16) float part_acc[];  // [ATTN_WARPS][GM][D]
 
+    trace_mark(a.trace, 0);
     pdl_wait();
     pdl_launch_dependents();
+    trace_mark(a.trace, 1);
 
     const uint32_t b = blockIdx.z, split = blockIdx.y;
     const uint32_t kvh = blockIdx.x / ka.g_chunks, gc = blockIdx.x % ka.g_chunks;
@@ -281,7 +283,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         is_last_s = last;
     }
     __syncthreads();
-    if (!is_last_s) return;
+    if (!is_last_s) { trace_exit(a.trace); return; }
     __threadfence();
     // every split's (m, l) first, all loads in flight at once; then the weighted sum with the loads unrolled
     float* ml = part_acc;  // [GM][n_splits][2], reuses the merge buffer (n_splits <= 64)
@@ -309,6 +311,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         }
         a.out[(size_t)b * a.Hq * D + (size_t)h * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
     }
+    trace_exit(a.trace);
 }
 
 // scratch: partials [batch][Hq][n_splits][D+2] floats, then counters [batch][Hq] u32 (upper bound)

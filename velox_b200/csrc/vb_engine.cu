@@ -34,6 +34,8 @@ struct vb_ctx {
     int gemv_path = 1;
     bool use_pdl = true;
     bool fuse_append = true;
+    unsigned long long* trace = nullptr;  // [TRACE_MAX][4] device timestamps when the "trace" option is on
+    uint32_t trace_n = 0;
     float* rope_inv_freq = nullptr;  // [head_dim/2]
 
     // derived
@@ -242,6 +244,8 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     const vb_model_desc& d = c->d;
     const uint32_t B = d.max_batch;
     cudaError_t e;
+    uint32_t tn = 0;
+    auto next_trace = [&]() -> unsigned long long* { return (c->trace && tn < 1024) ? c->trace + 4 * (size_t)(tn++) : nullptr; };
 #define VB_TRY(x) do { e = (x); if (e != cudaSuccess) return e; } while (0)
     Tensor& emb = c->tensor(VB_ROLE_EMBED, 0);
     // the first kernel of a step must not overlap the previous step's tail: launched without PDL
@@ -254,6 +258,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         g.x = c->hidden; g.dst = c->qkv;
         g.norm_w = c->tensor(VB_ROLE_ATTN_NORM, L).m.data; g.norm_fmt = c->tensor(VB_ROLE_ATTN_NORM, L).m.fmt; g.eps = d.rms_eps;
         g.w = c->tensor(VB_ROLE_WQ, L).m; g.w.rows = c->qkv_rows;
+        g.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), g, c->gemv_path));
         // bias + RoPE + KV append
         __half* kv_layer = c->kv_pool + (size_t)l * c->kv_layer_elems;
@@ -273,22 +278,26 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
         a.state = state; a.Hq = d.n_q_heads; a.Hkv = d.n_kv_heads; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
+        a.trace = next_trace();
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
         o.state = state; o.batch = B; o.x = c->attn_out; o.dst = c->hidden; o.epilogue = EPI_RESIDUAL;
         o.w = c->tensor(VB_ROLE_WO, L).m;
+        o.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
         // RMSNorm + gate/up + SiLU*up
         GemvArgs gu;
         gu.state = state; gu.batch = B; gu.x = c->hidden; gu.dst = c->act; gu.epilogue = EPI_SWIGLU;
         gu.norm_w = c->tensor(VB_ROLE_MLP_NORM, L).m.data; gu.norm_fmt = c->tensor(VB_ROLE_MLP_NORM, L).m.fmt; gu.eps = d.rms_eps;
         gu.w = c->tensor(VB_ROLE_WGATE, L).m; gu.w2 = c->tensor(VB_ROLE_WUP, L).m;
+        gu.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
         // down projection + residual
         GemvArgs dn;
         dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = c->hidden; dn.epilogue = EPI_RESIDUAL;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
+        dn.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
     }
     if (with_head) {
@@ -296,10 +305,12 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         h.state = state; h.batch = B; h.x = c->hidden; h.dst = c->logits;
         h.norm_w = c->tensor(VB_ROLE_FINAL_NORM, 0).m.data; h.norm_fmt = c->tensor(VB_ROLE_FINAL_NORM, 0).m.fmt; h.eps = d.rms_eps;
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
+        h.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
         VB_TRY(argmax(lcfg(c, true), nullptr, c->logits, d.vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
     }
 #undef VB_TRY
+    c->trace_n = tn;
     return cudaSuccess;
 }
 
@@ -407,7 +418,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
     if (c->graph) cudaGraphDestroy(c->graph);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
-                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq};
+                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -783,10 +794,34 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "gemv_path")) { c->gemv_path = (int)value; return VB_OK; }
     if (!strcmp(name, "pdl")) { c->use_pdl = value != 0; return VB_OK; }
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
+    if (!strcmp(name, "trace")) {
+        if (value && !c->trace) {
+            VB_CUDA(cudaMalloc((void**)&c->trace, 1024 * 4 * sizeof(unsigned long long)));
+            VB_CUDA(cudaMemset(c->trace, 0, 1024 * 4 * sizeof(unsigned long long)));
+        } else if (!value && c->trace) {
+            cudaFree(c->trace);
+            c->trace = nullptr;
+        }
+        return VB_OK;
+    }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
     set_error("vb_set_option: unknown option '%s'", name);
     return VB_ERR_INVALID;
+}
+
+int32_t vb_trace_read(vb_ctx* c, uint64_t* out, uint32_t max_records, uint32_t* n_records) {
+    VB_REQUIRE(c && out && n_records, "vb_trace_read: null argument");
+    if (!c->trace) { set_error("vb_trace_read: enable the \"trace\" option first"); return VB_ERR_STATE; }
+    VB_CUDA(cudaSetDevice(c->device));
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    const uint32_t n = c->trace_n < max_records ? c->trace_n : max_records;
+    std::vector<unsigned long long> buf((size_t)n * 4);
+    VB_CUDA(cudaMemcpy(buf.data(), c->trace, buf.size() * 8, cudaMemcpyDeviceToHost));
+    for (uint32_t i = 0; i < n; ++i) { out[3 * i] = buf[4 * i]; out[3 * i + 1] = buf[4 * i + 1]; out[3 * i + 2] = buf[4 * i + 2]; }
+    VB_CUDA(cudaMemset(c->trace, 0, 1024 * 4 * sizeof(unsigned long long)));  // exit stamps are running maxima
+    *n_records = n;
+    return VB_OK;
 }
 
 int32_t vb_tp_unique_id(void* id128) {

@@ -51,6 +51,7 @@ struct ImmaArgs {
     int epilogue;            // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU (interleaved 8+8 tiles)
     uint32_t* err;
     uint32_t n_stages;
+    unsigned long long* trace;  // optional timestamp record
 };
 
 __device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
@@ -60,7 +61,7 @@ __device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, u
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
 }
 
-__device__ __forceinline__ void im_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(IM_CONSUMERS) : "memory"); }
+__device__ __forceinline__ void im_consumer_sync() { __syncthreads(); }
 
 __device__ __forceinline__ float im_norm_w(const void* w, int fmt, uint32_t i) {
     return fmt == VB_FMT_F16 ? __half2float(((const __half*)w)[i])
@@ -101,50 +102,65 @@ __device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, i
     }
 }
 
-// grid: min(row tiles, 2 per SM) persistent blocks of 8 consumer warps + 1 producer warp
-__global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// The sequence of 16x128 blocks one warp works through: block `kk` (kk = warp, warp+8, ...) of row tile `tile`
+// (tile = blockIdx.x, += gridDim.x).
+struct BlockCursor {
+    uint32_t tile, kk;
+    __device__ __forceinline__ bool valid(uint32_t n_tiles) const { return tile < n_tiles; }
+    __device__ __forceinline__ void advance(uint32_t KT, uint32_t warp) {
+        kk += IM_WARPS;
+        if (kk >= KT) { kk = warp; tile += gridDim.x; }
+    }
+};
+
+// One warp requests one block (1152 bytes) into its private ring slot: 72 asynchronous 16-byte copies.
+__device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w, uint32_t KT, const BlockCursor& cur, uint32_t slot_smem,
+                                            uint32_t lane) {
+    const unsigned char* src = w + ((size_t)cur.tile * KT + cur.kk) * IM_BLK_BYTES;
+    cp_async16(slot_smem + lane * 16, src + lane * 16);
+    cp_async16(slot_smem + 512 + lane * 16, src + 512 + lane * 16);
+    if (lane < 8) cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
+}
+
+// grid: min(row tiles, 2 per SM) persistent blocks of 8 warps.  Each warp streams its own blocks through a
+// private ring of NS slots with cp.async (16-byte asynchronous copies, L1 bypassed): no block-wide
+// synchronisation on the data path, ~130 KB per SM in flight, started before the grid-dependency wait.
+template <int NS>
+__global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16, NS = a.n_stages;
-    const uint32_t n_chunks = (KT + IM_SB - 1) / IM_SB;
-    unsigned char* ring = smem_raw;                                              // [NS][IM_STAGE_BYTES]
-    unsigned char* xq = ring + (size_t)NS * IM_STAGE_BYTES;                      // [K/32][64]
+    const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
+    unsigned char* ring = smem_raw;                                              // [IM_WARPS][NS][IM_BLK_BYTES]
+    unsigned char* xq = ring + (size_t)IM_WARPS * NS * IM_BLK_BYTES;             // [K/32][64]
     int* sx = reinterpret_cast<int*>(xq + (size_t)K * 2);                        // [K/32]
     float* invp = reinterpret_cast<float*>(sx + K / 32);                         // [K/32]
     float* red = invp + K / 32;                                                  // [2][IM_WARPS][16]
-    __shared__ __align__(8) unsigned long long bar_full[IM_MAX_STAGES], bar_empty[IM_MAX_STAGES];
     __shared__ float ssq[IM_WARPS];
 
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < NS; ++s) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), IM_WARPS); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
+    trace_mark(a.trace, 0);
     pdl_launch_dependents();
 
-    if (warp == IM_WARPS) {
-        // ---- producer: weights do not depend on the previous kernel, so no grid-dependency wait here ----------
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t it = 0;
-            for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                const unsigned char* wt = a.w + (size_t)tile * KT * IM_BLK_BYTES;
-                for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
-                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                    if (ok && !mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u)) { ok = false; atomicExch(a.err, IM_ERR_EMPTY); }
-                    const uint32_t nblk = min((uint32_t)IM_SB, KT - c * IM_SB);
-                    const uint32_t bytes = nblk * IM_BLK_BYTES;
-                    mbar_expect_tx(smem_u32(&bar_full[s]), bytes);
-                    tma_load_1d(smem_u32(ring + (size_t)s * IM_STAGE_BYTES), wt + (size_t)c * IM_SB * IM_BLK_BYTES, bytes,
-                                smem_u32(&bar_full[s]));
-                }
-            }
-        }
-        return;
+    // ---- prologue: weights do not depend on the previous kernel; fill the ring before waiting for x ----------
+    const uint32_t my_ring = smem_u32(ring + (size_t)warp * NS * IM_BLK_BYTES);
+    BlockCursor icur{blockIdx.x, warp};  // next block to request
+    uint32_t issued = 0;
+    if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
+#pragma unroll
+    for (int i = 0; i < NS - 1; ++i) {
+        if (icur.valid(n_tiles)) { issue_block(a.w, KT, icur, my_ring + (issued % NS) * IM_BLK_BYTES, lane); icur.advance(KT, warp); ++issued; }
+        cp_async_commit();
     }
 
-    // ---- consumers ----------------------------------------------------------------------------------------------
+    // ---- x: only now wait for the producer kernel ----------------------------------------------------------------
     pdl_wait();
+    trace_mark(a.trace, 1);
     const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
 
     // x -> shared memory.  Rows of up to 4096 elements make one trip through registers.
@@ -206,21 +222,23 @@ __global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
         im_consumer_sync();
     }
 
-    // residual rows fetched early so that the epilogue does not wait on them
-    bool ok = true;
-    uint32_t it = 0, parity = 0;
+    // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
+    uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 4 * t;
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, parity ^= 1) {
+        // residual rows fetched early so that the epilogue does not wait on them
         float resid = 0.0f;
         if (a.epilogue == EPI_RESIDUAL && threadIdx.x < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + threadIdx.x];
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
-        for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
-            const uint32_t s = it % NS, ph = (it / NS) & 1u;
-            if (ok && !mbar_wait(smem_u32(&bar_full[s]), ph)) { ok = false; atomicExch(a.err, IM_ERR_FULL); }
-            const uint32_t kk = c * IM_SB + warp;
-            if (kk < KT && active) {
-                const unsigned char* blk = ring + (size_t)s * IM_STAGE_BYTES + (size_t)warp * IM_BLK_BYTES;
+        for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
+            // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
+            if (icur.valid(n_tiles)) { issue_block(a.w, KT, icur, my_ring + (issued % NS) * IM_BLK_BYTES, lane); icur.advance(KT, warp); ++issued; }
+            cp_async_commit();
+            cp_async_wait<NS - 1>();
+            __syncwarp();
+            if (active) {
+                const unsigned char* blk = ring + ((size_t)warp * NS + consumed % NS) * IM_BLK_BYTES;
                 const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
                 const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
                 const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
@@ -234,9 +252,9 @@ __global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
                 int d[4] = {0, 0, 0, 0};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const uint32_t m = 0x0F0F0F0Fu;
+                    const uint32_t msk = 0x0F0F0F0Fu;
                     const uint32_t b0 = (gj == (uint32_t)j) ? bx0 : 0u, b1 = (gj == (uint32_t)j) ? bx1 : 0u;
-                    imma_16832(d, war[j] & m, wbr[j] & m, (war[j] >> 4) & m, (wbr[j] >> 4) & m, b0, b1, d);
+                    imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, b0, b1, d);
                 }
                 // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
                 const int r0 = d[0] * 256 + d[1] - 8 * sxt;
@@ -245,8 +263,7 @@ __global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
                 acc0 = fmaf((float)r0 * ip, s2.x, acc0);
                 acc1 = fmaf((float)r1 * ip, s2.y, acc1);
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+            __syncwarp();  // every lane is done with the slot before the next iteration overwrites its predecessor
         }
         // the four lanes of a row hold different groups: add them, then reduce the 8 warps through shared memory
         acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
@@ -269,6 +286,7 @@ __global__ void __launch_bounds__(IM_THREADS, 2) k_gemv_q4_imma(ImmaArgs a) {
             }
         }
     }
+    trace_exit(a.trace);
 }
 
 // ---- canonical -> v3 repack (load time) ---------------------------------------------------------------------
@@ -335,7 +353,10 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
 }
 
 cudaError_t gemv_imma_init() {
-    return cudaFuncSetAttribute(k_gemv_q4_imma, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+    cudaError_t e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_gemv_q4_imma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
 }
 
 bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
@@ -352,11 +373,12 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + 2 * (size_t)IM_WARPS * 16 * 4 + 256;
     if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
     size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
-    if (ns > IM_MAX_STAGES) ns = IM_MAX_STAGES;
+    ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : 2);  // ring depth per warp (template parameter)
     ImmaArgs f;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
     f.dst_offset = a.dst_offset; f.epilogue = a.epilogue; f.n_stages = (uint32_t)ns;
+    f.trace = a.trace;
     cudaError_t e = fast_error_word(&f.err);
     if (e != cudaSuccess) return e;
     static int n_sm = 0;
@@ -367,7 +389,11 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     }
     const uint32_t n_tiles = rows / 16;
     *handled = true;
-    return launch(lc, k_gemv_q4_imma, dim3(n_tiles < 2u * n_sm ? n_tiles : 2u * n_sm), dim3(IM_THREADS), fixed + ns * IM_STAGE_BYTES, f);
+    const dim3 grid(n_tiles < 2u * n_sm ? n_tiles : 2u * n_sm);
+    const size_t smem = fixed + ns * IM_STAGE_BYTES;
+    if (ns == 8) return launch(lc, k_gemv_q4_imma<8>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 4) return launch(lc, k_gemv_q4_imma<4>, grid, dim3(IM_CONSUMERS), smem, f);
+    return launch(lc, k_gemv_q4_imma<2>, grid, dim3(IM_CONSUMERS), smem, f);
 }
 
 }  // namespace vb

@@ -147,6 +147,20 @@ __device__ __forceinline__ void unpack8_f32(uint32_t p, float q[8]) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 
+// Device-timestamp trace (profiling aid): record[0] = entry of block 0, record[1] = block 0 past the
+// grid-dependency wait, record[2] = latest exit over all blocks (nanoseconds of the global timer).
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void trace_mark(unsigned long long* rec, int slot) {
+    if (rec && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) rec[slot] = global_ns();
+}
+__device__ __forceinline__ void trace_exit(unsigned long long* rec) {
+    if (rec && threadIdx.x == 0) atomicMax(rec + 2, global_ns());
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);

@@ -47,6 +47,7 @@ struct GemvArgs {
     uint32_t dst_stride = 0;         // elements between batch rows of dst (0 = out_dim)
     uint32_t dst_offset = 0;         // column offset inside dst
     int epilogue = EPI_STORE;
+    unsigned long long* trace = nullptr;  // 3-slot timestamp record of this launch (tuned kernels only)
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
 
@@ -87,6 +88,7 @@ struct AttnArgs {
     uint32_t Hq = 0, Hkv = 0, D = 0, batch = 1;
     uint32_t max_splits = 1;       // grid size along the context (fixed per context so that graphs replay)
     uint32_t tokens_per_split = 32; // multiple of block_tokens
+    unsigned long long* trace = nullptr;
     float* scratch = nullptr;      // attn_scratch_floats(): partials, then the split counters (zero before the first launch)
 };
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits);

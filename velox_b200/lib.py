@@ -67,6 +67,7 @@ SIGNATURES = {
     "vb_launch_count": (_i32, [_vp, C.POINTER(_u64)]),
     "vb_step_bytes": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "vb_set_option": (_i32, [_vp, C.c_char_p, C.c_int64]),
+    "vb_trace_read": (_i32, [_vp, _vp, _u32, C.POINTER(_u32)]),
     "vb_tp_unique_id": (_i32, [_vp]),
     "vb_tp_init": (_i32, [_vp, _vp]),
     "vb_op_embed": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp]),
