@@ -16,13 +16,19 @@
 //
 // The cache is either the reference's contiguous fp32 layout [t][Hkv*D] or this library's paged fp16 pool,
 // per layer [block][K|V][kv_head][block_tokens][D].
+#include <cooperative_groups.h>
+#include <stdlib.h>
+
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace vb {
 
 constexpr int ATTN_WARPS = 4;
-constexpr int ATTN_MAX_SPLITS = 64;
+constexpr int ATTN_MAX_SPLITS = 8;  // portable thread-block cluster size
+constexpr int ATTN_MAX_BLOCKS = 1024;  // KV blocks one block's slice may span (16384 tokens)
 
 struct AttnKArgs {
     AttnArgs a;
@@ -97,18 +103,39 @@ __device__ __forceinline__ void warp_transpose_reduce(float v[NV], uint32_t lane
     }
 }
 
+__device__ __forceinline__ void attn_cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+
+// Shared-memory plan of one block (dynamic): K/V staging for two chunks of CH tokens, the warp-merge buffer.
+template <typename KVT, int EPL, int GM>
+struct AttnSmem {
+    static constexpr int D = EPL * 32;
+    // tokens per staged chunk: K+V of a chunk take at most 32 KB, at most 64 tokens
+    static constexpr int CH = (16384 / (D * (int)sizeof(KVT))) > 64 ? 64 : (16384 / (D * (int)sizeof(KVT)));
+    static constexpr size_t kv_bytes = (size_t)2 * 2 * CH * D * sizeof(KVT);  // [buffer][K|V][CH][D]
+    static constexpr size_t acc_bytes = (size_t)ATTN_WARPS * GM * D * sizeof(float);
+    static constexpr size_t total = kv_bytes + acc_bytes;
+};
+
 template <typename KVT, int EPL, int GM>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     const AttnArgs& a = ka.a;
-    constexpr int D = EPL * 32;
+    using SM = AttnSmem<KVT, EPL, GM>;
+    constexpr int D = EPL * 32, CH = SM::CH;
     constexpr int TCH = (EPL >= 8) ? 2 : ((GM >= 8) ? 4 : 8);  // tokens a warp handles at once
     constexpr int NV = TCH * GM;                              // partial dot products per lane (<= 32)
+    constexpr int ROW16 = D * sizeof(KVT) / 16;               // 16-byte pieces per K or V row
     static_assert(NV <= 32 && (NV & (NV - 1)) == 0, "values per lane must be a power of two <= 32");
     __shared__ float q_s[GM][D];
     __shared__ float sc_s[ATTN_WARPS][32];
     __shared__ float part_ml[ATTN_WARPS][GM][2];
-    __shared__ uint32_t is_last_s;
-    extern __shared__ __align__(16) float part_acc[];  // [ATTN_WARPS][GM][D]
+    __shared__ float comb[GM][D + 2];       // this block's partial, read by the whole cluster
+    __shared__ int32_t blk_s[ATTN_MAX_BLOCKS];  // block-table entries of this block's slice
+    __shared__ __align__(16) KVT new_kv[2][D];  // the appended token's K and V (fused mode)
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
+    KVT* kv_s = reinterpret_cast<KVT*>(dyn_smem);
+    float* part_acc = reinterpret_cast<float*>(dyn_smem + SM::kv_bytes);  // [ATTN_WARPS][GM][D]
 
     trace_mark(a.trace, 0);
     pdl_wait();
@@ -122,7 +149,12 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     if (a.state && !a.state[b].active) return;
     const uint32_t seq_len = (a.state ? a.state[b].pos : a.pos) + 1;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const uint32_t t_lo = min(seq_len, split * ka.tokens_per_split), t_hi = min(seq_len, t_lo + ka.tokens_per_split);
+    // the context is cut into n_splits equal slices of whole KV blocks, whatever its current length
+    uint32_t per = (seq_len + ka.n_splits - 1) / ka.n_splits;
+    per = ((per + a.block_tokens - 1) / a.block_tokens) * a.block_tokens;
+    const uint32_t t_lo = min(seq_len, split * per), t_hi = min(seq_len, t_lo + per);
+    const uint32_t pos = seq_len - 1;
+    const bool appender = a.qkv_raw && t_lo <= pos && pos < t_hi;
 
     float m[GM], l[GM], acc[GM][EPL];
 #pragma unroll
@@ -132,10 +164,38 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
     }
 
+    // One chunk = tokens [c0, c0+CH) of the slice: every 16-byte piece of its K and V rows is requested at once.
+    auto stage_chunk = [&](uint32_t c0, uint32_t buf) {
+        const uint32_t n_tok = min((uint32_t)CH, t_hi - c0);
+        KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
+        for (uint32_t i = threadIdx.x; i < n_tok * 2 * ROW16; i += blockDim.x) {
+            const uint32_t piece = i % ROW16, kv = (i / ROW16) & 1, tok = i / (2 * ROW16);
+            const uint32_t tt = c0 + tok;
+            const KVT* src;
+            if (a.block_table) {
+                const int32_t blk = blk_s[(tt - t_lo) / a.block_tokens];
+                src = reinterpret_cast<const KVT*>(a.k) + (((size_t)blk * 2 + kv) * a.Hkv + kvh) * a.block_tokens * D +
+                      (size_t)(tt % a.block_tokens) * D;
+            } else {
+                const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
+                src = reinterpret_cast<const KVT*>(kv ? a.v : a.k) + off;
+            }
+            attn_cp_async16((uint32_t)__cvta_generic_to_shared(kb + ((size_t)kv * CH + tok) * D) + piece * 16,
+                            reinterpret_cast<const unsigned char*>(src) + piece * 16);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
     if (t_lo < t_hi) {
+        // ---- one trip: block-table entries of the slice, the query heads (and, fused, the new token's K/V) ----
+        if (a.block_table) {
+            const uint32_t nblk = (t_hi - t_lo + a.block_tokens - 1) / a.block_tokens;
+            for (uint32_t i = threadIdx.x; i < nblk && i < (uint32_t)ATTN_MAX_BLOCKS; i += blockDim.x)
+                blk_s[i] = a.block_table[(size_t)b * a.max_blocks + t_lo / a.block_tokens + i];
+        }
         if (a.qkv_raw) {
-            // fused bias + RoPE on the raw projections; the block whose slice holds `pos` appends K and V
-            const uint32_t pos = seq_len - 1, half = D / 2;
+            // fused bias + RoPE on the raw projections
+            const uint32_t half = D / 2;
             const float* raw = a.qkv_raw + (size_t)b * (a.Hq + 2 * a.Hkv) * D;
             for (uint32_t i = threadIdx.x; i < GM * half; i += blockDim.x) {
                 const uint32_t g = i / half, j = i % half;
@@ -152,11 +212,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                 q_s[g][j] = r1;
                 q_s[g][j + half] = r2;
             }
-            if (t_lo <= pos && pos < t_hi && gc == 0) {
-                const int32_t blk = a.block_table[(size_t)b * a.max_blocks + pos / a.block_tokens];
-                __half* kd = reinterpret_cast<__half*>(const_cast<void*>(a.k)) +
-                             (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D + (size_t)(pos % a.block_tokens) * D;
-                __half* vd = kd + (size_t)a.Hkv * a.block_tokens * D;
+            if (appender) {
                 const float* kr_raw = raw + (size_t)a.Hq * D + (size_t)kvh * D;
                 const float* vr_raw = raw + (size_t)(a.Hq + a.Hkv) * D + (size_t)kvh * D;
                 for (uint32_t j = threadIdx.x; j < half; j += blockDim.x) {
@@ -165,87 +221,112 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     if (a.bv) { v1 += bias_at(a.bv, a.bias_fmt, kvh * D + j); v2 += bias_at(a.bv, a.bias_fmt, kvh * D + j + half); }
                     float sn, cs;
                     sincosf((float)pos * a.rope_inv_freq[j], &sn, &cs);
-                    kd[j] = __float2half_rn(x1 * cs - x2 * sn);
-                    kd[j + half] = __float2half_rn(x2 * cs + x1 * sn);
-                    vd[j] = __float2half_rn(v1);
-                    vd[j + half] = __float2half_rn(v2);
+                    new_kv[0][j] = (KVT)__float2half_rn(x1 * cs - x2 * sn);
+                    new_kv[0][j + half] = (KVT)__float2half_rn(x2 * cs + x1 * sn);
+                    new_kv[1][j] = (KVT)__float2half_rn(v1);
+                    new_kv[1][j + half] = (KVT)__float2half_rn(v2);
                 }
             }
         } else {
             const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
             for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) q_s[i / D][i % D] = (i < ng * D) ? qb[i] : 0.0f;
         }
-        __syncthreads();  // q_s complete; the appended K/V row (written by this block) is visible to it
+        __syncthreads();
+        if (appender && gc == 0) {
+            // the new token's row goes to the cache (16-byte stores); this block reads it from new_kv below
+            const int32_t blk = blk_s[(pos - t_lo) / a.block_tokens];
+            KVT* kd = reinterpret_cast<KVT*>(const_cast<void*>(a.k)) + (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D +
+                      (size_t)(pos % a.block_tokens) * D;
+            KVT* vd = kd + (size_t)a.Hkv * a.block_tokens * D;
+            for (uint32_t i = threadIdx.x; i < 2 * ROW16; i += blockDim.x) {
+                const uint32_t kv = i / ROW16, piece = i % ROW16;
+                reinterpret_cast<uint4*>(kv ? vd : kd)[piece] = reinterpret_cast<const uint4*>(new_kv[kv])[piece];
+            }
+        }
+
         float qr[GM][EPL];
 #pragma unroll
         for (int g = 0; g < GM; ++g)
 #pragma unroll
             for (int e = 0; e < EPL; ++e) qr[g][e] = q_s[g][lane * EPL + e];
 
-        for (uint32_t t0 = t_lo + warp * TCH; t0 < t_hi; t0 += ATTN_WARPS * TCH) {
-            float kr[TCH][EPL], vr[TCH][EPL];
-#pragma unroll
-            for (int i = 0; i < TCH; ++i) {
-                const uint32_t tt = min(t0 + i, t_hi - 1);  // out-of-range tokens re-read the last row, masked below
-                const KVT *kp, *vp;
-                if (a.block_table) {
-                    const int32_t blk = a.block_table[(size_t)b * a.max_blocks + tt / a.block_tokens];
-                    const size_t base = (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D + (size_t)(tt % a.block_tokens) * D;
-                    kp = reinterpret_cast<const KVT*>(a.k) + base;
-                    vp = kp + (size_t)a.Hkv * a.block_tokens * D;
-                } else {
-                    const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
-                    kp = reinterpret_cast<const KVT*>(a.k) + off;
-                    vp = reinterpret_cast<const KVT*>(a.v) + off;
-                }
-                load_row<KVT, EPL>(kp, lane, kr[i]);
-                load_row<KVT, EPL>(vp, lane, vr[i]);
+        // ---- the slice, CH tokens at a time, double buffered: one memory trip per chunk ----------------------
+        const uint32_t n_ch = (t_hi - t_lo + CH - 1) / CH;
+        stage_chunk(t_lo, 0);
+        for (uint32_t c = 0; c < n_ch; ++c) {
+            const uint32_t c0 = t_lo + c * CH, buf = c & 1;
+            if (c + 1 < n_ch) {
+                stage_chunk(c0 + CH, buf ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
             }
-            // partial dot products, value index = g * TCH + i
-            float pv[NV];
-#pragma unroll
-            for (int g = 0; g < GM; ++g)
+            __syncthreads();
+            KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
+            if (appender && c0 <= pos && pos < c0 + CH) {
+                // overwrite the staged copy of the new token's row with the values just computed
+                for (uint32_t i = threadIdx.x; i < 2 * ROW16; i += blockDim.x) {
+                    const uint32_t kv = i / ROW16, piece = i % ROW16;
+                    reinterpret_cast<uint4*>(kb + ((size_t)kv * CH + (pos - c0)) * D)[piece] = reinterpret_cast<const uint4*>(new_kv[kv])[piece];
+                }
+                __syncthreads();
+            }
+            const uint32_t c_hi = min(t_hi, c0 + CH);
+            for (uint32_t t0 = c0 + warp * TCH; t0 < c_hi; t0 += ATTN_WARPS * TCH) {
+                float kr[TCH][EPL], vr[TCH][EPL];
 #pragma unroll
                 for (int i = 0; i < TCH; ++i) {
-                    float d = 0.0f;
-#pragma unroll
-                    for (int e = 0; e < EPL; ++e) d = fmaf(qr[g][e], kr[i][e], d);
-                    pv[g * TCH + i] = d;
+                    const uint32_t tok = min(t0 + i, c_hi - 1) - c0;  // out-of-range tokens re-read the last row, masked below
+                    load_row<KVT, EPL>(kb + (size_t)tok * D, lane, kr[i]);
+                    load_row<KVT, EPL>(kb + ((size_t)CH + tok) * D, lane, vr[i]);
                 }
-            warp_transpose_reduce<NV>(pv, lane);
-            __syncwarp();
-            if (lane < NV) {
-                const uint32_t i = lane % TCH;
-                sc_s[warp][lane] = (t0 + i < t_hi) ? pv[0] * ka.scale : -INFINITY;
-            }
-            __syncwarp();
+                // partial dot products, value index = g * TCH + i
+                float pv[NV];
 #pragma unroll
-            for (int g = 0; g < GM; ++g) {
-                float s[TCH];
-                float cmax = -INFINITY;
+                for (int g = 0; g < GM; ++g)
 #pragma unroll
-                for (int i = 0; i < TCH; ++i) { s[i] = sc_s[warp][g * TCH + i]; cmax = fmaxf(cmax, s[i]); }
-                const float new_m = fmaxf(m[g], cmax);
-                if (new_m != -INFINITY) {
-                    const float alpha = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - new_m);
-                    float p[TCH], psum = 0.0f;
+                    for (int i = 0; i < TCH; ++i) {
+                        float d = 0.0f;
 #pragma unroll
-                    for (int i = 0; i < TCH; ++i) { p[i] = __expf(s[i] - new_m); psum += p[i]; }
-                    l[g] = fmaf(l[g], alpha, psum);
-                    m[g] = new_m;
+                        for (int e = 0; e < EPL; ++e) d = fmaf(qr[g][e], kr[i][e], d);
+                        pv[g * TCH + i] = d;
+                    }
+                warp_transpose_reduce<NV>(pv, lane);
+                __syncwarp();
+                if (lane < NV) {
+                    const uint32_t i = lane % TCH;
+                    sc_s[warp][lane] = (t0 + i < c_hi) ? pv[0] * ka.scale : -INFINITY;
+                }
+                __syncwarp();
 #pragma unroll
-                    for (int e = 0; e < EPL; ++e) {
-                        float v = acc[g][e] * alpha;
+                for (int g = 0; g < GM; ++g) {
+                    float sv[TCH];
+                    float cmax = -INFINITY;
 #pragma unroll
-                        for (int i = 0; i < TCH; ++i) v = fmaf(p[i], vr[i][e], v);
-                        acc[g][e] = v;
+                    for (int i = 0; i < TCH; ++i) { sv[i] = sc_s[warp][g * TCH + i]; cmax = fmaxf(cmax, sv[i]); }
+                    const float new_m = fmaxf(m[g], cmax);
+                    if (new_m != -INFINITY) {
+                        const float alpha = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - new_m);
+                        float p[TCH], psum = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < TCH; ++i) { p[i] = __expf(sv[i] - new_m); psum += p[i]; }
+                        l[g] = fmaf(l[g], alpha, psum);
+                        m[g] = new_m;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) {
+                            float v = acc[g][e] * alpha;
+#pragma unroll
+                            for (int i = 0; i < TCH; ++i) v = fmaf(p[i], vr[i][e], v);
+                            acc[g][e] = v;
+                        }
                     }
                 }
             }
+            __syncthreads();  // the buffer is free for the chunk after next
         }
     }
 
-    // ---- merge the 4 warps, write this split's partial -----------------------------------------------------
+    // ---- merge the 4 warps into this block's partial (m, l, unnormalised acc), kept in shared memory --------
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
         if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
@@ -253,7 +334,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
     }
     __syncthreads();
-    for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) {
+    for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) {
         const uint32_t g = i / D, d = i % D;
         float M = -INFINITY;
 #pragma unroll
@@ -266,76 +347,87 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
             L = fmaf(part_ml[w][g][1], f, L);
             A = fmaf(part_acc[((size_t)w * GM + g) * D + d], f, A);
         }
-        const uint32_t h = kvh * ka.G + g0 + g;
-        float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits + split) * (D + 2);
-        ps[2 + d] = A;
-        if (d == 0) { ps[0] = M; ps[1] = L; }
+        comb[g][2 + d] = A;
+        if (d == 0) { comb[g][0] = M; comb[g][1] = L; }
     }
 
-    // ---- the last block of this (sequence, head group) merges all splits --------------------------------------
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t* ctr = ka.counters + (size_t)b * gridDim.x + blockIdx.x;
-        const uint32_t prev = atomicAdd(ctr, 1u);
-        const uint32_t last = (prev == ka.n_splits - 1) ? 1u : 0u;
-        if (last) *ctr = 0u;  // ready for the next launch / graph replay
-        is_last_s = last;
-    }
-    __syncthreads();
-    if (!is_last_s) { trace_exit(a.trace); return; }
-    __threadfence();
-    // every split's (m, l) first, all loads in flight at once; then the weighted sum with the loads unrolled
-    float* ml = part_acc;  // [GM][n_splits][2], reuses the merge buffer (n_splits <= 64)
-    for (uint32_t i = threadIdx.x; i < ng * ka.n_splits; i += blockDim.x) {
-        const uint32_t g = i / ka.n_splits, sidx = i % ka.n_splits;
-        const float* ps = a.scratch + (((size_t)b * a.Hq + kvh * ka.G + g0 + g) * ka.n_splits + sidx) * (D + 2);
-        ml[2 * i] = __ldcg(ps);
-        ml[2 * i + 1] = __ldcg(ps + 1);
-    }
-    __syncthreads();
-    for (uint32_t i = threadIdx.x; i < ng * D; i += blockDim.x) {
-        const uint32_t g = i / D, d = i % D;
-        const uint32_t h = kvh * ka.G + g0 + g;
-        const float* ps = a.scratch + (((size_t)b * a.Hq + h) * ka.n_splits) * (D + 2) + 2 + d;
-        const float* mlg = ml + (size_t)g * ka.n_splits * 2;
-        float M = -INFINITY;
-        for (uint32_t sidx = 0; sidx < ka.n_splits; ++sidx) M = fmaxf(M, mlg[2 * sidx]);
-        float L = 0.0f, A = 0.0f;
-#pragma unroll 8
-        for (uint32_t sidx = 0; sidx < ka.n_splits; ++sidx) {
-            const float ms = mlg[2 * sidx];
-            const float f = (ms == -INFINITY) ? 0.0f : __expf(ms - M);
-            L = fmaf(mlg[2 * sidx + 1], f, L);
-            A = fmaf(__ldcg(ps + (size_t)sidx * (D + 2)), f, A);
+    // ---- merge the splits: the blocks of one (sequence, head group) form a thread-block cluster and read each
+    // other's partials through distributed shared memory -- no global round trip, no atomics, fixed order
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const uint32_t n = ka.n_splits;  // == cluster size along y
+    const uint32_t per_d = (D + n - 1) / n;
+    const uint32_t d_lo = split * per_d, d_hi = min((uint32_t)D, d_lo + per_d);
+    for (uint32_t i = threadIdx.x; i < ng * per_d; i += blockDim.x) {
+        const uint32_t g = i / per_d, d = d_lo + i % per_d;
+        if (d < d_hi) {
+            // all remote reads are issued before any is used (a remote shared-memory load costs hundreds of cycles)
+            float ms[ATTN_MAX_SPLITS], ls[ATTN_MAX_SPLITS], as[ATTN_MAX_SPLITS];
+#pragma unroll
+            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) {
+                const float* rc = cluster.map_shared_rank(&comb[g][0], (uint32_t)r < n ? r : 0);
+                const bool on = (uint32_t)r < n;
+                ms[r] = on ? rc[0] : -INFINITY;
+                ls[r] = on ? rc[1] : 0.0f;
+                as[r] = on ? rc[2 + d] : 0.0f;
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) M = fmaxf(M, ms[r]);
+            float L = 0.0f, A = 0.0f;
+#pragma unroll
+            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) {
+                const float f = (ms[r] == -INFINITY) ? 0.0f : __expf(ms[r] - M);
+                L = fmaf(ls[r], f, L);
+                A = fmaf(as[r], f, A);
+            }
+            a.out[(size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0 + g) * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
         }
-        a.out[(size_t)b * a.Hq * D + (size_t)h * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
     }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
     trace_exit(a.trace);
 }
 
-// scratch: partials [batch][Hq][n_splits][D+2] floats, then counters [batch][Hq] u32 (upper bound)
+// the split partials live in shared memory now; a small scratch is still reserved for callers that pass one
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits) {
-    return (uint64_t)batch * Hq * max_splits * (D + 2) + (uint64_t)batch * Hq + 16;
+    (void)Hq; (void)D; (void)batch; (void)max_splits;
+    return 64;
 }
-// tokens per split: whole KV blocks, at least 32, at most ATTN_MAX_SPLITS splits over max_seq
+// kept for callers that size things per split; the kernel itself divides the current length evenly
 uint32_t attn_tokens_per_split(uint32_t max_seq) {
-    uint32_t tps = (max_seq + ATTN_MAX_SPLITS - 1) / ATTN_MAX_SPLITS;
-    tps = ((tps + 15) / 16) * 16;
-    return tps < 32 ? 32 : tps;
+    const uint32_t n = attn_pick_splits(max_seq);
+    uint32_t tps = ((max_seq ? max_seq : 1) + n - 1) / n;
+    return ((tps + 15) / 16) * 16;
 }
+// one split per 32 tokens of the longest context, at most a cluster's worth
 uint32_t attn_pick_splits(uint32_t max_seq) {
-    const uint32_t tps = attn_tokens_per_split(max_seq ? max_seq : 1);
-    const uint32_t s = ((max_seq ? max_seq : 1) + tps - 1) / tps;
+    uint32_t s = ((max_seq ? max_seq : 1) + 31) / 32;
+    if (s > (uint32_t)ATTN_MAX_SPLITS) s = ATTN_MAX_SPLITS;
     return s < 1 ? 1 : s;
 }
 
 template <typename KVT, int EPL, int GM>
 static cudaError_t launch_split_g(const LaunchCfg& lc, AttnKArgs ka) {
     ka.g_chunks = (ka.G + GM - 1) / GM;
-    const size_t smem = (size_t)ATTN_WARPS * GM * EPL * 32 * sizeof(float);
+    const size_t smem = AttnSmem<KVT, EPL, GM>::total;
     dim3 grid(ka.a.Hkv * ka.g_chunks, ka.n_splits, ka.a.batch);
-    return launch(lc, k_attn_split<KVT, EPL, GM>, grid, dim3(ATTN_WARPS * 32), smem, ka);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(ATTN_WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = lc.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = ka.n_splits; attr[0].val.clusterDim.z = 1;
+    cfg.numAttrs = 1;
+    if (lc.pdl) {
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attr;
+    if (lc.counter) ++*lc.counter;
+    return cudaLaunchKernelEx(&cfg, k_attn_split<KVT, EPL, GM>, ka);
 }
 
 template <typename KVT, int EPL>
@@ -364,17 +456,19 @@ static cudaError_t dispatch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
 
 template <typename KVT, int EPL, int GM>
 static cudaError_t opt_in_one() {
-    const size_t smem = (size_t)ATTN_WARPS * GM * EPL * 32 * sizeof(float);
-    if (smem <= 16 * 1024) return cudaSuccess;
+    const size_t smem = AttnSmem<KVT, EPL, GM>::total;
     return cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 template <typename KVT>
 static cudaError_t opt_in_all() {
     cudaError_t e;
-    if ((e = opt_in_one<KVT, 4, 8>()) != cudaSuccess) return e;
-    if ((e = opt_in_one<KVT, 4, 4>()) != cudaSuccess) return e;
-    if ((e = opt_in_one<KVT, 8, 1>()) != cudaSuccess) return e;
-    return opt_in_one<KVT, 16, 1>();
+#define VB_ATTN_OPT(E, G) if ((e = opt_in_one<KVT, E, G>()) != cudaSuccess) return e
+    VB_ATTN_OPT(1, 1); VB_ATTN_OPT(1, 2); VB_ATTN_OPT(1, 4); VB_ATTN_OPT(1, 8);
+    VB_ATTN_OPT(2, 1); VB_ATTN_OPT(2, 2); VB_ATTN_OPT(2, 4); VB_ATTN_OPT(2, 8);
+    VB_ATTN_OPT(4, 1); VB_ATTN_OPT(4, 2); VB_ATTN_OPT(4, 4); VB_ATTN_OPT(4, 8);
+    VB_ATTN_OPT(8, 1); VB_ATTN_OPT(16, 1);
+#undef VB_ATTN_OPT
+    return cudaSuccess;
 }
 cudaError_t attn_init() {
     cudaError_t e = opt_in_all<__half>();
@@ -393,7 +487,7 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
     ka.n_splits = a.max_splits;
     ka.tokens_per_split = a.tokens_per_split;
     ka.kv_batch_stride = kv_batch_stride;
-    ka.counters = reinterpret_cast<uint32_t*>(a.scratch + (uint64_t)a.batch * a.Hq * a.max_splits * (a.D + 2));
+    ka.counters = nullptr;
     return a.kv_fp16 ? dispatch_split<__half>(lc, ka) : dispatch_split<float>(lc, ka);
 }
 
@@ -421,8 +515,6 @@ extern "C" int32_t vb_op_gqa_attention(float* out, const float* q, const float* 
                (unsigned long long)scratch_bytes, (unsigned long long)need);
     LaunchCfg lc; lc.stream = (cudaStream_t)stream;
     VB_CUDA(kernels_init());
-    // the split counters must start at zero; a caller's scratch is not
-    VB_CUDA(cudaMemsetAsync((float*)scratch + (uint64_t)n_q * a.max_splits * (head_dim + 2), 0, (size_t)n_q * 4 + 64, lc.stream));
     VB_CUDA(attention(lc, a));
     return VB_OK;
 }

@@ -815,11 +815,14 @@ int32_t vb_trace_read(vb_ctx* c, uint64_t* out, uint32_t max_records, uint32_t* 
     if (!c->trace) { set_error("vb_trace_read: enable the \"trace\" option first"); return VB_ERR_STATE; }
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    const uint32_t n = c->trace_n < max_records ? c->trace_n : max_records;
+    uint32_t n = c->trace_n < max_records ? c->trace_n : max_records;
+    if (getenv("VB_DBG_TRACE_ALL")) n = max_records < 1024 ? max_records : 1024;
     std::vector<unsigned long long> buf((size_t)n * 4);
     VB_CUDA(cudaMemcpy(buf.data(), c->trace, buf.size() * 8, cudaMemcpyDeviceToHost));
     for (uint32_t i = 0; i < n; ++i) { out[3 * i] = buf[4 * i]; out[3 * i + 1] = buf[4 * i + 1]; out[3 * i + 2] = buf[4 * i + 2]; }
-    VB_CUDA(cudaMemset(c->trace, 0, 1024 * 4 * sizeof(unsigned long long)));  // exit stamps are running maxima
+    // exit stamps are running maxima: clear them, on the context's own (non-blocking) stream
+    VB_CUDA(cudaMemsetAsync(c->trace, 0, 1024 * 4 * sizeof(unsigned long long), c->stream));
+    VB_CUDA(cudaStreamSynchronize(c->stream));
     *n_records = n;
     return VB_OK;
 }

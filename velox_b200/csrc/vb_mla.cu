@@ -37,8 +37,6 @@ cudaError_t mla_absorbed(const LaunchCfg& lc, float* dst, const float* x, const 
     a.max_splits = attn_pick_splits(safe_step + 1);
     a.tokens_per_split = attn_tokens_per_split(safe_step + 1);
     a.scratch = part;
-    // split counters start at zero
-    if ((e = cudaMemsetAsync(part + (size_t)a.max_splits * (latent + 2), 0, 64, lc.stream)) != cudaSuccess) return e;
     const float scale = (latent >= 128) ? (1.0f / sqrtf(128.0f)) : (1.0f / sqrtf((float)latent));
     if ((e = attention_ex(lc, a, scale, 0)) != cudaSuccess) return e;
     if (dst != x) {
