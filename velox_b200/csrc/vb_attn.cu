@@ -1,14 +1,19 @@
 // Decode attention: flash-decode split-K over the KV length with grouped queries, one kernel.
 //
 // Grid (kv_head x q-head chunk, split, sequence).  A block owns one KV head, the (up to 8) query heads that
-// share it and one slice of the context (a whole number of 16-token KV blocks).  Each of its 4 warps takes 4
-// or 8 tokens at a time: all their K and V rows are requested before anything is computed (the kernel is
-// latency-bound at decode sizes), every row is used for all query heads of the group, the per-lane partial
-// dot products are reduced with a transposing butterfly (one value per lane instead of one reduction per
-// value), and each warp keeps an online-softmax state (m, l, acc) per query head.  The block's partial goes
-// to scratch; the LAST block of a (sequence, head group) to finish -- found with a fence and an atomic
-// counter that it also resets, so the kernel can be replayed from a CUDA graph -- merges the splits.  The
-// merge order is fixed, so results do not depend on which block came last.
+// share it and one slice of the context (a whole number of 16-token KV blocks).  The kernel is latency-bound
+// at decode sizes, so it makes as few dependent memory trips as it can: (1) the sequence's position, (2) the
+// slice's block-table entries together with the query heads, (3) per chunk of up to 64 tokens ALL K and V
+// rows at once, cp.async into shared memory, double buffered.  Each of the 4 warps then takes 4 or 8 tokens
+// at a time, uses every row for all query heads of the group, reduces the per-lane partial dot products
+// with a transposing butterfly (one value per lane instead of one reduction per value) and keeps an
+// online-softmax state (m, l, acc) per query head.  The splits of one (sequence, head group) form a
+// thread-block cluster: each block leaves its partial in its own shared memory and, after a cluster barrier,
+// every block merges one slice of the head dimension by reading the others' partials through distributed
+// shared memory -- no global round trip, no atomics, a fixed merge order.
+// In the engine the kernel also does what the reference runs as separate kernels before attention
+// (fused_rope_kernel and the KV write of fused_qkv, src/runners/tinystories_smollm.cu:189-318): bias, RoPE of
+// q and of the new k at the sequence's position, and the append of K/V to the cache.
 //
 // The reference computes the same quantity with a two-pass softmax on the CPU (src/runtime.rs:772-831) and a
 // sequential online softmax on the GPU (src/runners/tinystories_smollm.cu:321-393); its split-K test is
@@ -36,9 +41,7 @@ struct AttnKArgs {
     uint32_t G;          // query heads per KV head
     uint32_t g_chunks;   // ceil(G / GM), GM = query heads a block handles at once
     uint32_t n_splits;
-    uint32_t tokens_per_split;
     size_t kv_batch_stride;  // contiguous: elements between sequences
-    uint32_t* counters;      // [batch][Hkv * g_chunks], zero between launches
 };
 
 template <typename KVT, int EPL>
@@ -485,9 +488,7 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
     ka.G = a.Hq / a.Hkv;
     ka.g_chunks = 1;
     ka.n_splits = a.max_splits;
-    ka.tokens_per_split = a.tokens_per_split;
     ka.kv_batch_stride = kv_batch_stride;
-    ka.counters = nullptr;
     return a.kv_fp16 ? dispatch_split<__half>(lc, ka) : dispatch_split<float>(lc, ka);
 }
 

@@ -815,8 +815,7 @@ int32_t vb_trace_read(vb_ctx* c, uint64_t* out, uint32_t max_records, uint32_t* 
     if (!c->trace) { set_error("vb_trace_read: enable the \"trace\" option first"); return VB_ERR_STATE; }
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    uint32_t n = c->trace_n < max_records ? c->trace_n : max_records;
-    if (getenv("VB_DBG_TRACE_ALL")) n = max_records < 1024 ? max_records : 1024;
+    const uint32_t n = c->trace_n < max_records ? c->trace_n : max_records;
     std::vector<unsigned long long> buf((size_t)n * 4);
     VB_CUDA(cudaMemcpy(buf.data(), c->trace, buf.size() * 8, cudaMemcpyDeviceToHost));
     for (uint32_t i = 0; i < n; ++i) { out[3 * i] = buf[4 * i]; out[3 * i + 1] = buf[4 * i + 1]; out[3 * i + 2] = buf[4 * i + 2]; }

@@ -21,24 +21,23 @@
 // element 4t+b of the group in its low nibble and element 16+4t+b in its high nibble -- the A fragment of
 // m16n8k32 after the two ANDs.  At byte 1024 + 4*L: half2(scale[row g][group t], scale[row g+8][group t]).
 //
-// Data movement and overlap are those of the pipelined fp16 kernel: persistent blocks, a producer warp
-// streaming row tiles through a shared-memory ring with cp.async.bulk + mbarriers (started before the
-// grid-dependency wait), eight consumer warps, bounded waits that report through a device error word.
+// Data movement.  Blocks are persistent (two per SM, 8 warps); the 8 warps split the K extent of the current
+// 16-row tile.  Each warp streams ITS blocks through a private shared-memory ring with cp.async (16-byte
+// asynchronous copies that bypass L1 and need no registers): ~130 KB per SM stay in flight, which is what it
+// takes to pull >6 TB/s, and the data path has no block-wide barrier and no spin-wait at all.  (A ring fed by
+// one producer thread with cp.async.bulk + mbarriers measured ~4.4 TB/s at any depth on this part and was
+// dropped here.)  Kernels are launched with programmatic stream serialization: weights never depend on the
+// previous kernel, so every warp fills its ring BEFORE the grid-dependency wait and only then reads x.
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
-#include "vb_tma.cuh"
 
 namespace vb {
 
 constexpr int IM_WARPS = 8;
 constexpr int IM_CONSUMERS = IM_WARPS * 32;
-constexpr int IM_THREADS = IM_CONSUMERS + 32;
 constexpr int IM_BLK_BYTES = 1152;
-constexpr int IM_SB = 8;  // blocks per stage
-constexpr int IM_STAGE_BYTES = IM_SB * IM_BLK_BYTES;
-constexpr int IM_MAX_STAGES = 8;
+constexpr int IM_STAGE_BYTES = IM_WARPS * IM_BLK_BYTES;  // one ring slot of every warp
 constexpr int IM_MAX_SMEM = 112 * 1024;
-constexpr uint32_t IM_ERR_FULL = 0x61u, IM_ERR_EMPTY = 0x62u;
 
 struct ImmaArgs {
     const unsigned char* w;  // v3 tile-major blocks
@@ -49,8 +48,6 @@ struct ImmaArgs {
     const SeqState* state;
     uint32_t dst_offset;
     int epilogue;            // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU (interleaved 8+8 tiles)
-    uint32_t* err;
-    uint32_t n_stages;
     unsigned long long* trace;  // optional timestamp record
 };
 
@@ -148,7 +145,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
     pdl_launch_dependents();
 
     // ---- prologue: weights do not depend on the previous kernel; fill the ring before waiting for x ----------
-    const uint32_t my_ring = smem_u32(ring + (size_t)warp * NS * IM_BLK_BYTES);
+    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * NS * IM_BLK_BYTES);
     BlockCursor icur{blockIdx.x, warp};  // next block to request
     uint32_t issued = 0;
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
@@ -377,10 +374,8 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     ImmaArgs f;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
-    f.dst_offset = a.dst_offset; f.epilogue = a.epilogue; f.n_stages = (uint32_t)ns;
+    f.dst_offset = a.dst_offset; f.epilogue = a.epilogue;
     f.trace = a.trace;
-    cudaError_t e = fast_error_word(&f.err);
-    if (e != cudaSuccess) return e;
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;

@@ -1,0 +1,55 @@
+"""Per-kernel device timeline of one decode step (profiling aid).
+
+    python -m velox_b200.trace [--layers 4] [--prompt-len 512]
+
+Builds a Llama-3-8B-shape int4 model with synthetic weights, captures the decode graph with the "trace"
+option on and prints, for every traced kernel of one replayed step, when its first block entered, when it got
+past the grid-dependency wait and when its last block left (microseconds since the step's first kernel).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+
+import numpy as np
+
+from . import lib as L
+from .engine import Engine
+from .modelspec import LLAMA3_8B_INT4, PROMPT_STREAM
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=4)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    args = ap.parse_args()
+    spec = LLAMA3_8B_INT4.scaled(name="trace", n_layers=args.layers)
+    eng = Engine(spec, max_seq_len=args.prompt_len + 64)
+    eng.load_synthetic(1)
+    eng.set_option("trace", 1)
+    rng = np.random.default_rng(PROMPT_STREAM)
+    prompt = rng.integers(0, spec.vocab, args.prompt_len, dtype=np.uint32)
+    eng.reserve(0, args.prompt_len + 64)
+    eng.prefill(prompt, 0)
+    eng.build_graph()
+    eng.decode(8)
+    out = np.zeros(3 * 1024, dtype=np.uint64)
+    n = C.c_uint32()
+    lib = L.load()
+    L.check(lib.vb_trace_read(eng.h, out.ctypes.data_as(C.c_void_p), 1024, C.byref(n)))  # clears
+    ms = eng.decode(1, timed=True)
+    L.check(lib.vb_trace_read(eng.h, out.ctypes.data_as(C.c_void_p), 1024, C.byref(n)))
+    r = out[:3 * n.value].reshape(-1, 3).astype(np.int64)
+    names = ["qkv", "attn", "o_proj", "gate_up", "down"]
+    print("step %.4f ms, %d traced kernels (context %d)" % (ms, n.value, args.prompt_len + 8))
+    t0, prev = r[0, 0], r[0, 0]
+    for i, (a, b, c) in enumerate(r):
+        nm = names[i % 5] if i < args.layers * 5 else "lm_head"
+        print("%-8s enter %8.2f  past_wait %8.2f  exit %8.2f | after_wait %6.2f us  gap %5.2f us"
+              % (nm, (a - t0) / 1e3, (b - t0) / 1e3, (c - t0) / 1e3, (c - b) / 1e3, (b - prev) / 1e3))
+        prev = c
+    eng.close()
+
+
+if __name__ == "__main__":
+    main()
