@@ -182,6 +182,17 @@ int32_t vb_op_gqa_attention(float* out, const float* q, const float* k_cache, co
 /* SampleArgmax (src/runtime.rs:1078-1088): first index of the maximum; NaN never wins. */
 int32_t vb_op_sample_argmax(uint32_t* out_token, const float* logits, uint32_t n, void* scratch,
                             uint64_t scratch_bytes, void* stream);
+/* The same argmax for callers that must not allocate device memory and have none to spare: a runner that has
+ * handed all of its memory to the arenas up front (the reference's "0 dynamic allocations" serving rule), code
+ * running while a stream is being captured, or a host behind an FFI that forbids cudaMalloc.  No counterpart in
+ * the reference.  The stage-1 candidates go to a scratch array built into the library (a file-scope __device__
+ * array, 4 KiB, which every GPU that loads the library keeps until exit) instead of a caller buffer, so n is
+ * limited to 1,048,576 logits; a larger n is refused with VB_ERR_INVALID.  The call itself allocates nothing
+ * (no cudaMalloc/cudaFree, no allocating library routine).  The first call on a device looks the array's device
+ * address up (cudaGetSymbolAddress): make that first call before any stream capture.  All calls on a device
+ * share the one array: calls that may overlap on the GPU (different streams) race and must be serialised by
+ * the caller.  Nothing in the array has to start at zero -- every slot read was written by the same call. */
+int32_t vb_op_sample_argmax_static(uint32_t* out_token, const float* logits, uint32_t n, void* stream);
 /* FusedMlaAbsorbedAttn (src/runtime.rs:944-1044): one layer's latent pool [max_seq][latent], fp32. */
 int32_t vb_op_mla_absorbed(float* dst, const float* x, const float* w_norm, const float* w_dkv,
                            const float* w_absq, const float* w_abso, float* latent_pool, uint32_t step,

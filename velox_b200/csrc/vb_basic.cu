@@ -582,6 +582,36 @@ int32_t vb_op_sample_argmax(uint32_t* out_token, const float* logits, uint32_t n
     return VB_OK;
 }
 
+// ---- argmax without any allocation ------------------------------------------------------------------------
+// Largest row the built-in scratch covers: 2^20 logits = 512 stage-1 candidates of 8 bytes.
+#define VB_STATIC_ARGMAX_MAX_N (1u << 20)
+static __device__ __align__(256) unsigned char g_argmax_scratch[(VB_STATIC_ARGMAX_MAX_N / 2048) * 8];
+// In host code `g_argmax_scratch` is only a stand-in for the symbol; the device address is looked up once per
+// device (with that device current) and kept here.
+static void* g_argmax_scratch_dev[64] = {nullptr};
+
+int32_t vb_op_sample_argmax_static(uint32_t* out_token, const float* logits, uint32_t n, void* stream) {
+    VB_REQUIRE(out_token && logits, "vb_op_sample_argmax_static: null pointer");
+    VB_REQUIRE(n > 0, "vb_op_sample_argmax_static: empty logits");
+    VB_REQUIRE(n <= VB_STATIC_ARGMAX_MAX_N, "vb_op_sample_argmax_static: n=%u exceeds the built-in scratch (max %u logits); "
+               "use vb_op_sample_argmax with your own scratch", n, (unsigned)VB_STATIC_ARGMAX_MAX_N);
+    int dev = 0;
+    VB_CUDA(cudaGetDevice(&dev));
+    VB_REQUIRE(dev >= 0 && dev < 64, "vb_op_sample_argmax_static: device ordinal %d not supported", dev);
+    if (!g_argmax_scratch_dev[dev]) {
+        void* p = nullptr;
+        VB_CUDA(cudaGetSymbolAddress(&p, g_argmax_scratch));  // set-up, first call on this device
+        g_argmax_scratch_dev[dev] = p;
+    }
+    const uint32_t nc = argmax_chunks(n);
+    float* cv = (float*)g_argmax_scratch_dev[dev];
+    uint32_t* ci = (uint32_t*)(cv + nc);
+    LaunchCfg lc; lc.stream = (cudaStream_t)stream;
+    // stage 1 writes every candidate slot that stage 2 reads, so nothing has to be cleared between calls
+    VB_CUDA(argmax(lc, out_token, logits, n, 1, cv, ci, nullptr, nullptr, 0));
+    return VB_OK;
+}
+
 int32_t vb_dev_alloc(void** out, uint64_t bytes) {
     VB_REQUIRE(out != nullptr, "vb_dev_alloc: null out");
     void* p = nullptr;

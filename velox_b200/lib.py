@@ -76,6 +76,7 @@ SIGNATURES = {
     "vb_op_rope": (_i32, [_vp, _u32, _u32, _u32, _f32, _vp]),
     "vb_op_gqa_attention": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
     "vb_op_sample_argmax": (_i32, [_vp, _vp, _u32, _vp, _u64, _vp]),
+    "vb_op_sample_argmax_static": (_i32, [_vp, _vp, _u32, _vp]),
     "vb_op_mla_absorbed": (_i32, [_vp] * 7 + [_u32] * 4 + [_f32, _vp, _u64, _vp]),
     "vb_op_quantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
     "vb_op_dequantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
