@@ -9,6 +9,9 @@ A "step" is one decode step (one token).  `value` is decode tok/s with everythin
 CUDA events on the library's stream around K CUDA-graph replays; `e2e` is the same metric when every step
 is driven from the host through the C ABI (token and position sent in, sampled token read back).
 N>1 runs N independent replicas (the 8B model fits one GPU): weak scaling, no data-path collective.
+The workloads named qwen2-72b-int4-tp* instead shard ONE Qwen2-72B-shape model over the N ranks (tensor
+parallel: one NCCL all-reduce after the O and the down projection, captured in the decode graph): strong
+scaling, `value` is the tok/s of the group and the roofline is per GPU.
 
 --impl reference times the CPU restatement of the reference runtime (oracle/, OpenMP on all host cores) on
 a bounded sample of the same workload; rank 0 only.
@@ -90,10 +93,18 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def is_tp(name: str) -> bool:
+    return name.startswith("qwen2-72b-int4-tp")
+
+
 def workload_spec(name: str):
-    from velox_b200.modelspec import LLAMA3_8B_INT4
+    from velox_b200.modelspec import LLAMA3_8B_INT4, QWEN2_72B_INT4
     if name == "llama3-8b-int4-bs1":
         return LLAMA3_8B_INT4, 1
+    if name == "qwen2-72b-int4-tp-bs1":
+        return QWEN2_72B_INT4, 1
+    if name == "qwen2-72b-int4-tp-bs1-8layers":  # quick check of the sharded path
+        return QWEN2_72B_INT4.scaled(name="qwen2-72b-int4g32-8layers", n_layers=8), 1
     if name == "llama3-8b-int4-bs1-4layers":  # quick functional check of the bench itself
         return LLAMA3_8B_INT4.scaled(name="llama3-8b-int4g32-4layers", n_layers=4), 1
     raise SystemExit("unknown workload %r" % name)
@@ -190,7 +201,14 @@ def main():
 
     from velox_b200.engine import Engine
     max_seq = args.prompt_len + args.warmup + 2 * args.steps + 16
-    eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank)
+    tp = is_tp(args.workload)
+    if tp and world > 1:
+        # one model over all ranks; the 72B shape only fits one GPU with the single-layout arena
+        from velox_b200.tp import share_unique_id
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, tp_rank=rank, tp_size=world, lean_weights=True)
+        eng.tp_init(share_unique_id(Engine.tp_unique_id))
+    else:
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp)
     eng.set_option("gemv_path", args.gemv_path)
     if args.no_pdl:
         eng.set_option("pdl", 0)
@@ -231,7 +249,8 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    value = world * batch * 1e3 / ms_per_step
+    groups = 1 if tp else world  # independent model instances
+    value = groups * batch * 1e3 / ms_per_step
 
     # ---- end to end: every step driven from the host through the C ABI ----------------------------------
     tok, pos = eng.state(0)
@@ -252,22 +271,23 @@ def main():
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
-    e2e = world * batch * args.steps / e2e_s
+    e2e = groups * batch * args.steps / e2e_s
 
     peak, peak_kind = load_peaks()
     step_bytes = wbytes + (kv0 + kv1) // 2  # mean context over the timed region
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len,
                    "weights": "int4 g32 + fp16 scales, fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
                    "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),
-                   "gemv_path": args.gemv_path, "replicas": world},
+                   "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
-                     "kernel": "decode step (one CUDA-graph launch = one token)", "bytes_per_launch": step_bytes},
+                     "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
+                     "bytes_per_launch": step_bytes},
         "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch},
         "gpu_launches": int(launches), "clocks": clocks,
         "ttft_ms": 1e3 * ttft_s, "load_s": load_s,

@@ -69,6 +69,12 @@ enum {
 enum { VB_LOC_HOST = 0, VB_LOC_DEVICE = 1 };
 enum { VB_ATTN_GQA = 0, VB_ATTN_MLA_REF = 1 };
 
+/* vb_model_desc.flags */
+#define VB_FLAG_LEAN_WEIGHTS 1u /* keep, of each int4 g32 matrix, only the tile-major copy the batch-1 decode
+                                 * kernel streams (1x the packed bytes instead of ~3-4x): for models sized to fill
+                                 * the GPU.  Needs max_batch == 1; vb_export_tensor and the exact (gemv_path 0)
+                                 * kernels are unavailable for those matrices. */
+
 /* Model description: the VELOX_MODEL_* constants the compiler emits (src/codegen.rs:101-113) plus
  * the serving parameters the runner chooses.  Replaces VeloxCudaArena/TransformerConfig
  * (src/codegen.rs:1032-1043, src/runtime.rs:1160-1171). */
@@ -88,7 +94,8 @@ typedef struct vb_model_desc {
     uint32_t attn_kind;       /* VB_ATTN_*                                                      */
     uint32_t mla_latent;      /* latent width of the reference absorbed-MLA block               */
     uint32_t tp_rank, tp_size;/* tensor-parallel coordinates (tp_size 1 = single GPU)           */
-    uint32_t reserved[8];
+    uint32_t flags;           /* VB_FLAG_* (0 = default)                                        */
+    uint32_t reserved[7];
 } vb_model_desc;
 
 typedef struct vb_ctx vb_ctx;

@@ -105,6 +105,30 @@ def test_eager_graph_and_stepwise_agree():
         assert np.array_equal(lg, outs[0][1])
 
 
+def test_lean_weight_layout_is_bit_identical_and_smaller():
+    """VB_FLAG_LEAN_WEIGHTS keeps one tile-major copy per int4 matrix: same tokens and logits, less memory,
+    no canonical copy to export."""
+    from velox_b200.engine import Engine
+    spec = SMALL_SPECS[3]
+    prompt = H.prompt_tokens(spec, 9, 6)
+    full = H.build_engine(spec, 9, 48)
+    lean = Engine(spec, max_seq_len=48, lean_weights=True)
+    lean.load_synthetic(9)
+    a, b = full.generate_greedy(prompt, 10), lean.generate_greedy(prompt, 10)
+    assert np.array_equal(a, b) and np.array_equal(full.logits(), lean.logits())
+    wf, wl = L.C.c_uint64(), L.C.c_uint64()
+    L.load().vb_weight_bytes(full.h, L.C.byref(wf))
+    L.load().vb_weight_bytes(lean.h, L.C.byref(wl))
+    assert wl.value * 2 < wf.value
+    with pytest.raises(L.VeloxError) as ei:
+        lean.export_tensor(L.ROLE_WQ, 0, spec.qdim, spec.d_model)
+    assert ei.value.code == L.ERR_STATE
+    with pytest.raises(L.VeloxError):
+        Engine(spec, max_seq_len=48, max_batch=2, lean_weights=True)
+    full.close()
+    lean.close()
+
+
 def test_batched_variable_length_sequences():
     """Several slots with different prompt lengths decode together; each matches its own CPU run."""
     spec = SMALL_SPECS[4]

@@ -48,6 +48,33 @@ cudaError_t fill_normal(const LaunchCfg& lc, float* dst, uint64_t n, uint64_t se
                   std * (1.0f / 65536.0f));
 }
 
+// The same generator restricted to the rectangle rows [r0, r0+rows) x cols [c0, c0+cols) of a [*][full_cols] tensor:
+// a tensor-parallel rank fills its shard with exactly the values the whole tensor would hold there.
+__global__ void k_fill_normal_slice(float* __restrict__ dst, uint64_t rows, uint64_t cols, uint64_t full_cols, uint64_t r0,
+                                    uint64_t c0, uint64_t key, float mean, float scale) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, n = rows * cols;
+    for (; i < n; i += stride) {
+        const uint64_t r = i / cols, c = i - r * cols;
+        const uint64_t g = (r0 + r) * full_cols + c0 + c;
+        uint32_t s = 0;
+#pragma unroll
+        for (uint64_t j = 0; j < 3; ++j) s += lanes16_sum(mix64(key + (3ULL * g + j + 1ULL) * 0x9E3779B97F4A7C15ULL));
+        float v = __fmul_rn((float)((int32_t)s - 393210), scale);
+        dst[i] = __fadd_rn(v, mean);
+    }
+}
+
+cudaError_t fill_normal_slice(const LaunchCfg& lc, float* dst, uint64_t rows, uint64_t cols, uint64_t full_cols, uint64_t r0,
+                              uint64_t c0, uint64_t seed, uint64_t stream_id, float mean, float std) {
+    const uint64_t n = rows * cols;
+    if (n == 0) return cudaSuccess;
+    uint64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    return launch(lc, k_fill_normal_slice, dim3((unsigned)blocks), dim3(256), 0, dst, rows, cols, full_cols, r0, c0,
+                  stream_key(seed, stream_id), mean, std * (1.0f / 65536.0f));
+}
+
 // ---- quantizers ------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t pack8(const uint32_t q[8]) {
     return (q[0] << 0) | (q[2] << 4) | (q[4] << 8) | (q[6] << 12) | (q[1] << 16) | (q[3] << 20) | (q[5] << 24) |
@@ -458,8 +485,11 @@ __global__ void k_argmax_stage1(float* __restrict__ cand_v, uint32_t* __restrict
 }
 
 // stage 2: one block per sequence; writes the token, optionally advances the device state and the ring
+// With `pair_out` (vocab-parallel head) it instead stores this rank's best as (value, index + idx_offset) and
+// leaves the state alone: k_argmax_pairs picks the winner over all ranks.
 __global__ void k_argmax_stage2(uint32_t* __restrict__ out_token, const float* __restrict__ cand_v, const uint32_t* __restrict__ cand_i,
-                                uint32_t n_cand, SeqState* __restrict__ state, uint32_t* __restrict__ ring, uint32_t ring_slots) {
+                                uint32_t n_cand, SeqState* __restrict__ state, uint32_t* __restrict__ ring, uint32_t ring_slots,
+                                ArgPair* __restrict__ pair_out, uint32_t idx_offset) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ ArgPair red[32];
@@ -471,7 +501,9 @@ __global__ void k_argmax_stage2(uint32_t* __restrict__ out_token, const float* _
         best = arg_merge(best, c);
     }
     best = arg_block(best, red);
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && pair_out) {
+        pair_out[b] = ArgPair{best.v, best.i == 0xFFFFFFFFu ? best.i : best.i + idx_offset};
+    } else if (threadIdx.x == 0) {
         const uint32_t tok = (best.i == 0xFFFFFFFFu) ? 0u : best.i;
         if (out_token) out_token[b] = tok;
         if (state) {
@@ -489,7 +521,39 @@ cudaError_t argmax(const LaunchCfg& lc, uint32_t* out_token, const float* logits
     const uint32_t n_chunks = (n + chunk - 1) / chunk;
     cudaError_t e = launch(lc, k_argmax_stage1, dim3(n_chunks, batch), dim3(256), 0, cand_v, cand_i, logits, n, chunk);
     if (e != cudaSuccess) return e;
-    return launch(lc, k_argmax_stage2, dim3(batch), dim3(256), 0, out_token, cand_v, cand_i, n_chunks, state, ring, ring_slots);
+    return launch(lc, k_argmax_stage2, dim3(batch), dim3(256), 0, out_token, cand_v, cand_i, n_chunks, state, ring, ring_slots,
+                  (ArgPair*)nullptr, 0u);
+}
+
+// Vocab-parallel head, step 1: this rank's best (value, global index) per sequence into pair_out[batch] (8 bytes each).
+cudaError_t argmax_shard(const LaunchCfg& lc, void* pair_out, const float* logits, uint32_t n, uint32_t idx_offset, uint32_t batch,
+                         float* cand_v, uint32_t* cand_i, SeqState* state) {
+    const uint32_t chunk = 2048;
+    const uint32_t n_chunks = (n + chunk - 1) / chunk;
+    cudaError_t e = launch(lc, k_argmax_stage1, dim3(n_chunks, batch), dim3(256), 0, cand_v, cand_i, logits, n, chunk);
+    if (e != cudaSuccess) return e;
+    return launch(lc, k_argmax_stage2, dim3(batch), dim3(256), 0, (uint32_t*)nullptr, cand_v, cand_i, n_chunks, state,
+                  (uint32_t*)nullptr, 0u, (ArgPair*)pair_out, idx_offset);
+}
+
+// Step 2, after the all-gather: pairs[rank][batch]; same rule (greater value, then lower index; no candidate -> 0).
+__global__ void k_argmax_pairs(const ArgPair* __restrict__ pairs, uint32_t n_ranks, uint32_t batch, SeqState* __restrict__ state,
+                               uint32_t* __restrict__ ring, uint32_t ring_slots) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch || !state[b].active) return;
+    ArgPair best{-INFINITY, 0xFFFFFFFFu};
+    for (uint32_t r = 0; r < n_ranks; ++r) best = arg_merge(best, pairs[(size_t)r * batch + b]);
+    const uint32_t tok = (best.i == 0xFFFFFFFFu) ? 0u : best.i;
+    const uint32_t pos = state[b].pos;
+    if (ring) ring[(size_t)b * ring_slots + (pos % ring_slots)] = tok;
+    state[b].token = tok;
+    state[b].pos = pos + 1;
+}
+cudaError_t argmax_pairs(const LaunchCfg& lc, const void* pairs, uint32_t n_ranks, uint32_t batch, SeqState* state, uint32_t* ring,
+                         uint32_t ring_slots) {
+    return launch(lc, k_argmax_pairs, dim3((batch + 63) / 64), dim3(64), 0, (const ArgPair*)pairs, n_ranks, batch, state, ring, ring_slots);
 }
 uint32_t argmax_chunks(uint32_t n) { return (n + 2047) / 2048; }
 

@@ -12,6 +12,7 @@
 
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
+#include "vb_nccl.h"
 
 namespace vb {
 
@@ -40,6 +41,13 @@ struct vb_ctx {
 
     // derived
     uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1, tokens_per_split = 32;
+    // this rank's shard (tensor parallel; equal to the whole model when tp_size == 1):
+    // query/KV heads, FFN columns [ffn_off, ffn_off + ffn) in whole 128-column blocks, vocabulary rows
+    uint32_t hq = 0, hkv = 0, ffn = 0, ffn_off = 0, vocab = 0, vocab_off = 0;
+    void* nccl = nullptr;                 // communicator of the TP group
+    float* partial = nullptr;             // [max_batch][d_model] row-parallel partial sums (all-reduced in place)
+    unsigned char* tp_pair = nullptr;     // [max_batch] (value, index) of this rank's best logit
+    unsigned char* tp_pairs = nullptr;    // [tp_size][max_batch] gathered
 
     // weight arena (execution order, 256-byte aligned slabs)
     uint8_t* arena = nullptr;
@@ -86,7 +94,7 @@ bool role_is_vector(int role) {
            role == VB_ROLE_BK || role == VB_ROLE_BV;
 }
 
-// expected [rows][cols] and storage format of a role
+// [rows][cols] of this rank's shard of a role, and its storage format
 bool role_shape(const vb_ctx* c, int role, uint32_t* rows, uint32_t* cols, int32_t* fmt) {
     const vb_model_desc& d = c->d;
     const int32_t wf = (int32_t)d.weight_fmt;
@@ -98,13 +106,42 @@ bool role_shape(const vb_ctx* c, int role, uint32_t* rows, uint32_t* cols, int32
     case VB_ROLE_WQ: *rows = c->qdim; *cols = d.d_model; *fmt = wf; return true;
     case VB_ROLE_WK: case VB_ROLE_WV: *rows = c->kvdim; *cols = d.d_model; *fmt = wf; return true;
     case VB_ROLE_WO: *rows = d.d_model; *cols = c->qdim; *fmt = wf; return true;
-    case VB_ROLE_WGATE: case VB_ROLE_WUP: *rows = d.ffn_dim; *cols = d.d_model; *fmt = wf; return true;
-    case VB_ROLE_WDOWN: *rows = d.d_model; *cols = d.ffn_dim; *fmt = wf; return true;
-    case VB_ROLE_LM_HEAD: *rows = d.vocab; *cols = d.d_model; *fmt = (int32_t)d.head_fmt; return true;
+    case VB_ROLE_WGATE: case VB_ROLE_WUP: *rows = c->ffn; *cols = d.d_model; *fmt = wf; return true;
+    case VB_ROLE_WDOWN: *rows = d.d_model; *cols = c->ffn; *fmt = wf; return true;
+    case VB_ROLE_LM_HEAD: *rows = c->vocab; *cols = d.d_model; *fmt = (int32_t)d.head_fmt; return true;
     case VB_ROLE_BQ: *rows = 1; *cols = c->qdim; *fmt = vf; return d.qkv_bias != 0;
     case VB_ROLE_BK: case VB_ROLE_BV: *rows = 1; *cols = c->kvdim; *fmt = vf; return d.qkv_bias != 0;
     default: return false;
     }
+}
+
+// Where this rank's shard sits inside the full tensor [*full_rows][*full_cols]: rows [r0, r0+rows), cols [c0, c0+cols).
+void role_slice(const vb_ctx* c, int role, uint32_t* full_rows, uint32_t* full_cols, uint32_t* r0, uint32_t* c0) {
+    const vb_model_desc& d = c->d;
+    const uint32_t tp = d.tp_size ? d.tp_size : 1, r = d.tp_rank;
+    uint32_t rows = 0, cols = 0; int32_t fmt;
+    role_shape(c, role, &rows, &cols, &fmt);
+    *full_rows = rows; *full_cols = cols; *r0 = 0; *c0 = 0;
+    switch (role) {
+    case VB_ROLE_WQ: *full_rows = rows * tp; *r0 = r * rows; break;
+    case VB_ROLE_WK: case VB_ROLE_WV: *full_rows = rows * tp; *r0 = r * rows; break;
+    case VB_ROLE_BQ: case VB_ROLE_BK: case VB_ROLE_BV: *full_cols = cols * tp; *c0 = r * cols; break;
+    case VB_ROLE_WO: *full_cols = cols * tp; *c0 = r * cols; break;
+    case VB_ROLE_WGATE: case VB_ROLE_WUP: *full_rows = d.ffn_dim; *r0 = c->ffn_off; break;
+    case VB_ROLE_WDOWN: *full_cols = d.ffn_dim; *c0 = c->ffn_off; break;
+    case VB_ROLE_LM_HEAD: *full_rows = d.vocab; *r0 = c->vocab_off; break;
+    default: break;
+    }
+}
+
+// Tied head: lm_head reads (this rank's rows of) the embedding table.
+void set_tied_head(vb_ctx* c) {
+    Tensor& h = c->tensor(VB_ROLE_LM_HEAD, 0);
+    h = c->tensor(VB_ROLE_EMBED, 0);
+    h.m.rows = c->vocab;
+    h.m.data = (const unsigned char*)h.m.data + wmat_data_bytes(h.m.fmt, c->vocab_off, h.m.cols);
+    if (h.m.scales) h.m.scales = (const unsigned char*)h.m.scales + wmat_scale_bytes(h.m.fmt, c->vocab_off, h.m.cols);
+    h.m.tiled = h.m.tiled_scales = h.m.v3 = nullptr;
 }
 
 // Lay the arena out in execution order.  Wq|Wk|Wv (and their scales) are adjacent so that the fused QKV
@@ -115,40 +152,50 @@ int32_t plan_arena(vb_ctx* c) {
     struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales, v3; bool has_tiled; };
     std::vector<Slot> slots;
     std::vector<uint64_t> swiglu_off, swiglu_v3_off;
+    const bool lean = (c->d.flags & VB_FLAG_LEAN_WEIGHTS) != 0;
     auto add_group = [&](std::initializer_list<int> roles, int layer) {
-        // data of all members first (contiguous rows), then their scales (contiguous too)
         std::vector<Slot> g;
+        bool tile_all = true;
         for (int role : roles) {
             uint32_t rows, cols; int32_t fmt;
             if (!role_shape(c, role, &rows, &cols, &fmt)) continue;
             Tensor& t = c->tensor(role, layer);
             t.m.fmt = fmt; t.m.rows = rows; t.m.cols = cols;
-            g.push_back({role, layer, off, 0, 0, 0, 0, false});
-            off += wmat_data_bytes(fmt, rows, cols);
+            g.push_back({role, layer, ~0ULL, ~0ULL, 0, 0, ~0ULL, false});
+            if (fmt != VB_FMT_Q4G32 || !tile_q4_supported(rows, cols)) tile_all = false;
         }
-        off = align256(off);
-        bool tile_all = !g.empty();
-        for (Slot& s : g) {
-            Tensor& t = c->tensor(s.role, s.layer);
-            s.scales = off;
-            off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
-            if (t.m.fmt != VB_FMT_Q4G32 || !tile_q4_supported(t.m.rows, t.m.cols)) tile_all = false;
-        }
-        off = align256(off);
-        if (tile_all) {
-            // tile-major copies for the tuned kernel, members adjacent again (fused QKV = one tiled matrix)
+        if (g.empty()) return;
+        const bool lean_group = lean && tile_all;  // only the integer tensor-core layout is kept
+        auto packed_bytes = [&](const Slot& s) {
+            const Tensor& t = c->tensor(s.role, s.layer);
+            return wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+        };
+        if (!lean_group) {
+            // canonical layout: data of all members first (contiguous rows), then their scales (contiguous too)
             for (Slot& s : g) {
-                Tensor& t = c->tensor(s.role, s.layer);
-                s.has_tiled = true; s.tiled = off; s.tiled_scales = off;  // scales are interleaved block by block
-                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+                const Tensor& t = c->tensor(s.role, s.layer);
+                s.data = off;
+                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols);
             }
             off = align256(off);
-            for (Slot& s : g) {  // and the integer tensor-core layout
-                Tensor& t = c->tensor(s.role, s.layer);
-                s.v3 = off;
-                off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
+            for (Slot& s : g) {
+                const Tensor& t = c->tensor(s.role, s.layer);
+                s.scales = off;
+                off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
             }
             off = align256(off);
+        }
+        if (tile_all) {
+            if (!lean_group) {
+                // tile-major copies for the fp16 tensor-core kernel, members adjacent again (fused QKV = one tiled matrix)
+                for (Slot& s : g) { s.has_tiled = true; s.tiled = off; s.tiled_scales = off; off += packed_bytes(s); }
+                off = align256(off);
+            }
+            const bool swiglu_only = lean_group && (g[0].role == VB_ROLE_WGATE || g[0].role == VB_ROLE_WUP);
+            if (!swiglu_only) {
+                for (Slot& s : g) { s.v3 = off; off += packed_bytes(s); }  // the integer tensor-core layout
+                off = align256(off);
+            }
         }
         for (Slot& s : g) slots.push_back(s);
     };
@@ -164,9 +211,13 @@ int32_t plan_arena(vb_ctx* c) {
             // gate and up interleaved 8 rows by 8 rows for the fused SwiGLU kernel
             Tensor& tg = c->tensor(VB_ROLE_WGATE, (int)l);
             if (tg.m.fmt == VB_FMT_Q4G32 && tg.m.rows % 8 == 0 && tg.m.cols % 128 == 0) {
-                swiglu_off.push_back(off);
-                off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
-                off = align256(off);
+                if (lean && tile_q4_supported(tg.m.rows, tg.m.cols)) {
+                    swiglu_off.push_back(~0ULL);
+                } else {
+                    swiglu_off.push_back(off);
+                    off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
+                    off = align256(off);
+                }
                 swiglu_v3_off.push_back(off);
                 off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
                 off = align256(off);
@@ -185,19 +236,16 @@ int32_t plan_arena(vb_ctx* c) {
     if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(weight arena)", __FILE__, __LINE__); return VB_ERR_OOM; }
     for (const Slot& s : slots) {
         Tensor& t = c->tensor(s.role, s.layer);
-        t.m.data = c->arena + s.data;
-        t.m.scales = wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols) ? c->arena + s.scales : nullptr;
-        if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; t.m.v3 = c->arena + s.v3; }
+        t.m.data = s.data != ~0ULL ? c->arena + s.data : nullptr;
+        t.m.scales = (s.scales != ~0ULL && wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols)) ? c->arena + s.scales : nullptr;
+        if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; }
+        if (s.v3 != ~0ULL) t.m.v3 = c->arena + s.v3;
     }
-    for (uint32_t l = 0; l < c->d.n_layers; ++l)
-        if (swiglu_off[l] != ~0ULL) {
-            c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
-            c->tensor(VB_ROLE_WGATE, (int)l).m.v3_swiglu = c->arena + swiglu_v3_off[l];
-        }
-    if (c->d.tied_lm_head) {
-        Tensor& h = c->tensor(VB_ROLE_LM_HEAD, 0);
-        h = c->tensor(VB_ROLE_EMBED, 0);
+    for (uint32_t l = 0; l < c->d.n_layers; ++l) {
+        if (swiglu_off[l] != ~0ULL) c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
+        if (swiglu_v3_off[l] != ~0ULL) c->tensor(VB_ROLE_WGATE, (int)l).m.v3_swiglu = c->arena + swiglu_v3_off[l];
     }
+    if (c->d.tied_lm_head) set_tied_head(c);
     return VB_OK;
 }
 
@@ -250,6 +298,15 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     Tensor& emb = c->tensor(VB_ROLE_EMBED, 0);
     // the first kernel of a step must not overlap the previous step's tail: launched without PDL
     VB_TRY(embed(lcfg(c, false), c->hidden, nullptr, state, emb.m.data, emb.m.scales, emb.m.fmt, d.d_model, d.vocab, B));
+    // Tensor parallel: O and down are row-parallel.  Rank 0 adds its partial product onto the residual stream,
+    // the other ranks overwrite theirs with the bare partial; one in-place sum all-reduce then leaves the new
+    // residual stream, bit-identical, on every rank (no separate residual-add pass).
+    const bool tp = c->nccl != nullptr;
+    const int row_epi = (!tp || d.tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
+    auto exchange = [&]() -> cudaError_t {
+        if (!tp) return cudaSuccess;
+        return nccl_allreduce_sum_f32(c->nccl, c->hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
+    };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
         const int L = (int)l;
         // RMSNorm + fused QKV projection
@@ -267,25 +324,26 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
             bq = c->tensor(VB_ROLE_BQ, L).m.data; bk = c->tensor(VB_ROLE_BK, L).m.data; bv = c->tensor(VB_ROLE_BV, L).m.data;
             bf = c->tensor(VB_ROLE_BQ, L).m.fmt;
         }
-        const bool fused_append = (d.n_q_heads / d.n_kv_heads) <= 8 && c->fuse_append;
+        const bool fused_append = (c->hq / c->hkv) <= 8 && c->fuse_append;
         if (!fused_append)
             VB_TRY(bias_rope_kv_append(lcfg(c, true), c->q, c->qkv, state, bq, bk, bv, bf, kv_layer, c->block_table_dev,
-                                       c->max_blocks, d.n_q_heads, d.n_kv_heads, d.head_dim, d.kv_block_tokens, d.rope_theta, B));
+                                       c->max_blocks, c->hq, c->hkv, d.head_dim, d.kv_block_tokens, d.rope_theta, B));
         // split-K attention over the paged cache (with the bias + RoPE + KV append fused in when possible)
         AttnArgs a;
         a.out = c->attn_out; a.q = c->q; a.k = kv_layer; a.kv_fp16 = 1;
         if (fused_append) { a.qkv_raw = c->qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; }
         a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
-        a.state = state; a.Hq = d.n_q_heads; a.Hkv = d.n_kv_heads; a.D = d.head_dim; a.batch = B;
+        a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         a.trace = next_trace();
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
-        o.state = state; o.batch = B; o.x = c->attn_out; o.dst = c->hidden; o.epilogue = EPI_RESIDUAL;
+        o.state = state; o.batch = B; o.x = c->attn_out; o.dst = c->hidden; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
         o.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
+        VB_TRY(exchange());
         // RMSNorm + gate/up + SiLU*up
         GemvArgs gu;
         gu.state = state; gu.batch = B; gu.x = c->hidden; gu.dst = c->act; gu.epilogue = EPI_SWIGLU;
@@ -295,10 +353,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
         // down projection + residual
         GemvArgs dn;
-        dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = c->hidden; dn.epilogue = EPI_RESIDUAL;
+        dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = c->hidden; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
         dn.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
+        VB_TRY(exchange());
     }
     if (with_head) {
         GemvArgs h;
@@ -307,7 +366,14 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
         h.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
-        VB_TRY(argmax(lcfg(c, true), nullptr, c->logits, d.vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
+        if (!tp) {
+            VB_TRY(argmax(lcfg(c, true), nullptr, c->logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
+        } else {
+            // vocab-parallel head: best (value, global index) per rank, gathered, same tie rule over the ranks
+            VB_TRY(argmax_shard(lcfg(c, true), c->tp_pair, c->logits, c->vocab, c->vocab_off, B, c->cand_v, c->cand_i, state));
+            if (nccl_allgather_bytes(c->nccl, c->tp_pair, c->tp_pairs, (size_t)B * 8, c->stream) != VB_OK) return cudaErrorUnknown;
+            VB_TRY(argmax_pairs(lcfg(c, false), c->tp_pairs, d.tp_size, B, state, c->ring_dev, RING_SLOTS));
+        }
     }
 #undef VB_TRY
     c->trace_n = tn;
@@ -318,6 +384,7 @@ int32_t check_ready(vb_ctx* c, const char* who) {
     if (!c) { set_error("%s: null context", who); return VB_ERR_INVALID; }
     const char* missing = nullptr;
     if (!all_loaded(c, &missing)) { set_error("%s: tensor '%s' has not been loaded", who, missing); return VB_ERR_STATE; }
+    if (c->d.tp_size > 1 && !c->nccl) { set_error("%s: tensor-parallel context without a communicator (call vb_tp_init)", who); return VB_ERR_STATE; }
     return VB_OK;
 }
 
@@ -344,7 +411,19 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     VB_REQUIRE(!d.tied_lm_head || d.head_fmt == d.embed_fmt, "vb_create: tied lm_head needs head_fmt == embed_fmt");
     VB_REQUIRE((uint64_t)d.ffn_dim * 4 <= 200 * 1024 && (uint64_t)d.d_model * 4 <= 200 * 1024, "vb_create: width exceeds the staging limit");
     if (d.attn_kind != VB_ATTN_GQA) { set_error("vb_create: attn_kind %u is served by vb_op_mla_absorbed only", d.attn_kind); return VB_ERR_UNSUPPORTED; }
-    if (d.tp_size > 1) { set_error("vb_create: tensor parallel contexts are not available in this build"); return VB_ERR_UNSUPPORTED; }
+    VB_REQUIRE((d.flags & ~VB_FLAG_LEAN_WEIGHTS) == 0, "vb_create: unknown flags 0x%x", d.flags);
+    VB_REQUIRE(!(d.flags & VB_FLAG_LEAN_WEIGHTS) || d.max_batch == 1, "vb_create: VB_FLAG_LEAN_WEIGHTS serves max_batch == 1 only");
+    const uint32_t tp = d.tp_size ? d.tp_size : 1;
+    VB_REQUIRE(tp <= 64 && d.tp_rank < tp, "vb_create: tp_rank=%u / tp_size=%u", d.tp_rank, tp);
+    if (tp > 1) {
+        VB_REQUIRE(d.n_kv_heads % tp == 0 && d.n_q_heads % tp == 0, "vb_create: heads (%u q, %u kv) not divisible by tp_size=%u",
+                   d.n_q_heads, d.n_kv_heads, tp);
+        VB_REQUIRE(d.ffn_dim % 128 == 0 && d.ffn_dim / 128 >= tp, "vb_create: tensor parallel needs ffn_dim in whole 128-column blocks");
+        VB_REQUIRE(d.vocab % (16 * tp) == 0, "vb_create: vocab=%u not divisible by 16*tp_size", d.vocab);
+        VB_REQUIRE(fmt_shape_ok((int32_t)d.weight_fmt, d.n_q_heads / tp * d.head_dim), "vb_create: per-rank attention width breaks the quantization group");
+        // per-row scales of a column slice would differ from the whole row's: int8 per-channel stays single-GPU
+        if (d.weight_fmt == VB_FMT_I8PC) { set_error("vb_create: VB_FMT_I8PC weights cannot be sharded (per-row scales)"); return VB_ERR_UNSUPPORTED; }
+    }
 
     VB_CUDA(cudaSetDevice(device));
     VB_CUDA(kernels_init());
@@ -352,9 +431,20 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     if (!c) { set_error("vb_create: out of host memory"); return VB_ERR_OOM; }
     c->d = d;
     c->device = device;
-    c->qdim = d.n_q_heads * d.head_dim;
-    c->kvdim = d.n_kv_heads * d.head_dim;
+    c->hq = d.n_q_heads / tp;
+    c->hkv = d.n_kv_heads / tp;
+    c->qdim = c->hq * d.head_dim;
+    c->kvdim = c->hkv * d.head_dim;
     c->qkv_rows = c->qdim + 2 * c->kvdim;
+    {
+        // FFN columns in whole 128-column blocks, the first (blocks % tp) ranks take one more: quantization
+        // groups (32 columns) never straddle ranks, so every shard dequantizes to the same values as TP-1
+        const uint32_t nb = tp > 1 ? d.ffn_dim / 128 : 0, per = tp > 1 ? nb / tp : 0, extra = tp > 1 ? nb % tp : 0;
+        c->ffn = tp > 1 ? 128 * (per + (d.tp_rank < extra ? 1 : 0)) : d.ffn_dim;
+        c->ffn_off = tp > 1 ? 128 * (per * d.tp_rank + (d.tp_rank < extra ? d.tp_rank : extra)) : 0;
+        c->vocab = d.vocab / tp;
+        c->vocab_off = c->vocab * d.tp_rank;
+    }
     c->max_blocks = (d.max_seq_len + d.kv_block_tokens - 1) / d.kv_block_tokens;
     c->n_blocks = d.kv_blocks_total ? d.kv_blocks_total : d.max_batch * c->max_blocks;
     c->n_splits = attn_pick_splits(d.max_seq_len);
@@ -368,7 +458,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     VB_CREATE_CUDA(cudaEventCreate(&c->ev0));
     VB_CREATE_CUDA(cudaEventCreate(&c->ev1));
     VB_CREATE_TRY(plan_arena(c));
-    c->kv_layer_elems = (uint64_t)c->n_blocks * 2 * d.n_kv_heads * d.kv_block_tokens * d.head_dim;
+    c->kv_layer_elems = (uint64_t)c->n_blocks * 2 * c->hkv * d.kv_block_tokens * d.head_dim;
     VB_CREATE_TRY(dev_alloc(&c->kv_pool, c->kv_layer_elems * d.n_layers));
     VB_CREATE_CUDA(cudaMemsetAsync(c->kv_pool, 0, c->kv_layer_elems * d.n_layers * sizeof(__half), c->stream));
     VB_CREATE_TRY(dev_alloc(&c->block_table_dev, (uint64_t)d.max_batch * c->max_blocks));
@@ -390,12 +480,17 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     VB_CREATE_TRY(dev_alloc(&c->qkv, B * c->qkv_rows));
     VB_CREATE_TRY(dev_alloc(&c->q, B * c->qdim));
     VB_CREATE_TRY(dev_alloc(&c->attn_out, B * c->qdim));
-    VB_CREATE_TRY(dev_alloc(&c->act, B * d.ffn_dim));
-    VB_CREATE_TRY(dev_alloc(&c->logits, B * d.vocab));
-    VB_CREATE_TRY(dev_alloc(&c->attn_scratch, attn_scratch_floats(d.n_q_heads, d.head_dim, d.max_batch, c->n_splits)));
-    VB_CREATE_CUDA(cudaMemsetAsync(c->attn_scratch, 0, attn_scratch_floats(d.n_q_heads, d.head_dim, d.max_batch, c->n_splits) * 4, c->stream));
-    VB_CREATE_TRY(dev_alloc(&c->cand_v, B * argmax_chunks(d.vocab)));
-    VB_CREATE_TRY(dev_alloc(&c->cand_i, B * argmax_chunks(d.vocab)));
+    VB_CREATE_TRY(dev_alloc(&c->act, B * c->ffn));
+    VB_CREATE_TRY(dev_alloc(&c->logits, B * c->vocab));
+    if (tp > 1) {
+        VB_CREATE_TRY(dev_alloc(&c->partial, B * d.d_model));
+        VB_CREATE_TRY(dev_alloc(&c->tp_pair, B * 8));
+        VB_CREATE_TRY(dev_alloc(&c->tp_pairs, B * 8 * tp));
+    }
+    VB_CREATE_TRY(dev_alloc(&c->attn_scratch, attn_scratch_floats(c->hq, d.head_dim, d.max_batch, c->n_splits)));
+    VB_CREATE_CUDA(cudaMemsetAsync(c->attn_scratch, 0, attn_scratch_floats(c->hq, d.head_dim, d.max_batch, c->n_splits) * 4, c->stream));
+    VB_CREATE_TRY(dev_alloc(&c->cand_v, B * argmax_chunks(c->vocab)));
+    VB_CREATE_TRY(dev_alloc(&c->cand_i, B * argmax_chunks(c->vocab)));
     {
         // RoPE frequencies exactly as the reference computes them on the host (src/runtime.rs:758)
         std::vector<float> f(d.head_dim / 2);
@@ -417,8 +512,9 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
     if (c->graph) cudaGraphDestroy(c->graph);
+    if (c->nccl) nccl_comm_destroy(c->nccl);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
-                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace};
+                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -428,7 +524,15 @@ int32_t vb_destroy(vb_ctx* c) {
     return VB_OK;
 }
 
-static int32_t load_common(vb_ctx* c, int32_t role, int32_t layer, uint64_t rows, uint64_t cols, Tensor** out, const char* who) {
+// What a loader was handed: the whole tensor (every rank passes the same checkpoint tensor and keeps its own
+// rectangle) or, when `whole` is false, exactly this rank's shard.
+struct LoadView {
+    Tensor* t = nullptr;
+    bool whole = false;
+    uint32_t full_rows = 0, full_cols = 0, r0 = 0, c0 = 0;
+};
+
+static int32_t load_common(vb_ctx* c, int32_t role, int32_t layer, uint64_t rows, uint64_t cols, LoadView* out, const char* who) {
     VB_REQUIRE(c != nullptr, "%s: null context", who);
     VB_REQUIRE(role >= 0 && role <= VB_ROLE_BV, "%s: role %d is not an engine tensor", who, role);
     if (role_is_global(role)) layer = 0;
@@ -436,26 +540,49 @@ static int32_t load_common(vb_ctx* c, int32_t role, int32_t layer, uint64_t rows
     uint32_t er, ec; int32_t fmt;
     VB_REQUIRE(role_shape(c, role, &er, &ec, &fmt), "%s: role %d is not part of this model", who, role);
     VB_REQUIRE(!(role == VB_ROLE_LM_HEAD && c->d.tied_lm_head), "%s: lm_head is tied to the embedding table", who);
-    VB_REQUIRE(rows * cols == (uint64_t)er * ec && (rows == er || role_is_vector(role)), "%s: role %d expects [%u][%u], got [%llu][%llu]",
-               who, role, er, ec, (unsigned long long)rows, (unsigned long long)cols);
-    *out = &c->tensor(role, layer);
+    role_slice(c, role, &out->full_rows, &out->full_cols, &out->r0, &out->c0);
+    const bool vec = role_is_vector(role);
+    const bool is_shard = rows * cols == (uint64_t)er * ec && (rows == er || vec);
+    const bool is_whole = rows * cols == (uint64_t)out->full_rows * out->full_cols && (rows == out->full_rows || vec);
+    VB_REQUIRE(is_shard || is_whole, "%s: role %d expects [%u][%u] (whole tensor) or [%u][%u] (this rank's shard), got [%llu][%llu]",
+               who, role, out->full_rows, out->full_cols, er, ec, (unsigned long long)rows, (unsigned long long)cols);
+    out->whole = is_whole && (out->full_rows != er || out->full_cols != ec);
+    out->t = &c->tensor(role, layer);
     VB_CUDA(cudaSetDevice(c->device));
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     return VB_OK;
 }
 
-static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer) {
-    if (!t->m.tiled) return VB_OK;
+// Canonical (row-major packed) storage of a tensor while it is being loaded: its place in the arena, or for a
+// lean context a temporary that lives until the tile-major copy has been made.
+struct Canon {
+    void* data = nullptr;
+    void* scales = nullptr;
+    void* tmp = nullptr;
+    ~Canon() { if (tmp) cudaFree(tmp); }
+};
+
+static int32_t canon_begin(Tensor* t, Canon* cn) {
+    const uint64_t db = wmat_data_bytes(t->m.fmt, t->m.rows, t->m.cols), sb = wmat_scale_bytes(t->m.fmt, t->m.rows, t->m.cols);
+    if (t->m.data) { cn->data = const_cast<void*>(t->m.data); cn->scales = const_cast<void*>(t->m.scales); return VB_OK; }
+    cudaError_t e = cudaMalloc(&cn->tmp, align256(db) + sb + 256);
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(staging)", __FILE__, __LINE__); return VB_ERR_OOM; }
+    cn->data = cn->tmp;
+    cn->scales = sb ? (unsigned char*)cn->tmp + align256(db) : nullptr;
+    return VB_OK;
+}
+
+static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer, const Canon& cn) {
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
-    VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), t->m.data, t->m.scales, t->m.rows, t->m.cols));
-    VB_CUDA(tile_q4_v3(lc, const_cast<void*>(t->m.v3), t->m.data, t->m.scales, t->m.rows, t->m.cols));
+    if (t->m.tiled) VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), cn.data, cn.scales, t->m.rows, t->m.cols));
+    if (t->m.v3) VB_CUDA(tile_q4_v3(lc, const_cast<void*>(t->m.v3), cn.data, cn.scales, t->m.rows, t->m.cols));
     if (role == VB_ROLE_WGATE || role == VB_ROLE_WUP) {
         const int which = role == VB_ROLE_WUP ? 1 : 0;
         const void* il = c->tensor(VB_ROLE_WGATE, layer).m.tiled_swiglu;
-        if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), t->m.data, t->m.scales, t->m.rows, t->m.cols, which));
+        if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), cn.data, cn.scales, t->m.rows, t->m.cols, which));
         const void* il3 = c->tensor(VB_ROLE_WGATE, layer).m.v3_swiglu;
-        if (il3) VB_CUDA(tile_q4_v3_swiglu(lc, const_cast<void*>(il3), t->m.data, t->m.scales, t->m.rows, t->m.cols, which));
+        if (il3) VB_CUDA(tile_q4_v3_swiglu(lc, const_cast<void*>(il3), cn.data, cn.scales, t->m.rows, t->m.cols, which));
     }
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;
@@ -463,78 +590,97 @@ static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer) {
 
 static void mark_loaded(vb_ctx* c, int32_t role, Tensor* t) {
     t->loaded = true;
-    if (role == VB_ROLE_EMBED && c->d.tied_lm_head) c->tensor(VB_ROLE_LM_HEAD, 0) = *t;  // tied: the head reads the table
+    if (role == VB_ROLE_EMBED && c->d.tied_lm_head) set_tied_head(c);  // tied: the head reads the table
 }
 
 int32_t vb_load_tensor(vb_ctx* c, int32_t role, int32_t layer, const void* src, int32_t src_fmt, int32_t src_loc,
                        uint64_t rows, uint64_t cols) {
-    Tensor* t = nullptr;
-    int32_t rc = load_common(c, role, layer, rows, cols, &t, "vb_load_tensor");
+    LoadView lv;
+    int32_t rc = load_common(c, role, layer, rows, cols, &lv, "vb_load_tensor");
     if (rc != VB_OK) return rc;
+    Tensor* t = lv.t;
     VB_REQUIRE(src != nullptr, "vb_load_tensor: null source");
     VB_REQUIRE(src_fmt == VB_FMT_F32 || src_fmt == VB_FMT_F16 || src_fmt == VB_FMT_BF16, "vb_load_tensor: source format %d", src_fmt);
     VB_REQUIRE(src_loc == VB_LOC_HOST || src_loc == VB_LOC_DEVICE, "vb_load_tensor: source location %d", src_loc);
-    const uint64_t n = rows * cols;
-    const uint64_t src_bytes = n * (src_fmt == VB_FMT_F32 ? 4 : 2);
-    // stage: raw source on the device, then fp32, then the storage format
+    const uint64_t es = src_fmt == VB_FMT_F32 ? 4 : 2;
+    const uint64_t n = (uint64_t)t->m.rows * t->m.cols;  // elements this rank keeps
+    // stage: this rank's rectangle of the raw source on the device, then fp32, then the storage format
     void* raw = nullptr;
     float* f32 = nullptr;
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
     cudaError_t e = cudaSuccess;
     const void* dev_src = src;
-    if (src_loc == VB_LOC_HOST) {
-        if ((e = cudaMalloc(&raw, src_bytes)) != cudaSuccess) { cuda_fail(e, "cudaMalloc(staging)", __FILE__, __LINE__); return VB_ERR_OOM; }
-        e = cudaMemcpyAsync(raw, src, src_bytes, cudaMemcpyHostToDevice, c->stream);
+    Canon cn;
+    if ((rc = canon_begin(t, &cn)) != VB_OK) return rc;
+    if (src_loc == VB_LOC_HOST || lv.whole) {
+        if ((e = cudaMalloc(&raw, n * es)) != cudaSuccess) { cuda_fail(e, "cudaMalloc(staging)", __FILE__, __LINE__); return VB_ERR_OOM; }
+        const cudaMemcpyKind kind = src_loc == VB_LOC_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
+        if (lv.whole) {
+            const char* base = (const char*)src + ((uint64_t)lv.r0 * lv.full_cols + lv.c0) * es;
+            e = cudaMemcpy2DAsync(raw, (size_t)t->m.cols * es, base, (size_t)lv.full_cols * es, (size_t)t->m.cols * es, t->m.rows, kind, c->stream);
+        } else {
+            e = cudaMemcpyAsync(raw, src, n * es, kind, c->stream);
+        }
         dev_src = raw;
     }
     if (e == cudaSuccess && src_fmt != VB_FMT_F32) {
-        if ((e = cudaMalloc((void**)&f32, n * 4)) == cudaSuccess) e = dequantize(lc, f32, dev_src, nullptr, src_fmt, rows, cols);
+        if ((e = cudaMalloc((void**)&f32, n * 4)) == cudaSuccess) e = dequantize(lc, f32, dev_src, nullptr, src_fmt, t->m.rows, t->m.cols);
         dev_src = f32;
     }
-    if (e == cudaSuccess) e = quantize(lc, const_cast<void*>(t->m.data), const_cast<void*>(t->m.scales), (const float*)dev_src, t->m.fmt, t->m.rows, t->m.cols);
+    if (e == cudaSuccess) e = quantize(lc, cn.data, cn.scales, (const float*)dev_src, t->m.fmt, t->m.rows, t->m.cols);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     if (raw) cudaFree(raw);
     if (f32) cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor", __FILE__, __LINE__);
-    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
 
 int32_t vb_load_tensor_packed(vb_ctx* c, int32_t role, int32_t layer, const void* data, const void* scales, int32_t src_loc,
                               uint64_t rows, uint64_t cols) {
-    Tensor* t = nullptr;
-    int32_t rc = load_common(c, role, layer, rows, cols, &t, "vb_load_tensor_packed");
+    LoadView lv;
+    int32_t rc = load_common(c, role, layer, rows, cols, &lv, "vb_load_tensor_packed");
     if (rc != VB_OK) return rc;
+    Tensor* t = lv.t;
+    if (lv.whole) { set_error("vb_load_tensor_packed: a sharded context takes pre-quantized tensors shard by shard"); return VB_ERR_UNSUPPORTED; }
     const uint64_t db = wmat_data_bytes(t->m.fmt, t->m.rows, t->m.cols), sb = wmat_scale_bytes(t->m.fmt, t->m.rows, t->m.cols);
     VB_REQUIRE(data != nullptr && (sb == 0 || scales != nullptr), "vb_load_tensor_packed: null data/scales");
     const cudaMemcpyKind kind = (src_loc == VB_LOC_HOST) ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice;
-    VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.data), data, db, kind, c->stream));
-    if (sb) VB_CUDA(cudaMemcpyAsync(const_cast<void*>(t->m.scales), scales, sb, kind, c->stream));
+    Canon cn;
+    if ((rc = canon_begin(t, &cn)) != VB_OK) return rc;
+    VB_CUDA(cudaMemcpyAsync(cn.data, data, db, kind, c->stream));
+    if (sb) VB_CUDA(cudaMemcpyAsync(cn.scales, scales, sb, kind, c->stream));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
 
 int32_t vb_load_tensor_synthetic(vb_ctx* c, int32_t role, int32_t layer, uint64_t seed, uint64_t stream_id, float mean,
                                  float std, uint64_t rows, uint64_t cols) {
-    Tensor* t = nullptr;
-    int32_t rc = load_common(c, role, layer, rows, cols, &t, "vb_load_tensor_synthetic");
+    LoadView lv;
+    int32_t rc = load_common(c, role, layer, rows, cols, &lv, "vb_load_tensor_synthetic");
     if (rc != VB_OK) return rc;
-    const uint64_t n = rows * cols;
+    Tensor* t = lv.t;
+    // the generator is indexed by position in the WHOLE tensor, so a shard holds the values TP-1 holds there
+    VB_REQUIRE(lv.whole || (lv.full_rows == t->m.rows && lv.full_cols == t->m.cols), "vb_load_tensor_synthetic: pass the whole tensor's shape");
+    const uint64_t n = (uint64_t)t->m.rows * t->m.cols;
     float* f32 = nullptr;
+    Canon cn;
+    if ((rc = canon_begin(t, &cn)) != VB_OK) return rc;
     cudaError_t e = cudaMalloc((void**)&f32, n * 4);
     if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(staging)", __FILE__, __LINE__); return VB_ERR_OOM; }
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
-    e = fill_normal(lc, f32, n, seed, stream_id, mean, std);
-    if (e == cudaSuccess) e = quantize(lc, const_cast<void*>(t->m.data), const_cast<void*>(t->m.scales), f32, t->m.fmt, t->m.rows, t->m.cols);
+    e = lv.whole ? fill_normal_slice(lc, f32, t->m.rows, t->m.cols, lv.full_cols, lv.r0, lv.c0, seed, stream_id, mean, std)
+                 : fill_normal(lc, f32, n, seed, stream_id, mean, std);
+    if (e == cudaSuccess) e = quantize(lc, cn.data, cn.scales, f32, t->m.fmt, t->m.rows, t->m.cols);
     if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
     cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor_synthetic", __FILE__, __LINE__);
-    if ((rc = finish_load(c, t, role, layer)) != VB_OK) return rc;
+    if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
     mark_loaded(c, role, t);
     return VB_OK;
 }
@@ -546,6 +692,7 @@ int32_t vb_export_tensor(vb_ctx* c, int32_t role, int32_t layer, void* data, uin
     VB_REQUIRE(layer >= 0 && (uint32_t)layer < c->d.n_layers, "vb_export_tensor: layer %d out of range", layer);
     Tensor& t = c->tensor(role, layer);
     if (!t.loaded) { set_error("vb_export_tensor: tensor not loaded"); return VB_ERR_STATE; }
+    if (!t.m.data) { set_error("vb_export_tensor: a lean context keeps no canonical copy of this matrix"); return VB_ERR_STATE; }
     const uint64_t db = wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols), sb = wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
     VB_REQUIRE(data && data_bytes == db, "vb_export_tensor: data buffer is %llu bytes, tensor has %llu", (unsigned long long)data_bytes, (unsigned long long)db);
     VB_REQUIRE(sb == 0 || (scales && scales_bytes == sb), "vb_export_tensor: scale buffer is %llu bytes, tensor has %llu", (unsigned long long)scales_bytes, (unsigned long long)sb);
@@ -729,10 +876,11 @@ int32_t vb_read_tokens(vb_ctx* c, int32_t slot, uint32_t first_pos, uint32_t n, 
 int32_t vb_read_logits(vb_ctx* c, int32_t slot, float* out, uint64_t n_floats) {
     VB_REQUIRE(c && out, "vb_read_logits: null argument");
     VB_REQUIRE(slot >= 0 && (uint32_t)slot < c->d.max_batch, "vb_read_logits: slot %d out of range", slot);
-    VB_REQUIRE(n_floats == c->d.vocab, "vb_read_logits: buffer holds %llu floats, vocab is %u", (unsigned long long)n_floats, c->d.vocab);
+    // a tensor-parallel rank holds the logits of its own vocabulary rows [rank*vocab/tp, (rank+1)*vocab/tp)
+    VB_REQUIRE(n_floats == c->vocab, "vb_read_logits: buffer holds %llu floats, this context has %u logits", (unsigned long long)n_floats, c->vocab);
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaStreamSynchronize(c->stream));
-    VB_CUDA(cudaMemcpy(out, c->logits + (size_t)slot * c->d.vocab, (size_t)c->d.vocab * 4, cudaMemcpyDeviceToHost));
+    VB_CUDA(cudaMemcpy(out, c->logits + (size_t)slot * c->vocab, (size_t)c->vocab * 4, cudaMemcpyDeviceToHost));
     return VB_OK;
 }
 
@@ -827,14 +975,17 @@ int32_t vb_trace_read(vb_ctx* c, uint64_t* out, uint32_t max_records, uint32_t* 
 }
 
 int32_t vb_tp_unique_id(void* id128) {
-    (void)id128;
-    set_error("vb_tp_unique_id: tensor parallel contexts are not available in this build");
-    return VB_ERR_UNSUPPORTED;
+    VB_REQUIRE(id128 != nullptr, "vb_tp_unique_id: null argument");
+    return nccl_unique_id((NcclUniqueId*)id128);
 }
 int32_t vb_tp_init(vb_ctx* c, const void* id128) {
-    (void)c; (void)id128;
-    set_error("vb_tp_init: tensor parallel contexts are not available in this build");
-    return VB_ERR_UNSUPPORTED;
+    VB_REQUIRE(c && id128, "vb_tp_init: null argument");
+    VB_REQUIRE(c->d.tp_size > 1, "vb_tp_init: the context was created with tp_size <= 1");
+    VB_REQUIRE(c->nccl == nullptr, "vb_tp_init: communicator already initialised");
+    VB_CUDA(cudaSetDevice(c->device));
+    NcclUniqueId id;
+    memcpy(&id, id128, sizeof(id));
+    return nccl_comm_init(&c->nccl, (int)c->d.tp_size, &id, (int)c->d.tp_rank);
 }
 
 }  // extern "C"

@@ -142,6 +142,7 @@ cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path) {
         e = gemv_fast(lc, a, &handled);
         if (handled || e != cudaSuccess) return e;
     }
+    if (!a.w.data) return cudaErrorInvalidValue;  // a lean context holds no canonical copy for the exact kernels
     switch (a.w.fmt) {
     case VB_FMT_F32: return launch_exact<VB_FMT_F32>(lc, a);
     case VB_FMT_F16: return launch_exact<VB_FMT_F16>(lc, a);

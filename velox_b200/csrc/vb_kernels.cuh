@@ -13,6 +13,8 @@ cudaError_t attn_init();
 
 // vb_basic.cu
 cudaError_t fill_normal(const LaunchCfg& lc, float* dst, uint64_t n, uint64_t seed, uint64_t stream_id, float mean, float std);
+cudaError_t fill_normal_slice(const LaunchCfg& lc, float* dst, uint64_t rows, uint64_t cols, uint64_t full_cols, uint64_t r0,
+                              uint64_t c0, uint64_t seed, uint64_t stream_id, float mean, float std);
 cudaError_t quantize(const LaunchCfg& lc, void* data, void* scales, const float* src, int32_t fmt, uint64_t rows, uint64_t cols);
 cudaError_t dequantize(const LaunchCfg& lc, float* dst, const void* data, const void* scales, int32_t fmt, uint64_t rows, uint64_t cols);
 cudaError_t embed(const LaunchCfg& lc, float* dst, const uint32_t* tokens, const SeqState* state, const void* table,
@@ -26,6 +28,10 @@ cudaError_t bias_rope_kv_append(const LaunchCfg& lc, float* q_out, const float* 
 cudaError_t argmax(const LaunchCfg& lc, uint32_t* out_token, const float* logits, uint32_t n, uint32_t batch, float* cand_v,
                    uint32_t* cand_i, SeqState* state, uint32_t* ring, uint32_t ring_slots);
 uint32_t argmax_chunks(uint32_t n);
+cudaError_t argmax_shard(const LaunchCfg& lc, void* pair_out, const float* logits, uint32_t n, uint32_t idx_offset, uint32_t batch,
+                         float* cand_v, uint32_t* cand_i, SeqState* state);
+cudaError_t argmax_pairs(const LaunchCfg& lc, const void* pairs, uint32_t n_ranks, uint32_t batch, SeqState* state, uint32_t* ring,
+                         uint32_t ring_slots);
 
 // vb_gemv.cu
 // Epilogues of the matrix-vector kernels.

@@ -57,8 +57,11 @@ class DeviceBuffer:
 
 class Engine:
     def __init__(self, spec: ModelSpec, max_seq_len: int, max_batch: int = 1, device: int = 0,
-                 kv_blocks_total: int = 0):
+                 kv_blocks_total: int = 0, tp_rank: int = 0, tp_size: int = 1, lean_weights: bool = False):
+        """With tp_size > 1 this context is one rank of a tensor-parallel group: it keeps 1/tp of the heads,
+        FFN columns and vocabulary rows (see modelspec.shard_plan) and needs ``tp_init`` before the first step."""
         self.spec = spec
+        self.tp_rank, self.tp_size = int(tp_rank), int(tp_size)
         self.max_seq_len = int(max_seq_len)
         self.max_batch = int(max_batch)
         d = L.ModelDesc()
@@ -70,11 +73,24 @@ class Engine:
         d.rms_eps, d.rope_theta = spec.rms_eps, spec.rope_theta
         d.qkv_bias, d.tied_lm_head = int(spec.qkv_bias), int(spec.tied_lm_head)
         d.kv_block_tokens, d.kv_blocks_total = 16, int(kv_blocks_total)
-        d.attn_kind, d.tp_rank, d.tp_size = L.ATTN_GQA, 0, 1
+        d.attn_kind, d.tp_rank, d.tp_size = L.ATTN_GQA, self.tp_rank, self.tp_size
+        d.flags = L.FLAG_LEAN_WEIGHTS if lean_weights else 0
         self._lib = L.load()
         h = C.c_void_p()
         L.check(self._lib.vb_create(C.byref(d), device, C.byref(h)))
         self.h = h
+
+    # ---- tensor parallel ----------------------------------------------------------------------
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """128-byte communicator id; rank 0 makes it and the host passes it to the other ranks."""
+        buf = C.create_string_buffer(128)
+        L.check(L.load().vb_tp_unique_id(buf))
+        return buf.raw
+
+    def tp_init(self, unique_id: bytes):
+        assert len(unique_id) == 128
+        L.check(self._lib.vb_tp_init(self.h, C.create_string_buffer(unique_id, 128)))
 
     # ---- weights ----------------------------------------------------------------------------
     def load_tensor(self, role: int, layer: int, w: np.ndarray):
@@ -163,7 +179,8 @@ class Engine:
         return out
 
     def logits(self, slot: int = 0) -> np.ndarray:
-        out = np.empty(self.spec.vocab, dtype=np.float32)
+        """Logits of this context's vocabulary rows (all of them unless tensor parallel)."""
+        out = np.empty(self.spec.vocab // self.tp_size, dtype=np.float32)
         L.check(self._lib.vb_read_logits(self.h, slot, _ptr(out), out.size))
         return out
 

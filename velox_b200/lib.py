@@ -19,6 +19,7 @@ FMT_F32, FMT_F16, FMT_BF16, FMT_Q4G32, FMT_Q4G64REF, FMT_I8PC = range(6)
  ROLE_MLA_WABSQ, ROLE_MLA_WABSO) = range(19)
 LOC_HOST, LOC_DEVICE = 0, 1
 ATTN_GQA, ATTN_MLA_REF = 0, 1
+FLAG_LEAN_WEIGHTS = 1
 
 
 class VeloxError(RuntimeError):
@@ -34,8 +35,8 @@ class ModelDesc(C.Structure):
                                       "max_seq_len", "max_batch")]
         + [("rms_eps", C.c_float), ("rope_theta", C.c_float)]
         + [(n, C.c_uint32) for n in ("weight_fmt", "head_fmt", "embed_fmt", "qkv_bias", "tied_lm_head", "kv_block_tokens",
-                                      "kv_blocks_total", "attn_kind", "mla_latent", "tp_rank", "tp_size")]
-        + [("reserved", C.c_uint32 * 8)]
+                                      "kv_blocks_total", "attn_kind", "mla_latent", "tp_rank", "tp_size", "flags")]
+        + [("reserved", C.c_uint32 * 7)]
     )
 
 

@@ -75,6 +75,41 @@ class ModelSpec:
         return self.weight_fmt
 
 
+@dataclass(frozen=True)
+class ShardPlan:
+    """One tensor-parallel rank's part of a model: heads, FFN columns [ffn_off, ffn_off+ffn), vocabulary rows."""
+    q_heads: int
+    kv_heads: int
+    head_off: int      # first query head
+    kv_head_off: int   # first KV head
+    ffn: int
+    ffn_off: int
+    vocab: int
+    vocab_off: int
+
+
+def shard_plan(spec: ModelSpec, tp_rank: int, tp_size: int) -> ShardPlan:
+    """The split vb_create applies: heads and vocabulary evenly; FFN columns in whole 128-column blocks with
+    the first (blocks % tp) ranks taking one block more, so that 32-column quantization groups never straddle
+    two ranks and every shard dequantizes to the values the unsharded tensor holds there."""
+    if not (0 <= tp_rank < tp_size):
+        raise ValueError(f"tp_rank {tp_rank} outside [0, {tp_size})")
+    if tp_size == 1:
+        return ShardPlan(spec.n_q_heads, spec.n_kv_heads, 0, 0, spec.ffn_dim, 0, spec.vocab, 0)
+    if spec.n_q_heads % tp_size or spec.n_kv_heads % tp_size:
+        raise ValueError("heads not divisible by tp_size")
+    if spec.ffn_dim % 128 or spec.ffn_dim // 128 < tp_size:
+        raise ValueError("ffn_dim must be whole 128-column blocks, at least one per rank")
+    if spec.vocab % (16 * tp_size):
+        raise ValueError("vocab not divisible by 16 * tp_size")
+    nb = spec.ffn_dim // 128
+    per, extra = divmod(nb, tp_size)
+    ffn = 128 * (per + (1 if tp_rank < extra else 0))
+    ffn_off = 128 * (per * tp_rank + min(tp_rank, extra))
+    hq, hkv, v = spec.n_q_heads // tp_size, spec.n_kv_heads // tp_size, spec.vocab // tp_size
+    return ShardPlan(hq, hkv, hq * tp_rank, hkv * tp_rank, ffn, ffn_off, v, v * tp_rank)
+
+
 def stream_of(role: int, layer: int) -> int:
     return role * 4096 + layer
 

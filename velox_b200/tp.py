@@ -1,0 +1,60 @@
+"""Tensor-parallel host plumbing: one process per GPU, the ranks of one model found through torch.distributed.
+
+The reference states the intent only (examples/qwen2_72b.vlx:4, examples/nanbeige_33b.vlx:27-45:
+column-parallel QKV / gate / up, row-parallel O / down, one sum all-reduce after each); the exchange itself
+runs inside libvelox_b200 on its own NCCL communicator, captured into the decode graph.  torch.distributed
+is used for two host-side things only: passing rank 0's 128-byte communicator id to the other ranks and
+barriers / max-over-ranks of timings.
+"""
+from __future__ import annotations
+
+import os
+
+from .engine import Engine
+from .modelspec import ModelSpec
+
+
+def env_rank():
+    """(rank, world_size, local_rank) from the launcher's environment (torchrun); (0, 1, 0) when absent."""
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def init_process_group(backend: str | None = None):
+    """Join the launcher's group (rendezvous on 127.0.0.1 unless the launcher said otherwise)."""
+    import torch
+    import torch.distributed as dist
+    if dist.is_initialized():
+        return
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29531")
+    rank, world, local = env_rank()
+    if backend is None:
+        backend = "nccl" if torch.cuda.is_available() else "gloo"
+    if backend == "nccl":
+        torch.cuda.set_device(local)
+    dist.init_process_group(backend=backend, rank=rank, world_size=world)
+
+
+def share_unique_id(make_id) -> bytes:
+    """Rank 0 calls ``make_id()``; every rank returns the same 128 bytes."""
+    import torch.distributed as dist
+    box = [make_id() if dist.get_rank() == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    assert isinstance(box[0], bytes) and len(box[0]) == 128
+    return box[0]
+
+
+def create_tp_engine(spec: ModelSpec, max_seq_len: int, max_batch: int = 1, kv_blocks_total: int = 0,
+                     lean_weights: bool = False) -> Engine:
+    """This process's rank of a tensor-parallel engine over all ranks of the default group (device = LOCAL_RANK)."""
+    import torch.distributed as dist
+    init_process_group()
+    rank, world, local = dist.get_rank(), dist.get_world_size(), env_rank()[2]
+    if world == 1:
+        return Engine(spec, max_seq_len=max_seq_len, max_batch=max_batch, device=local, kv_blocks_total=kv_blocks_total,
+                      lean_weights=lean_weights)
+    eng = Engine(spec, max_seq_len=max_seq_len, max_batch=max_batch, device=local, kv_blocks_total=kv_blocks_total,
+                 tp_rank=rank, tp_size=world, lean_weights=lean_weights)
+    eng.tp_init(share_unique_id(Engine.tp_unique_id))
+    return eng
