@@ -179,6 +179,8 @@ def main():
     ap.add_argument("--gemv-path", type=int, default=1)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="tensor-parallel workloads: NVLink peer pushes inside the library's own kernels, or NCCL")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -204,9 +206,9 @@ def main():
     tp = is_tp(args.workload)
     if tp and world > 1:
         # one model over all ranks; the 72B shape only fits one GPU with the single-layout arena
-        from velox_b200.tp import share_unique_id
+        from velox_b200.tp import connect
         eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, tp_rank=rank, tp_size=world, lean_weights=True)
-        eng.tp_init(share_unique_id(Engine.tp_unique_id))
+        connect(eng, args.tp_exchange)
     else:
         eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp)
     eng.set_option("gemv_path", args.gemv_path)
@@ -215,6 +217,8 @@ def main():
     t0 = time.perf_counter()
     eng.load_synthetic(SEED)
     load_s = time.perf_counter() - t0
+    if dist is not None:
+        dist.barrier()  # ranks of one model step together
 
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import helpers as H
@@ -283,7 +287,8 @@ def main():
         "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len,
                    "weights": "int4 g32 + fp16 scales, fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
                    "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),
-                   "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1},
+                   "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1,
+                   "tp_exchange": (args.tp_exchange if tp and world > 1 else None)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),

@@ -168,6 +168,14 @@ int32_t vb_set_option(vb_ctx* ctx, const char* name, int64_t value);
 int32_t vb_tp_unique_id(void* id128);
 int32_t vb_tp_init(vb_ctx* ctx, const void* id128);
 
+/* Low-latency exchange over NVLink peer mappings (2..8 ranks on one node), used instead of NCCL once open:
+ * each rank exports a 64-byte handle of its receive region, the host gathers all tp_size handles (rank
+ * order) and every rank opens them.  The ranks' hosts must meet at a barrier after opening and before the
+ * first step, and again before vb_destroy.  A rank that waits ~10 s for a peer gives up: the next
+ * vb_sync / vb_read_tokens returns VB_ERR_TIMEOUT.  Option "tp_p2p" = 0 switches back to NCCL. */
+int32_t vb_tp_p2p_export(vb_ctx* ctx, void* handle64);
+int32_t vb_tp_p2p_open(vb_ctx* ctx, const void* handles, uint32_t n_handles);
+
 /* ---- per-op entry points: one per fused IR instruction (src/ir.rs:52-300) ------------------- */
 /* All pointers are device pointers; activations are fp32 as in the reference. */
 /* Embed (src/runners/tinystories_smollm.cu:87): dst[b][d] = table[tokens[b]][:]. */

@@ -39,11 +39,12 @@ def _run_group(tmp_path, world: int, extra=()):
     return [np.load(os.path.join(str(tmp_path), f"rank{k}.npz")) for k in range(world)]
 
 
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
 @pytest.mark.parametrize("graph", [True, False])
-def test_tp2_matches_unsharded_and_checker(tmp_path, graph):
+def test_tp2_matches_unsharded_and_checker(tmp_path, graph, exchange):
     if _gpu_count() < 2:
         pytest.skip("needs 2 GPUs")
-    ranks = _run_group(tmp_path, 2, () if graph else ("--no-graph",))
+    ranks = _run_group(tmp_path, 2, ("--exchange", exchange) + (() if graph else ("--no-graph",)))
     prompt = prompt_tokens(TP_SPEC, SEED, N_PROMPT)
     # unsharded engine on this process's GPU
     eng = build_engine(TP_SPEC, SEED, N_PROMPT + N_NEW + 8)
@@ -62,7 +63,7 @@ def test_tp2_matches_unsharded_and_checker(tmp_path, graph):
     o_tokens = orc.generate_greedy(prompt, N_NEW)
     assert np.array_equal(ranks[0]["tokens"][:32], o_tokens[:32])
     if np.array_equal(ranks[0]["tokens"], o_tokens):
-        assert np.max(np.abs(tp_logits - orc.logits())) <= 2e-2
+        assert np.max(np.abs(tp_logits - orc.logits)) <= 2e-2
     # stored shards are the unsharded tensors' rectangles, bit for bit
     hd, d = TP_SPEC.head_dim, TP_SPEC.d_model
     for k, r in enumerate(ranks):

@@ -30,11 +30,13 @@ def main():
     ap.add_argument("--prompt", type=int, default=24)
     ap.add_argument("--new", type=int, default=40)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
     a = ap.parse_args()
     rank, world, _ = env_rank()
     import torch.distributed as dist
-    eng = create_tp_engine(TP_SPEC, max_seq_len=a.prompt + a.new + 8)
+    eng = create_tp_engine(TP_SPEC, max_seq_len=a.prompt + a.new + 8, exchange=a.exchange)
     eng.load_synthetic(a.seed)
+    dist.barrier()  # the exchange waits ~10 s at most for a peer: start the steps together
     prompt = np.load(os.path.join(a.out, "prompt.npy"))
     toks = eng.generate_greedy(prompt, a.new, use_graph=not a.no_graph)
     logits = eng.logits()

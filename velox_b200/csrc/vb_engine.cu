@@ -45,6 +45,9 @@ struct vb_ctx {
     // query/KV heads, FFN columns [ffn_off, ffn_off + ffn) in whole 128-column blocks, vocabulary rows
     uint32_t hq = 0, hkv = 0, ffn = 0, ffn_off = 0, vocab = 0, vocab_off = 0;
     void* nccl = nullptr;                 // communicator of the TP group
+    TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
+    bool links_open = false, use_links = true;
+    uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
     float* partial = nullptr;             // [max_batch][d_model] row-parallel partial sums (all-reduced in place)
     unsigned char* tp_pair = nullptr;     // [max_batch] (value, index) of this rank's best logit
     unsigned char* tp_pairs = nullptr;    // [tp_size][max_batch] gathered
@@ -301,10 +304,17 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     // Tensor parallel: O and down are row-parallel.  Rank 0 adds its partial product onto the residual stream,
     // the other ranks overwrite theirs with the bare partial; one in-place sum all-reduce then leaves the new
     // residual stream, bit-identical, on every rank (no separate residual-add pass).
-    const bool tp = c->nccl != nullptr;
-    const int row_epi = (!tp || d.tp_rank == 0) ? EPI_RESIDUAL : EPI_STORE;
-    auto exchange = [&]() -> cudaError_t {
+    // With NVLink peer mappings every rank instead stores its partial, pushes it to all peers and each rank
+    // sums the parts onto its residual stream in rank order (tp_reduce): one small kernel, no fence, no flag.
+    const bool tp = d.tp_size > 1;
+    const bool p2p = tp && c->links_open && c->use_links;
+    const uint32_t n_sites = 2 * d.n_layers + 1;
+    const int row_epi = (!tp || (!p2p && d.tp_rank == 0)) ? EPI_RESIDUAL : EPI_STORE;
+    float* row_dst = p2p ? c->partial : c->hidden;
+    if (p2p) VB_TRY(tp_epoch_advance(lcfg(c, false), c->links));
+    auto exchange = [&](uint32_t site) -> cudaError_t {
         if (!tp) return cudaSuccess;
+        if (p2p) return tp_reduce(lcfg(c, true), c->links, c->hidden, c->partial, B * d.d_model, site, n_sites, c->err_word);
         return nccl_allreduce_sum_f32(c->nccl, c->hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
@@ -339,11 +349,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
-        o.state = state; o.batch = B; o.x = c->attn_out; o.dst = c->hidden; o.epilogue = row_epi;
+        o.state = state; o.batch = B; o.x = c->attn_out; o.dst = row_dst; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
         o.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
-        VB_TRY(exchange());
+        VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
         GemvArgs gu;
         gu.state = state; gu.batch = B; gu.x = c->hidden; gu.dst = c->act; gu.epilogue = EPI_SWIGLU;
@@ -353,11 +363,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
         // down projection + residual
         GemvArgs dn;
-        dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = c->hidden; dn.epilogue = row_epi;
+        dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = row_dst; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
         dn.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
-        VB_TRY(exchange());
+        VB_TRY(exchange(2 * l + 1));
     }
     if (with_head) {
         GemvArgs h;
@@ -371,8 +381,12 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         } else {
             // vocab-parallel head: best (value, global index) per rank, gathered, same tie rule over the ranks
             VB_TRY(argmax_shard(lcfg(c, true), c->tp_pair, c->logits, c->vocab, c->vocab_off, B, c->cand_v, c->cand_i, state));
-            if (nccl_allgather_bytes(c->nccl, c->tp_pair, c->tp_pairs, (size_t)B * 8, c->stream) != VB_OK) return cudaErrorUnknown;
-            VB_TRY(argmax_pairs(lcfg(c, false), c->tp_pairs, d.tp_size, B, state, c->ring_dev, RING_SLOTS));
+            if (p2p) {
+                VB_TRY(tp_argmax(lcfg(c, true), c->links, c->tp_pair, B, 2 * d.n_layers, n_sites, state, c->ring_dev, RING_SLOTS, c->err_word));
+            } else {
+                if (nccl_allgather_bytes(c->nccl, c->tp_pair, c->tp_pairs, (size_t)B * 8, c->stream) != VB_OK) return cudaErrorUnknown;
+                VB_TRY(argmax_pairs(lcfg(c, false), c->tp_pairs, d.tp_size, B, state, c->ring_dev, RING_SLOTS));
+            }
         }
     }
 #undef VB_TRY
@@ -384,7 +398,10 @@ int32_t check_ready(vb_ctx* c, const char* who) {
     if (!c) { set_error("%s: null context", who); return VB_ERR_INVALID; }
     const char* missing = nullptr;
     if (!all_loaded(c, &missing)) { set_error("%s: tensor '%s' has not been loaded", who, missing); return VB_ERR_STATE; }
-    if (c->d.tp_size > 1 && !c->nccl) { set_error("%s: tensor-parallel context without a communicator (call vb_tp_init)", who); return VB_ERR_STATE; }
+    if (c->d.tp_size > 1 && !c->nccl && !(c->links_open && c->use_links)) {
+        set_error("%s: tensor-parallel context without a communicator (call vb_tp_init or vb_tp_p2p_open)", who);
+        return VB_ERR_STATE;
+    }
     return VB_OK;
 }
 
@@ -499,6 +516,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
         VB_CREATE_CUDA(cudaMemcpyAsync(c->rope_inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice, c->stream));
         VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
     }
+    VB_CREATE_CUDA(fast_error_word(&c->err_word));
     VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
 #undef VB_CREATE_TRY
 #undef VB_CREATE_CUDA
@@ -513,6 +531,9 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
     if (c->graph) cudaGraphDestroy(c->graph);
     if (c->nccl) nccl_comm_destroy(c->nccl);
+    for (uint32_t r = 0; r < 8; ++r)
+        if (c->links.base[r] && r != c->links.rank) cudaIpcCloseMemHandle(c->links.base[r]);
+    if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs};
     for (void* p : frees) if (p) cudaFree(p);
@@ -952,6 +973,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         }
         return VB_OK;
     }
+    if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
     set_error("vb_set_option: unknown option '%s'", name);
@@ -986,6 +1008,52 @@ int32_t vb_tp_init(vb_ctx* c, const void* id128) {
     NcclUniqueId id;
     memcpy(&id, id128, sizeof(id));
     return nccl_comm_init(&c->nccl, (int)c->d.tp_size, &id, (int)c->d.tp_rank);
+}
+
+
+// ---- NVLink peer mappings for the tensor-parallel exchange ---------------------------------------------
+int32_t vb_tp_p2p_export(vb_ctx* c, void* handle64) {
+    VB_REQUIRE(c && handle64, "vb_tp_p2p_export: null argument");
+    VB_REQUIRE(c->d.tp_size > 1 && c->d.tp_size <= 8, "vb_tp_p2p_export: peer exchange serves 2..8 ranks (tp_size=%u)", c->d.tp_size);
+    VB_CUDA(cudaSetDevice(c->device));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    if (!c->links.base[c->d.tp_rank]) {
+        tp_links_layout(&c->links, c->d.tp_rank, c->d.tp_size, c->d.max_batch * c->d.d_model, c->d.max_batch);
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, c->links.bytes);
+        if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc(peer region)", __FILE__, __LINE__); return VB_ERR_OOM; }
+        VB_CUDA(cudaMemset(p, 0, c->links.bytes));
+        VB_CUDA(cudaDeviceSynchronize());
+        c->links.base[c->d.tp_rank] = (unsigned char*)p;
+    }
+    cudaIpcMemHandle_t h;
+    VB_CUDA(cudaIpcGetMemHandle(&h, c->links.base[c->d.tp_rank]));
+    memcpy(handle64, &h, 64);
+    return VB_OK;
+}
+
+int32_t vb_tp_p2p_open(vb_ctx* c, const void* handles, uint32_t n_handles) {
+    VB_REQUIRE(c && handles, "vb_tp_p2p_open: null argument");
+    VB_REQUIRE(n_handles == c->d.tp_size, "vb_tp_p2p_open: %u handles for tp_size=%u", n_handles, c->d.tp_size);
+    VB_REQUIRE(c->links.base[c->d.tp_rank] != nullptr, "vb_tp_p2p_open: call vb_tp_p2p_export first");
+    VB_REQUIRE(!c->links_open, "vb_tp_p2p_open: already open");
+    VB_CUDA(cudaSetDevice(c->device));
+    for (uint32_t r = 0; r < c->d.tp_size; ++r) {
+        if (r == c->d.tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const unsigned char*)handles + 64 * (size_t)r, 64);
+        void* p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            set_error("vb_tp_p2p_open: cannot map rank %u's region (%s); use the NCCL exchange (vb_tp_init)", r, cudaGetErrorString(e));
+            return VB_ERR_COMM;
+        }
+        c->links.base[r] = (unsigned char*)p;
+    }
+    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
+    c->links_open = true;
+    return VB_OK;
 }
 
 }  // extern "C"

@@ -28,6 +28,19 @@ cudaError_t bias_rope_kv_append(const LaunchCfg& lc, float* q_out, const float* 
 cudaError_t argmax(const LaunchCfg& lc, uint32_t* out_token, const float* logits, uint32_t n, uint32_t batch, float* cand_v,
                    uint32_t* cand_i, SeqState* state, uint32_t* ring, uint32_t ring_slots);
 uint32_t argmax_chunks(uint32_t n);
+
+// Peer-mapped receive regions of a tensor-parallel group (vb_tp.cu): base[r] is rank r's region as mapped here.
+struct TpLinks {
+    unsigned char* base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    uint32_t rank = 0, size = 1, max_batch = 0, max_pairs = 0;
+    uint64_t epoch_off = 0, pair_off = 0, data_off = 0, bytes = 0;
+};
+void tp_links_layout(TpLinks* l, uint32_t rank, uint32_t size, uint32_t max_elems, uint32_t max_batch);
+cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l);
+cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, const float* partial, uint32_t n, uint32_t site,
+                      uint32_t n_sites, uint32_t* err);
+cudaError_t tp_argmax(const LaunchCfg& lc, const TpLinks& l, const void* pairs, uint32_t batch, uint32_t site, uint32_t n_sites,
+                      SeqState* state, uint32_t* ring, uint32_t ring_slots, uint32_t* err);
 cudaError_t argmax_shard(const LaunchCfg& lc, void* pair_out, const float* logits, uint32_t n, uint32_t idx_offset, uint32_t batch,
                          float* cand_v, uint32_t* cand_i, SeqState* state);
 cudaError_t argmax_pairs(const LaunchCfg& lc, const void* pairs, uint32_t n_ranks, uint32_t batch, SeqState* state, uint32_t* ring,

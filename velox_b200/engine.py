@@ -92,6 +92,17 @@ class Engine:
         assert len(unique_id) == 128
         L.check(self._lib.vb_tp_init(self.h, C.create_string_buffer(unique_id, 128)))
 
+    def tp_p2p_export(self) -> bytes:
+        """64-byte handle of this rank's NVLink receive region (to be gathered from all ranks, in rank order)."""
+        buf = C.create_string_buffer(64)
+        L.check(self._lib.vb_tp_p2p_export(self.h, buf))
+        return buf.raw
+
+    def tp_p2p_open(self, handles):
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.tp_size
+        L.check(self._lib.vb_tp_p2p_open(self.h, C.create_string_buffer(blob, len(blob)), self.tp_size))
+
     # ---- weights ----------------------------------------------------------------------------
     def load_tensor(self, role: int, layer: int, w: np.ndarray):
         """fp32/fp16 [rows][cols] host array; converted to the storage format on the GPU."""

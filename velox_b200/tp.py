@@ -45,8 +45,22 @@ def share_unique_id(make_id) -> bytes:
     return box[0]
 
 
+def connect(eng: Engine, exchange: str = "p2p"):
+    """Gives a sharded engine its exchange: "nccl" (communicator inside the library) or "p2p" (NVLink peer
+    mappings, 2..8 ranks; the NCCL communicator is still created so that option "tp_p2p"=0 can fall back)."""
+    import torch.distributed as dist
+    if exchange not in ("p2p", "nccl"):
+        raise ValueError(exchange)
+    eng.tp_init(share_unique_id(Engine.tp_unique_id))
+    if exchange == "p2p":
+        handles = [None] * dist.get_world_size()
+        dist.all_gather_object(handles, eng.tp_p2p_export())
+        eng.tp_p2p_open(handles)
+    dist.barrier()  # every region is mapped (and zeroed) before anyone steps
+
+
 def create_tp_engine(spec: ModelSpec, max_seq_len: int, max_batch: int = 1, kv_blocks_total: int = 0,
-                     lean_weights: bool = False) -> Engine:
+                     lean_weights: bool = False, exchange: str = "p2p") -> Engine:
     """This process's rank of a tensor-parallel engine over all ranks of the default group (device = LOCAL_RANK)."""
     import torch.distributed as dist
     init_process_group()
@@ -56,5 +70,5 @@ def create_tp_engine(spec: ModelSpec, max_seq_len: int, max_batch: int = 1, kv_b
                       lean_weights=lean_weights)
     eng = Engine(spec, max_seq_len=max_seq_len, max_batch=max_batch, device=local, kv_blocks_total=kv_blocks_total,
                  tp_rank=rank, tp_size=world, lean_weights=lean_weights)
-    eng.tp_init(share_unique_id(Engine.tp_unique_id))
+    connect(eng, exchange)
     return eng
