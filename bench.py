@@ -302,7 +302,11 @@ def main():
         line["cpu_baseline"] = {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
                                 "sample": "2 decode tokens through 2 of %d layers + lm_head on the CPU restatement, "
                                           "extrapolated linearly to full depth" % spec.n_layers}
-    eng.close()
+    if tp and world > 1:
+        from velox_b200.tp import shutdown
+        shutdown(eng)
+    else:
+        eng.close()
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

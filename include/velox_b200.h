@@ -175,6 +175,9 @@ int32_t vb_tp_init(vb_ctx* ctx, const void* id128);
  * vb_sync / vb_read_tokens returns VB_ERR_TIMEOUT.  Option "tp_p2p" = 0 switches back to NCCL. */
 int32_t vb_tp_p2p_export(vb_ctx* ctx, void* handle64);
 int32_t vb_tp_p2p_open(vb_ctx* ctx, const void* handles, uint32_t n_handles);
+/* Unmaps the peers' regions (this rank's own region stays until vb_destroy).  Shut-down order for a group:
+ * every rank closes, the hosts meet at a barrier, then every rank destroys its context. */
+int32_t vb_tp_p2p_close(vb_ctx* ctx);
 
 /* ---- per-op entry points: one per fused IR instruction (src/ir.rs:52-300) ------------------- */
 /* All pointers are device pointers; activations are fp32 as in the reference. */

@@ -16,7 +16,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from velox_b200 import lib as L  # noqa: E402
 from velox_b200.modelspec import ModelSpec, shard_plan  # noqa: E402
-from velox_b200.tp import create_tp_engine, env_rank  # noqa: E402
+from velox_b200.tp import create_tp_engine, env_rank, shutdown  # noqa: E402
 
 TP_SPEC = ModelSpec("tp-tiny-q4", vocab=2048, d_model=512, n_layers=3, n_q_heads=8, n_kv_heads=2, head_dim=64,
                     ffn_dim=640, rms_eps=1e-6, rope_theta=1e6, weight_fmt=L.FMT_Q4G32, head_fmt=L.FMT_Q4G32,
@@ -48,9 +48,7 @@ def main():
     wg, wg_s = eng.export_tensor(L.ROLE_WGATE, 0, plan.ffn, TP_SPEC.d_model)
     np.savez(os.path.join(a.out, f"rank{rank}.npz"), tokens=toks, logits=logits, launches=np.int64(eng.launch_count()),
              wq=wq, wq_s=wq_s, wo=wo, wo_s=wo_s, wd=wd, wd_s=wd_s, wg=wg, wg_s=wg_s)
-    eng.sync()
-    dist.barrier()
-    eng.close()
+    shutdown(eng)
     dist.destroy_process_group()
 
 

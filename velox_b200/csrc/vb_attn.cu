@@ -4,13 +4,14 @@
 // share it and one slice of the context (a whole number of 16-token KV blocks).  The kernel is latency-bound
 // at decode sizes, so it makes as few dependent memory trips as it can: (1) the sequence's position, (2) the
 // slice's block-table entries together with the query heads, (3) per chunk of up to 64 tokens ALL K and V
-// rows at once, cp.async into shared memory, double buffered.  Each of the 4 warps then takes 4 or 8 tokens
+// rows at once, bulk copies (TMA) into two shared-memory buffers, requested before the grid-dependency wait
+// because cached rows do not depend on this step's projections.  Each of the 8 warps then takes 4 or 8 tokens
 // at a time, uses every row for all query heads of the group, reduces the per-lane partial dot products
 // with a transposing butterfly (one value per lane instead of one reduction per value) and keeps an
 // online-softmax state (m, l, acc) per query head.  The splits of one (sequence, head group) form a
-// thread-block cluster: each block leaves its partial in its own shared memory and, after a cluster barrier,
-// every block merges one slice of the head dimension by reading the others' partials through distributed
-// shared memory -- no global round trip, no atomics, a fixed merge order.
+// thread-block cluster: each block pushes slice j of its partial into block j's shared memory (distributed
+// shared memory stores) and, after one cluster barrier, every block merges its slice of the head dimension
+// locally -- no global round trip, no atomics, a fixed merge order.
 // In the engine the kernel also does what the reference runs as separate kernels before attention
 // (fused_rope_kernel and the KV write of fused_qkv, src/runners/tinystories_smollm.cu:189-318): bias, RoPE of
 // q and of the new k at the sequence's position, and the append of K/V to the cache.
@@ -26,14 +27,15 @@
 
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
+#include "vb_tma.cuh"
 
 namespace cg = cooperative_groups;
 
 namespace vb {
 
-constexpr int ATTN_WARPS = 4;
+constexpr int ATTN_WARPS = 8;
 constexpr int ATTN_MAX_SPLITS = 8;  // portable thread-block cluster size
-constexpr int ATTN_MAX_BLOCKS = 1024;  // KV blocks one block's slice may span (16384 tokens)
+constexpr int ATTN_SPEC_BLOCKS = ATTN_WARPS * 32;  // block-table rows up to this long are fetched whole, before the position is known
 
 struct AttnKArgs {
     AttnArgs a;
@@ -42,6 +44,8 @@ struct AttnKArgs {
     uint32_t g_chunks;   // ceil(G / GM), GM = query heads a block handles at once
     uint32_t n_splits;
     size_t kv_batch_stride;  // contiguous: elements between sequences
+    uint32_t inv_freq_n;     // > 0: the rotary frequencies below are valid
+    float inv_freq[256];     // [D/2], in parameter space: no memory trip before the angles can be computed
 };
 
 template <typename KVT, int EPL>
@@ -106,9 +110,6 @@ __device__ __forceinline__ void warp_transpose_reduce(float v[NV], uint32_t lane
     }
 }
 
-__device__ __forceinline__ void attn_cp_async16(uint32_t dst_smem, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
-}
 
 // Shared-memory plan of one block (dynamic): K/V staging for two chunks of CH tokens, the warp-merge buffer.
 template <typename KVT, int EPL, int GM>
@@ -133,22 +134,29 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     __shared__ float q_s[GM][D];
     __shared__ float sc_s[ATTN_WARPS][32];
     __shared__ float part_ml[ATTN_WARPS][GM][2];
-    __shared__ float comb[GM][D + 2];       // this block's partial, read by the whole cluster
-    __shared__ int32_t blk_s[ATTN_MAX_BLOCKS];  // block-table entries of this block's slice
+    __shared__ float gath[GM * (D + 32)];   // partials of all splits for this block's slice of the head dimension
+    __shared__ float rope_cs[D / 2], rope_sn[D / 2];
+    __shared__ __align__(8) unsigned long long kv_bar[2];  // one transaction barrier per staging buffer
+    __shared__ int32_t blk_s[ATTN_SPEC_BLOCKS];             // the sequence's block-table row (short tables only)
     __shared__ __align__(16) KVT new_kv[2][D];  // the appended token's K and V (fused mode)
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     KVT* kv_s = reinterpret_cast<KVT*>(dyn_smem);
     float* part_acc = reinterpret_cast<float*>(dyn_smem + SM::kv_bytes);  // [ATTN_WARPS][GM][D]
 
     trace_mark(a.trace, 0);
-    pdl_wait();
     pdl_launch_dependents();
-    trace_mark(a.trace, 1);
 
+    // ---- before the wait: nothing here depends on this step's projections.  The sequence's position (written
+    // by the previous step's sampler), the block table, the rotary angles and -- the long trip -- the first
+    // chunk of cached K/V rows are all on their way while the QKV product is still finishing.
     const uint32_t b = blockIdx.z, split = blockIdx.y;
     const uint32_t kvh = blockIdx.x / ka.g_chunks, gc = blockIdx.x % ka.g_chunks;
     const uint32_t g0 = gc * GM;
     const uint32_t ng = min((uint32_t)GM, ka.G - g0);
+    // the sequence's whole block-table row is requested together with its position when it is short enough
+    const bool spec_table = a.block_table && a.max_blocks <= (uint32_t)ATTN_SPEC_BLOCKS;
+    int32_t my_blk = 0;
+    if (spec_table && threadIdx.x < a.max_blocks) my_blk = a.block_table[(size_t)b * a.max_blocks + threadIdx.x];
     if (a.state && !a.state[b].active) return;
     const uint32_t seq_len = (a.state ? a.state[b].pos : a.pos) + 1;
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -158,7 +166,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     const uint32_t t_lo = min(seq_len, split * per), t_hi = min(seq_len, t_lo + per);
     const uint32_t pos = seq_len - 1;
     const bool appender = a.qkv_raw && t_lo <= pos && pos < t_hi;
-
+    // every block of the cluster must be running before anyone writes into its shared memory: arrive now,
+    // wait just before the pushes (the barrier's latency hides behind the attention itself)
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.barrier_arrive();
     float m[GM], l[GM], acc[GM][EPL];
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
@@ -167,68 +178,137 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
     }
 
-    // One chunk = tokens [c0, c0+CH) of the slice: every 16-byte piece of its K and V rows is requested at once.
-    auto stage_chunk = [&](uint32_t c0, uint32_t buf) {
+    // Chunk c = tokens [t_lo + c*CH, +CH) of the slice, fetched by bulk copies (TMA) into buffer c & 1 and
+    // announced on that buffer's transaction barrier: in the paged pool one copy moves the 16 cached rows of a
+    // KV block (K or V) for this head, so a 64-token chunk is 8 copies issued by 8 threads -- the block table
+    // entry each needs is read by the issuing thread itself.  The contiguous layout takes one copy per row.
+    // Called by warp 0 only; `rot` rotates the lanes so that two chunks requested back to back use different
+    // lanes (their block-table reads then overlap instead of queueing behind one another).
+    auto stage_chunk = [&](uint32_t c, uint32_t buf, uint32_t rot) {
+        const uint32_t c0 = t_lo + c * CH;
         const uint32_t n_tok = min((uint32_t)CH, t_hi - c0);
         KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
-        for (uint32_t i = threadIdx.x; i < n_tok * 2 * ROW16; i += blockDim.x) {
-            const uint32_t piece = i % ROW16, kv = (i / ROW16) & 1, tok = i / (2 * ROW16);
-            const uint32_t tt = c0 + tok;
-            const KVT* src;
-            if (a.block_table) {
-                const int32_t blk = blk_s[(tt - t_lo) / a.block_tokens];
-                src = reinterpret_cast<const KVT*>(a.k) + (((size_t)blk * 2 + kv) * a.Hkv + kvh) * a.block_tokens * D +
-                      (size_t)(tt % a.block_tokens) * D;
-            } else {
-                const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
-                src = reinterpret_cast<const KVT*>(kv ? a.v : a.k) + off;
+        const uint32_t bar = smem_u32(&kv_bar[buf]);
+        const uint32_t me = (lane + 32 - rot) & 31;
+        if (a.block_table) {
+            const uint32_t nb = (n_tok + a.block_tokens - 1) / a.block_tokens;
+            const uint32_t blk_bytes = a.block_tokens * D * (uint32_t)sizeof(KVT);
+            if (me == 0) mbar_expect_tx(bar, nb * 2 * blk_bytes);
+            for (uint32_t i = me; i < nb * 2; i += 32) {
+                const uint32_t kv = i & 1, j = i >> 1;
+                const uint32_t bi = c0 / a.block_tokens + j;
+                const int32_t blk = spec_table ? blk_s[bi] : a.block_table[(size_t)b * a.max_blocks + bi];
+                const KVT* src = reinterpret_cast<const KVT*>(a.k) + (((size_t)blk * 2 + kv) * a.Hkv + kvh) * a.block_tokens * D;
+                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + (size_t)j * a.block_tokens) * D), src, blk_bytes, bar);
             }
-            attn_cp_async16((uint32_t)__cvta_generic_to_shared(kb + ((size_t)kv * CH + tok) * D) + piece * 16,
-                            reinterpret_cast<const unsigned char*>(src) + piece * 16);
+        } else {
+            const uint32_t row_bytes = D * (uint32_t)sizeof(KVT);
+            if (me == 0) mbar_expect_tx(bar, n_tok * 2 * row_bytes);
+            for (uint32_t i = me; i < n_tok * 2; i += 32) {
+                const uint32_t kv = i & 1, tok = i >> 1;
+                const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)(c0 + tok) * a.Hkv * D + (size_t)kvh * D;
+                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + tok) * D), reinterpret_cast<const KVT*>(kv ? a.v : a.k) + off, row_bytes, bar);
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
-    if (t_lo < t_hi) {
-        // ---- one trip: block-table entries of the slice, the query heads (and, fused, the new token's K/V) ----
-        if (a.block_table) {
-            const uint32_t nblk = (t_hi - t_lo + a.block_tokens - 1) / a.block_tokens;
-            for (uint32_t i = threadIdx.x; i < nblk && i < (uint32_t)ATTN_MAX_BLOCKS; i += blockDim.x)
-                blk_s[i] = a.block_table[(size_t)b * a.max_blocks + t_lo / a.block_tokens + i];
+    const bool has_tokens = t_lo < t_hi;
+    const uint32_t n_ch = has_tokens ? (t_hi - t_lo + CH - 1) / CH : 0;
+    // In fused mode the cached rows are older than this step (the new token's row is patched in from new_kv
+    // below), so they may be fetched now; otherwise the kernel before this one wrote the newest row.
+    const bool early = a.qkv_raw != nullptr;
+    constexpr uint32_t half = D / 2;
+    constexpr int QIT = (GM * (int)half + ATTN_WARPS * 32 - 1) / (ATTN_WARPS * 32);  // (head, pair) items per thread
+    float bq1[QIT], bq2[QIT], bk1 = 0.f, bk2 = 0.f, bv1 = 0.f, bv2 = 0.f;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&kv_bar[0]), 1);
+        mbar_init(smem_u32(&kv_bar[1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (spec_table) {
+        blk_s[threadIdx.x] = my_blk;
+        __syncthreads();
+    }
+    if (warp == 0) {
+        // warp 0: the requests for the first two chunks
+        __syncwarp();
+        if (early) {
+            if (n_ch > 0) stage_chunk(0, 0, 0);
+            if (n_ch > 1) stage_chunk(1, 1, 16);
         }
+    } else if (a.qkv_raw) {
+        // the other warps: rotary angles of this position (one sincos per frequency, shared by all heads)
+        for (uint32_t j = threadIdx.x - 32; j < half; j += (ATTN_WARPS - 1) * 32) {
+            float sn, cs;
+            sincosf((float)pos * (ka.inv_freq_n ? ka.inv_freq[j] : a.rope_inv_freq[j]), &sn, &cs);
+            rope_cs[j] = cs;
+            rope_sn[j] = sn;
+        }
+    }
+    if (a.qkv_raw) {
+        // biases are weights: they can be in registers before the projections exist
+#pragma unroll
+        for (int it = 0; it < QIT; ++it) {
+            const uint32_t i = threadIdx.x + it * ATTN_WARPS * 32, g = i / half, j = i % half;
+            const uint32_t h = kvh * ka.G + g0 + g;
+            const bool on = a.bq && i < GM * half && g < ng;
+            bq1[it] = on ? bias_at(a.bq, a.bias_fmt, h * D + j) : 0.0f;
+            bq2[it] = on ? bias_at(a.bq, a.bias_fmt, h * D + j + half) : 0.0f;
+        }
+        if (appender && threadIdx.x < half) {
+            const uint32_t j = threadIdx.x;
+            if (a.bk) { bk1 = bias_at(a.bk, a.bias_fmt, kvh * D + j); bk2 = bias_at(a.bk, a.bias_fmt, kvh * D + j + half); }
+            if (a.bv) { bv1 = bias_at(a.bv, a.bias_fmt, kvh * D + j); bv2 = bias_at(a.bv, a.bias_fmt, kvh * D + j + half); }
+        }
+    }
+    __syncthreads();
+
+    pdl_wait();
+    trace_mark(a.trace, 1);
+    if (!early && warp == 0) {
+        if (n_ch > 0) stage_chunk(0, 0, 0);
+        if (n_ch > 1) stage_chunk(1, 1, 16);
+    }
+
+    if (has_tokens) {
         if (a.qkv_raw) {
-            // fused bias + RoPE on the raw projections
-            const uint32_t half = D / 2;
+            // fused bias + RoPE on the raw projections: all loads first, then the arithmetic
             const float* raw = a.qkv_raw + (size_t)b * (a.Hq + 2 * a.Hkv) * D;
-            for (uint32_t i = threadIdx.x; i < GM * half; i += blockDim.x) {
-                const uint32_t g = i / half, j = i % half;
-                float r1 = 0.0f, r2 = 0.0f;
-                if (g < ng) {
-                    const uint32_t h = kvh * ka.G + g0 + g;
-                    float x1 = raw[(size_t)h * D + j], x2 = raw[(size_t)h * D + j + half];
-                    if (a.bq) { x1 += bias_at(a.bq, a.bias_fmt, h * D + j); x2 += bias_at(a.bq, a.bias_fmt, h * D + j + half); }
-                    float sn, cs;
-                    sincosf((float)pos * a.rope_inv_freq[j], &sn, &cs);
-                    r1 = x1 * cs - x2 * sn;
-                    r2 = x2 * cs + x1 * sn;
-                }
-                q_s[g][j] = r1;
-                q_s[g][j + half] = r2;
+            float x1[QIT], x2[QIT], k1 = 0.f, k2 = 0.f, v1 = 0.f, v2 = 0.f;
+#pragma unroll
+            for (int it = 0; it < QIT; ++it) {
+                const uint32_t i = threadIdx.x + it * ATTN_WARPS * 32, g = i / half, j = i % half;
+                const uint32_t h = kvh * ka.G + g0 + g;
+                const bool on = i < GM * half && g < ng;
+                x1[it] = on ? raw[(size_t)h * D + j] : 0.0f;
+                x2[it] = on ? raw[(size_t)h * D + j + half] : 0.0f;
             }
-            if (appender) {
+            const bool kv_thread = appender && threadIdx.x < half;
+            if (kv_thread) {
                 const float* kr_raw = raw + (size_t)a.Hq * D + (size_t)kvh * D;
                 const float* vr_raw = raw + (size_t)(a.Hq + a.Hkv) * D + (size_t)kvh * D;
-                for (uint32_t j = threadIdx.x; j < half; j += blockDim.x) {
-                    float x1 = kr_raw[j], x2 = kr_raw[j + half], v1 = vr_raw[j], v2 = vr_raw[j + half];
-                    if (a.bk) { x1 += bias_at(a.bk, a.bias_fmt, kvh * D + j); x2 += bias_at(a.bk, a.bias_fmt, kvh * D + j + half); }
-                    if (a.bv) { v1 += bias_at(a.bv, a.bias_fmt, kvh * D + j); v2 += bias_at(a.bv, a.bias_fmt, kvh * D + j + half); }
-                    float sn, cs;
-                    sincosf((float)pos * a.rope_inv_freq[j], &sn, &cs);
-                    new_kv[0][j] = (KVT)__float2half_rn(x1 * cs - x2 * sn);
-                    new_kv[0][j + half] = (KVT)__float2half_rn(x2 * cs + x1 * sn);
-                    new_kv[1][j] = (KVT)__float2half_rn(v1);
-                    new_kv[1][j + half] = (KVT)__float2half_rn(v2);
+                const uint32_t j = threadIdx.x;
+                k1 = kr_raw[j]; k2 = kr_raw[j + half]; v1 = vr_raw[j]; v2 = vr_raw[j + half];
+            }
+#pragma unroll
+            for (int it = 0; it < QIT; ++it) {
+                const uint32_t i = threadIdx.x + it * ATTN_WARPS * 32, g = i / half, j = i % half;
+                if (i < GM * half) {
+                    const float a1 = x1[it] + bq1[it], a2 = x2[it] + bq2[it];
+                    const float sn = rope_sn[j], cs = rope_cs[j];
+                    const bool on = g < ng;
+                    q_s[g][j] = on ? a1 * cs - a2 * sn : 0.0f;
+                    q_s[g][j + half] = on ? a2 * cs + a1 * sn : 0.0f;
                 }
+            }
+            if (kv_thread) {
+                const uint32_t j = threadIdx.x;
+                const float a1 = k1 + bk1, a2 = k2 + bk2;
+                const float sn = rope_sn[j], cs = rope_cs[j];
+                new_kv[0][j] = (KVT)__float2half_rn(a1 * cs - a2 * sn);
+                new_kv[0][j + half] = (KVT)__float2half_rn(a2 * cs + a1 * sn);
+                new_kv[1][j] = (KVT)__float2half_rn(v1 + bv1);
+                new_kv[1][j + half] = (KVT)__float2half_rn(v2 + bv2);
             }
         } else {
             const float* qb = a.q + (size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0) * D;
@@ -237,7 +317,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         __syncthreads();
         if (appender && gc == 0) {
             // the new token's row goes to the cache (16-byte stores); this block reads it from new_kv below
-            const int32_t blk = blk_s[(pos - t_lo) / a.block_tokens];
+            const int32_t blk = spec_table ? blk_s[pos / a.block_tokens] : a.block_table[(size_t)b * a.max_blocks + pos / a.block_tokens];
             KVT* kd = reinterpret_cast<KVT*>(const_cast<void*>(a.k)) + (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D +
                       (size_t)(pos % a.block_tokens) * D;
             KVT* vd = kd + (size_t)a.Hkv * a.block_tokens * D;
@@ -253,18 +333,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
 #pragma unroll
             for (int e = 0; e < EPL; ++e) qr[g][e] = q_s[g][lane * EPL + e];
 
-        // ---- the slice, CH tokens at a time, double buffered: one memory trip per chunk ----------------------
-        const uint32_t n_ch = (t_hi - t_lo + CH - 1) / CH;
-        stage_chunk(t_lo, 0);
+        // ---- the slice, CH tokens at a time through the two buffers (both were requested above) ----------------
         for (uint32_t c = 0; c < n_ch; ++c) {
             const uint32_t c0 = t_lo + c * CH, buf = c & 1;
-            if (c + 1 < n_ch) {
-                stage_chunk(c0 + CH, buf ^ 1);
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-            } else {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-            }
-            __syncthreads();
+            if (!mbar_wait(smem_u32(&kv_bar[buf]), (c >> 1) & 1) && a.err) atomicOr(a.err, 0x400u);
             KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
             if (appender && c0 <= pos && pos < c0 + CH) {
                 // overwrite the staged copy of the new token's row with the values just computed
@@ -325,11 +397,15 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     }
                 }
             }
-            __syncthreads();  // the buffer is free for the chunk after next
+            __syncthreads();  // every warp is done with the buffer: it takes the chunk after next
+            if (c + 2 < n_ch && warp == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                stage_chunk(c + 2, buf, 0);
+            }
         }
     }
 
-    // ---- merge the 4 warps into this block's partial (m, l, unnormalised acc), kept in shared memory --------
+    // ---- merge the warps into this block's partial (m, l, unnormalised acc) ...
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
         if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
@@ -337,6 +413,14 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
     }
     __syncthreads();
+    // ---- ... and push it to the blocks of the cluster (the splits of one sequence and head group): block j
+    // merges slice j of the head dimension, so every value goes to exactly one block's shared memory.  One
+    // cluster barrier later each block holds all it needs locally: no global round trip, no atomics, a fixed
+    // merge order, and nobody reads remote memory after the barrier (blocks may leave at once).
+    cluster.barrier_wait();
+    const uint32_t n = ka.n_splits;  // == cluster size along y
+    const uint32_t per_d = (D + n - 1) / n;
+    const uint32_t gstride = per_d + 2;  // per (source split, head): M, L, per_d accumulators
     for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) {
         const uint32_t g = i / D, d = i % D;
         float M = -INFINITY;
@@ -350,44 +434,30 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
             L = fmaf(part_ml[w][g][1], f, L);
             A = fmaf(part_acc[((size_t)w * GM + g) * D + d], f, A);
         }
-        comb[g][2 + d] = A;
-        if (d == 0) { comb[g][0] = M; comb[g][1] = L; }
+        if (g < ng) {
+            const uint32_t owner = d / per_d, dd = d - owner * per_d;
+            float* dst = cluster.map_shared_rank(gath, owner) + ((size_t)split * GM + g) * gstride;
+            dst[2 + dd] = A;
+            if (dd == 0) { dst[0] = M; dst[1] = L; }
+        }
     }
-
-    // ---- merge the splits: the blocks of one (sequence, head group) form a thread-block cluster and read each
-    // other's partials through distributed shared memory -- no global round trip, no atomics, fixed order
-    cg::cluster_group cluster = cg::this_cluster();
     cluster.sync();
-    const uint32_t n = ka.n_splits;  // == cluster size along y
-    const uint32_t per_d = (D + n - 1) / n;
     const uint32_t d_lo = split * per_d, d_hi = min((uint32_t)D, d_lo + per_d);
     for (uint32_t i = threadIdx.x; i < ng * per_d; i += blockDim.x) {
-        const uint32_t g = i / per_d, d = d_lo + i % per_d;
+        const uint32_t g = i / per_d, dd = i % per_d, d = d_lo + dd;
         if (d < d_hi) {
-            // all remote reads are issued before any is used (a remote shared-memory load costs hundreds of cycles)
-            float ms[ATTN_MAX_SPLITS], ls[ATTN_MAX_SPLITS], as[ATTN_MAX_SPLITS];
-#pragma unroll
-            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) {
-                const float* rc = cluster.map_shared_rank(&comb[g][0], (uint32_t)r < n ? r : 0);
-                const bool on = (uint32_t)r < n;
-                ms[r] = on ? rc[0] : -INFINITY;
-                ls[r] = on ? rc[1] : 0.0f;
-                as[r] = on ? rc[2 + d] : 0.0f;
-            }
             float M = -INFINITY;
-#pragma unroll
-            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) M = fmaxf(M, ms[r]);
+            for (uint32_t r = 0; r < n; ++r) M = fmaxf(M, gath[((size_t)r * GM + g) * gstride]);
             float L = 0.0f, A = 0.0f;
-#pragma unroll
-            for (int r = 0; r < ATTN_MAX_SPLITS; ++r) {
-                const float f = (ms[r] == -INFINITY) ? 0.0f : __expf(ms[r] - M);
-                L = fmaf(ls[r], f, L);
-                A = fmaf(as[r], f, A);
+            for (uint32_t r = 0; r < n; ++r) {
+                const float* src = gath + ((size_t)r * GM + g) * gstride;
+                const float f = (src[0] == -INFINITY) ? 0.0f : __expf(src[0] - M);
+                L = fmaf(src[1], f, L);
+                A = fmaf(src[2 + dd], f, A);
             }
             a.out[(size_t)b * a.Hq * D + (size_t)(kvh * ka.G + g0 + g) * D + d] = (L > 0.0f) ? (A / L) : 0.0f;
         }
     }
-    cluster.sync();  // nobody leaves while its shared memory may still be read
     trace_exit(a.trace);
 }
 
@@ -482,6 +552,14 @@ cudaError_t attn_init() {
 cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, size_t kv_batch_stride) {
     if (a.batch == 0 || a.Hq == 0) return cudaSuccess;
     if (a.Hkv == 0 || a.Hq % a.Hkv != 0 || a.max_splits == 0 || a.tokens_per_split == 0) return cudaErrorInvalidValue;
+    // bulk copies move 16-byte aligned pieces; a paged chunk holds whole KV blocks
+    if ((reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) return cudaErrorMisalignedAddress;
+    if (a.block_table) {
+        const uint32_t esz = a.kv_fp16 ? 2 : 4;
+        uint32_t ch = 16384 / (a.D * esz);
+        if (ch > 64) ch = 64;
+        if (a.block_tokens == 0 || ch % a.block_tokens != 0) return cudaErrorInvalidValue;
+    }
     AttnKArgs ka;
     ka.a = a;
     ka.scale = (scale != 0.0f) ? scale : 1.0f / sqrtf((float)a.D);
@@ -489,6 +567,11 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
     ka.g_chunks = 1;
     ka.n_splits = a.max_splits;
     ka.kv_batch_stride = kv_batch_stride;
+    ka.inv_freq_n = 0;
+    if (a.rope_inv_freq_host && a.D / 2 <= 256) {
+        ka.inv_freq_n = a.D / 2;
+        for (uint32_t j = 0; j < a.D / 2; ++j) ka.inv_freq[j] = a.rope_inv_freq_host[j];
+    }
     return a.kv_fp16 ? dispatch_split<__half>(lc, ka) : dispatch_split<float>(lc, ka);
 }
 
@@ -505,6 +588,7 @@ extern "C" int32_t vb_op_gqa_attention(float* out, const float* q, const float* 
     VB_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "vb_op_gqa_attention: n_q=%u not a multiple of n_kv=%u", n_q, n_kv);
     VB_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256 || head_dim == 512,
                "vb_op_gqa_attention: head_dim=%u (supported: 32,64,128,256,512)", head_dim);
+    VB_REQUIRE(((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0, "vb_op_gqa_attention: the caches must be 16-byte aligned");
     AttnArgs a;
     a.out = out; a.q = q; a.k = k_cache; a.v = v_cache; a.kv_fp16 = 0;
     a.pos = pos; a.Hq = n_q; a.Hkv = n_kv; a.D = head_dim; a.batch = 1;

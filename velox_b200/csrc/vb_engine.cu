@@ -38,6 +38,7 @@ struct vb_ctx {
     unsigned long long* trace = nullptr;  // [TRACE_MAX][4] device timestamps when the "trace" option is on
     uint32_t trace_n = 0;
     float* rope_inv_freq = nullptr;  // [head_dim/2]
+    std::vector<float> rope_inv_freq_host;
 
     // derived
     uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1, tokens_per_split = 32;
@@ -47,6 +48,7 @@ struct vb_ctx {
     void* nccl = nullptr;                 // communicator of the TP group
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
     bool links_open = false, use_links = true;
+    uint32_t qkv_ring = 8;                // weight ring depth of the QKV product (see GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
     float* partial = nullptr;             // [max_batch][d_model] row-parallel partial sums (all-reduced in place)
     unsigned char* tp_pair = nullptr;     // [max_batch] (value, index) of this rank's best logit
@@ -325,6 +327,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         g.x = c->hidden; g.dst = c->qkv;
         g.norm_w = c->tensor(VB_ROLE_ATTN_NORM, L).m.data; g.norm_fmt = c->tensor(VB_ROLE_ATTN_NORM, L).m.fmt; g.eps = d.rms_eps;
         g.w = c->tensor(VB_ROLE_WQ, L).m; g.w.rows = c->qkv_rows;
+        g.max_ring = c->qkv_ring;  // the attention blocks start (and fetch K/V) under this kernel
         g.trace = next_trace();
         VB_TRY(gemv(lcfg(c, true), g, c->gemv_path));
         // bias + RoPE + KV append
@@ -341,11 +344,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         // split-K attention over the paged cache (with the bias + RoPE + KV append fused in when possible)
         AttnArgs a;
         a.out = c->attn_out; a.q = c->q; a.k = kv_layer; a.kv_fp16 = 1;
-        if (fused_append) { a.qkv_raw = c->qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; }
+        if (fused_append) { a.qkv_raw = c->qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; a.rope_inv_freq_host = c->rope_inv_freq_host.data(); }
         a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
         a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
-        a.trace = next_trace();
+        a.trace = next_trace(); a.err = c->err_word;
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
@@ -512,6 +515,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
         // RoPE frequencies exactly as the reference computes them on the host (src/runtime.rs:758)
         std::vector<float> f(d.head_dim / 2);
         for (uint32_t j = 0; j < d.head_dim / 2; ++j) f[j] = 1.0f / powf(d.rope_theta, (float)(2 * j) / (float)d.head_dim);
+        c->rope_inv_freq_host = f;
         VB_CREATE_TRY(dev_alloc(&c->rope_inv_freq, f.size()));
         VB_CREATE_CUDA(cudaMemcpyAsync(c->rope_inv_freq, f.data(), f.size() * 4, cudaMemcpyHostToDevice, c->stream));
         VB_CREATE_CUDA(cudaStreamSynchronize(c->stream));
@@ -973,6 +977,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         }
         return VB_OK;
     }
+    if (!strcmp(name, "qkv_ring")) { c->qkv_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
@@ -1053,6 +1058,18 @@ int32_t vb_tp_p2p_open(vb_ctx* c, const void* handles, uint32_t n_handles) {
     }
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     c->links_open = true;
+    return VB_OK;
+}
+
+
+int32_t vb_tp_p2p_close(vb_ctx* c) {
+    VB_REQUIRE(c != nullptr, "vb_tp_p2p_close: null context");
+    VB_CUDA(cudaSetDevice(c->device));
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
+    for (uint32_t r = 0; r < 8; ++r)
+        if (c->links.base[r] && r != c->links.rank) { cudaIpcCloseMemHandle(c->links.base[r]); c->links.base[r] = nullptr; }
+    c->links_open = false;
     return VB_OK;
 }
 

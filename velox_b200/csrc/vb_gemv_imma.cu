@@ -370,6 +370,7 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + 2 * (size_t)IM_WARPS * 16 * 4 + 256;
     if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
     size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
+    if (a.max_ring >= 2 && ns > a.max_ring) ns = a.max_ring;
     ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : 2);  // ring depth per warp (template parameter)
     ImmaArgs f;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;

@@ -66,6 +66,8 @@ struct GemvArgs {
     uint32_t dst_stride = 0;         // elements between batch rows of dst (0 = out_dim)
     uint32_t dst_offset = 0;         // column offset inside dst
     int epilogue = EPI_STORE;
+    uint32_t max_ring = 8;           // cap on the weight ring depth per warp (8, 4 or 2): a shallower ring leaves
+                                     // shared memory for the next kernel's blocks to start under this one
     unsigned long long* trace = nullptr;  // 3-slot timestamp record of this launch (tuned kernels only)
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
@@ -96,7 +98,8 @@ struct AttnArgs {
     const float* qkv_raw = nullptr;
     const void *bq = nullptr, *bk = nullptr, *bv = nullptr;
     int bias_fmt = VB_FMT_F32;
-    const float* rope_inv_freq = nullptr;  // [D/2], 1/theta^(2j/D)
+    const float* rope_inv_freq = nullptr;  // [D/2], 1/theta^(2j/D) (device)
+    const float* rope_inv_freq_host = nullptr;  // the same table on the host: travels as kernel parameters (no load)
     const void* k = nullptr;       // contiguous: [seq][Hkv*D]; paged: the layer's pool
     const void* v = nullptr;       // contiguous only
     int kv_fp16 = 0;               // element type of the cache
@@ -108,6 +111,7 @@ struct AttnArgs {
     uint32_t max_splits = 1;       // grid size along the context (fixed per context so that graphs replay)
     uint32_t tokens_per_split = 32; // multiple of block_tokens
     unsigned long long* trace = nullptr;
+    uint32_t* err = nullptr;       // device word that a bounded wait sets when it runs out
     float* scratch = nullptr;      // attn_scratch_floats(): partials, then the split counters (zero before the first launch)
 };
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits);

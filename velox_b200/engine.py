@@ -103,6 +103,9 @@ class Engine:
         assert len(blob) == 64 * self.tp_size
         L.check(self._lib.vb_tp_p2p_open(self.h, C.create_string_buffer(blob, len(blob)), self.tp_size))
 
+    def tp_p2p_close(self):
+        L.check(self._lib.vb_tp_p2p_close(self.h))
+
     # ---- weights ----------------------------------------------------------------------------
     def load_tensor(self, role: int, layer: int, w: np.ndarray):
         """fp32/fp16 [rows][cols] host array; converted to the storage format on the GPU."""

@@ -73,6 +73,7 @@ SIGNATURES = {
     "vb_tp_init": (_i32, [_vp, _vp]),
     "vb_tp_p2p_export": (_i32, [_vp, _vp]),
     "vb_tp_p2p_open": (_i32, [_vp, _vp, _u32]),
+    "vb_tp_p2p_close": (_i32, [_vp]),
     "vb_op_embed": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp]),
     "vb_op_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _u32, _u32, _f32, _vp]),
     "vb_op_matmul": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp]),

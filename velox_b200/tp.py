@@ -72,3 +72,14 @@ def create_tp_engine(spec: ModelSpec, max_seq_len: int, max_batch: int = 1, kv_b
                  tp_rank=rank, tp_size=world, lean_weights=lean_weights)
     connect(eng, exchange)
     return eng
+
+
+def shutdown(eng: Engine):
+    """Closes a sharded engine in the order peer mappings need: every rank unmaps its peers, all ranks meet,
+    then each frees its own region with the context."""
+    import torch.distributed as dist
+    eng.sync()
+    if eng.tp_size > 1:
+        eng.tp_p2p_close()
+        dist.barrier()
+    eng.close()

@@ -1,8 +1,10 @@
 """Per-kernel device timeline of one decode step (profiling aid).
 
-    python -m velox_b200.trace [--layers 4] [--prompt-len 512]
+    python -m velox_b200.trace [--model llama3-8b|qwen2-72b] [--layers 4] [--prompt-len 512]
+    python -m torch.distributed.run --nproc-per-node N -m velox_b200.trace --model qwen2-72b [--exchange p2p|nccl]
 
-Builds a Llama-3-8B-shape int4 model with synthetic weights, captures the decode graph with the "trace"
+Builds a Llama-3-8B- or Qwen2-72B-shape int4 model with synthetic weights (sharded over the launcher's ranks
+when there are several: the gap before gate_up / the next qkv then contains the exchange), captures the decode graph with the "trace"
 option on and prints, for every traced kernel of one replayed step, when its first block entered, when it got
 past the grid-dependency wait and when its last block left (microseconds since the step's first kernel).
 """
@@ -15,17 +17,31 @@ import numpy as np
 
 from . import lib as L
 from .engine import Engine
-from .modelspec import LLAMA3_8B_INT4, PROMPT_STREAM
+from .modelspec import LLAMA3_8B_INT4, PROMPT_STREAM, QWEN2_72B_INT4
+from .tp import connect, env_rank, init_process_group, shutdown
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-72b"])
+    ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
     args = ap.parse_args()
-    spec = LLAMA3_8B_INT4.scaled(name="trace", n_layers=args.layers)
-    eng = Engine(spec, max_seq_len=args.prompt_len + 64)
+    base = LLAMA3_8B_INT4 if args.model == "llama3-8b" else QWEN2_72B_INT4
+    spec = base.scaled(name="trace", n_layers=args.layers)
+    rank, world, local = env_rank()
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        init_process_group()
+        eng = Engine(spec, max_seq_len=args.prompt_len + 64, device=local, tp_rank=rank, tp_size=world)
+        connect(eng, args.exchange)
+    else:
+        eng = Engine(spec, max_seq_len=args.prompt_len + 64)
     eng.load_synthetic(1)
+    if dist is not None:
+        dist.barrier()
     eng.set_option("trace", 1)
     rng = np.random.default_rng(PROMPT_STREAM)
     prompt = rng.integers(0, spec.vocab, args.prompt_len, dtype=np.uint32)
@@ -39,16 +55,23 @@ def main():
     L.check(lib.vb_trace_read(eng.h, out.ctypes.data_as(C.c_void_p), 1024, C.byref(n)))  # clears
     ms = eng.decode(1, timed=True)
     L.check(lib.vb_trace_read(eng.h, out.ctypes.data_as(C.c_void_p), 1024, C.byref(n)))
+    if dist is not None:
+        eng.sync()
+        dist.barrier()
+    if rank != 0:
+        shutdown(eng)
+        return
     r = out[:3 * n.value].reshape(-1, 3).astype(np.int64)
     names = ["qkv", "attn", "o_proj", "gate_up", "down"]
-    print("step %.4f ms, %d traced kernels (context %d)" % (ms, n.value, args.prompt_len + 8))
+    print("%s x%d layers, %d rank(s)%s: step %.4f ms, %d traced kernels (context %d)"
+          % (args.model, args.layers, world, (" exchange=" + args.exchange) if world > 1 else "", ms, n.value, args.prompt_len + 8))
     t0, prev = r[0, 0], r[0, 0]
     for i, (a, b, c) in enumerate(r):
         nm = names[i % 5] if i < args.layers * 5 else "lm_head"
         print("%-8s enter %8.2f  past_wait %8.2f  exit %8.2f | after_wait %6.2f us  gap %5.2f us"
               % (nm, (a - t0) / 1e3, (b - t0) / 1e3, (c - t0) / 1e3, (c - b) / 1e3, (b - prev) / 1e3))
         prev = c
-    eng.close()
+    shutdown(eng) if world > 1 else eng.close()
 
 
 if __name__ == "__main__":
