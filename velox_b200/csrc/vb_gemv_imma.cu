@@ -155,35 +155,48 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
         cp_async_commit();
     }
 
+    // Norm weights are parameters too: the 16-bit ones of a row that fits in registers are fetched now.
+    constexpr int XC = 4;  // chunks of 8 elements a thread holds at once
+    const uint32_t n_chunks = K / 8;
+    const bool in_regs = n_chunks <= (uint32_t)XC * IM_CONSUMERS;  // rows of up to 8192 elements: one trip through registers
+    const bool nw_pre = a.norm_w && in_regs && (a.norm_fmt == VB_FMT_F16 || a.norm_fmt == VB_FMT_BF16);
+    uint4 nw[XC];
+#pragma unroll
+    for (int i = 0; i < XC; ++i) {
+        const uint32_t c = threadIdx.x + i * IM_CONSUMERS;
+        nw[i] = (nw_pre && c < n_chunks) ? reinterpret_cast<const uint4*>(a.norm_w)[c] : make_uint4(0, 0, 0, 0);
+    }
+
     // ---- x: only now wait for the producer kernel ----------------------------------------------------------------
     pdl_wait();
     trace_mark(a.trace, 1);
     const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
 
-    // x -> shared memory.  Rows of up to 4096 elements make one trip through registers.
+    // x -> shared memory.  All of a thread's loads of a batch are issued before any value is used: one memory
+    // trip per batch of XC * 2048 elements (the whole row up to 8192 elements), not one per chunk.
     {
         const float* x = a.x;
-        const bool in_regs = K <= 4096;
-        float xr[2][8];
+        float xr[XC][8];
+        auto load_batch = [&](uint32_t it0) {
+#pragma unroll
+            for (int i = 0; i < XC; ++i) {
+                const uint32_t c = threadIdx.x + (it0 + i) * IM_CONSUMERS;
+                float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+                if (active && c < n_chunks) { v0 = *reinterpret_cast<const float4*>(x + c * 8); v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4); }
+                xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
+                xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
+            }
+        };
+        const uint32_t n_it = (n_chunks + IM_CONSUMERS - 1) / IM_CONSUMERS;  // chunk rounds of the whole block
         float ss = 0.0f;
+        if (in_regs) load_batch(0);
         if (active && a.norm_w) {
-            if (in_regs) {
+            for (uint32_t it0 = 0; it0 < n_it; it0 += XC) {
+                if (!in_regs) load_batch(it0);
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                    const uint32_t c = threadIdx.x + i * IM_CONSUMERS;
-                    if (c < K / 8) {
-                        const float4 v0 = *reinterpret_cast<const float4*>(x + c * 8), v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-                        xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
-                        xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
+                for (int i = 0; i < XC; ++i)
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) ss = fmaf(xr[i][e], xr[i][e], ss);
-                    }
-                }
-            } else {
-                for (uint32_t k = threadIdx.x * 4; k < K; k += IM_CONSUMERS * 4) {
-                    const float4 v = *reinterpret_cast<const float4*>(x + k);
-                    ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-                }
+                    for (int e = 0; e < 8; ++e) ss = fmaf(xr[i][e], xr[i][e], ss);  // chunks past the row are zero
             }
             ss = warp_sum(ss);
             if (lane == 0) ssq[warp] = ss;
@@ -196,25 +209,35 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
             for (int w = 0; w < IM_WARPS; ++w) tot += ssq[w];
             inv = 1.0f / sqrtf(tot / (float)K + a.eps);
         }
-        for (uint32_t c0 = 0; c0 < K / 8; c0 += IM_CONSUMERS) {
-            const uint32_t c = c0 + threadIdx.x;
-            const bool valid = active && c < K / 8;  // groups of 4 lanes are valid together
-            float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            if (valid) {
-                if (in_regs && a.norm_w) {
-                    const int i = (int)(c0 / IM_CONSUMERS);
+        for (uint32_t it0 = 0; it0 < n_it; it0 += XC) {
+            if (!in_regs) load_batch(it0);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = i == 0 ? xr[0][e] : xr[1][e];
-                } else {
-                    const float4 v0 = *reinterpret_cast<const float4*>(x + c * 8), v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4);
-                    v[0] = v0.x; v[1] = v0.y; v[2] = v0.z; v[3] = v0.w; v[4] = v1.x; v[5] = v1.y; v[6] = v1.z; v[7] = v1.w;
-                }
-                if (a.norm_w) {
+            for (int i = 0; i < XC; ++i) {
+                if (it0 + i < n_it) {  // uniform over the block: every lane of a warp stages together
+                    const uint32_t c = threadIdx.x + (it0 + i) * IM_CONSUMERS;
+                    const bool valid = active && c < n_chunks;  // groups of 4 lanes are valid together
+                    float v[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
+                    for (int e = 0; e < 8; ++e) v[e] = xr[i][e];
+                    if (a.norm_w && valid) {
+                        if (nw_pre) {
+                            const uint32_t pk[4] = {nw[i].x, nw[i].y, nw[i].z, nw[i].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float2 f;
+                                if (a.norm_fmt == VB_FMT_F16) f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
+                                else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[e]));
+                                v[2 * e] = (v[2 * e] * inv) * f.x;
+                                v[2 * e + 1] = (v[2 * e + 1] * inv) * f.y;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
+                        }
+                    }
+                    im_stage_chunk(xq, sx, invp, v, c, valid);
                 }
             }
-            im_stage_chunk(xq, sx, invp, v, c, valid);
         }
         im_consumer_sync();
     }
