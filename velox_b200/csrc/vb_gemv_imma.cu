@@ -33,11 +33,12 @@
 
 namespace vb {
 
-constexpr int IM_WARPS = 8;
-constexpr int IM_CONSUMERS = IM_WARPS * 32;
+constexpr int IM_WARPS = 8;                              // warps that share one 16-row tile (they split its K extent)
+constexpr int IM_GROUPS = 2;                             // tile groups per block: they share the staged x, nothing else
+constexpr int IM_CONSUMERS = IM_GROUPS * IM_WARPS * 32;  // threads per block
 constexpr int IM_BLK_BYTES = 1152;
-constexpr int IM_STAGE_BYTES = IM_WARPS * IM_BLK_BYTES;  // one ring slot of every warp
-constexpr int IM_MAX_SMEM = 112 * 1024;
+constexpr int IM_STAGE_BYTES = IM_GROUPS * IM_WARPS * IM_BLK_BYTES;  // one ring slot of every warp
+constexpr int IM_MAX_SMEM = 216 * 1024;
 
 struct ImmaArgs {
     const unsigned char* w;  // v3 tile-major blocks
@@ -59,6 +60,10 @@ __device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, u
 }
 
 __device__ __forceinline__ void im_consumer_sync() { __syncthreads(); }
+// barrier among the 8 warps of one tile group (hardware barrier 1 + group)
+__device__ __forceinline__ void im_group_sync(uint32_t group) {
+    asm volatile("bar.sync %0, %1;" ::"r"(1u + group), "n"(IM_WARPS * 32) : "memory");
+}
 
 __device__ __forceinline__ float im_norm_w(const void* w, int fmt, uint32_t i) {
     return fmt == VB_FMT_F16 ? __half2float(((const __half*)w)[i])
@@ -107,13 +112,13 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // The sequence of 16x128 blocks one warp works through: block `kk` (kk = warp, warp+8, ...) of row tile `tile`
-// (tile = blockIdx.x, += gridDim.x).
+// (tile = 2 * blockIdx.x + group, += 2 * gridDim.x).
 struct BlockCursor {
     uint32_t tile, kk;
     __device__ __forceinline__ bool valid(uint32_t n_tiles) const { return tile < n_tiles; }
     __device__ __forceinline__ void advance(uint32_t KT, uint32_t warp) {
         kk += IM_WARPS;
-        if (kk >= KT) { kk = warp; tile += gridDim.x; }
+        if (kk >= KT) { kk = warp; tile += IM_GROUPS * gridDim.x; }
     }
 };
 
@@ -126,27 +131,33 @@ __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w,
     if (lane < 8) cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
 }
 
-// grid: min(row tiles, 2 per SM) persistent blocks of 8 warps.  Each warp streams its own blocks through a
+// grid: one persistent block of 16 warps per SM.  The block stages x once (all 512 threads) and then works as
+// two independent groups of 8 warps, each on its own row tile; each warp streams its own blocks through a
 // private ring of NS slots with cp.async (16-byte asynchronous copies, L1 bypassed): no block-wide
 // synchronisation on the data path, ~130 KB per SM in flight, started before the grid-dependency wait.
+// (Two blocks of 8 warps per SM move the same bytes but each stages its own copy of x: twice the L2 reads
+// and twice the conversion work in the serial part of the kernel.)
 template <int NS>
-__global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
+__global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
-    unsigned char* ring = smem_raw;                                              // [IM_WARPS][NS][IM_BLK_BYTES]
-    unsigned char* xq = ring + (size_t)IM_WARPS * NS * IM_BLK_BYTES;             // [K/32][64]
+    unsigned char* ring = smem_raw;                                              // [IM_GROUPS * IM_WARPS][NS][IM_BLK_BYTES]
+    unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * IM_BLK_BYTES; // [K/32][64]
     int* sx = reinterpret_cast<int*>(xq + (size_t)K * 2);                        // [K/32]
     float* invp = reinterpret_cast<float*>(sx + K / 32);                         // [K/32]
-    float* red = invp + K / 32;                                                  // [2][IM_WARPS][16]
-    __shared__ float ssq[IM_WARPS];
+    float* red = invp + K / 32;                                                  // [IM_GROUPS][2][IM_WARPS][16]
+    __shared__ float ssq[IM_GROUPS * IM_WARPS];
 
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const uint32_t group = wid / IM_WARPS, warp = wid % IM_WARPS;  // tile group, warp within the group
+    const uint32_t gt = threadIdx.x % (IM_WARPS * 32);            // thread within the group
+    const uint32_t vtile0 = IM_GROUPS * blockIdx.x + group, vstride = IM_GROUPS * gridDim.x;
     trace_mark(a.trace, 0);
     pdl_launch_dependents();
 
     // ---- prologue: weights do not depend on the previous kernel; fill the ring before waiting for x ----------
-    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)warp * NS * IM_BLK_BYTES);
-    BlockCursor icur{blockIdx.x, warp};  // next block to request
+    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)wid * NS * IM_BLK_BYTES);
+    BlockCursor icur{vtile0, warp};  // next block to request
     uint32_t issued = 0;
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
 #pragma unroll
@@ -158,7 +169,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
     // Norm weights are parameters too: the 16-bit ones of a row that fits in registers are fetched now.
     constexpr int XC = 4;  // chunks of 8 elements a thread holds at once
     const uint32_t n_chunks = K / 8;
-    const bool in_regs = n_chunks <= (uint32_t)XC * IM_CONSUMERS;  // rows of up to 8192 elements: one trip through registers
+    const bool in_regs = n_chunks <= (uint32_t)XC * IM_CONSUMERS;  // rows of up to 16384 elements: one trip through registers
     const bool nw_pre = a.norm_w && in_regs && (a.norm_fmt == VB_FMT_F16 || a.norm_fmt == VB_FMT_BF16);
     uint4 nw[XC];
 #pragma unroll
@@ -173,7 +184,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
     const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
 
     // x -> shared memory.  All of a thread's loads of a batch are issued before any value is used: one memory
-    // trip per batch of XC * 2048 elements (the whole row up to 8192 elements), not one per chunk.
+    // trip per batch of XC * 4096 elements (the whole row up to 16384 elements), not one per chunk.
     {
         const float* x = a.x;
         float xr[XC][8];
@@ -199,14 +210,14 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
                     for (int e = 0; e < 8; ++e) ss = fmaf(xr[i][e], xr[i][e], ss);  // chunks past the row are zero
             }
             ss = warp_sum(ss);
-            if (lane == 0) ssq[warp] = ss;
+            if (lane == 0) ssq[wid] = ss;
         }
         im_consumer_sync();
         float inv = 1.0f;
         if (a.norm_w && active) {
             float tot = 0.0f;
 #pragma unroll
-            for (int w = 0; w < IM_WARPS; ++w) tot += ssq[w];
+            for (int w = 0; w < IM_GROUPS * IM_WARPS; ++w) tot += ssq[w];
             inv = 1.0f / sqrtf(tot / (float)K + a.eps);
         }
         for (uint32_t it0 = 0; it0 < n_it; it0 += XC) {
@@ -246,10 +257,10 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
     uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 4 * t;
-    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, parity ^= 1) {
+    for (uint32_t tile = vtile0; tile < n_tiles; tile += vstride, parity ^= 1) {
         // residual rows fetched early so that the epilogue does not wait on them
         float resid = 0.0f;
-        if (a.epilogue == EPI_RESIDUAL && threadIdx.x < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + threadIdx.x];
+        if (a.epilogue == EPI_RESIDUAL && gt < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + gt];
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
         for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
@@ -258,7 +269,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
             cp_async_wait<NS - 1>();
             __syncwarp();
             if (active) {
-                const unsigned char* blk = ring + ((size_t)warp * NS + consumed % NS) * IM_BLK_BYTES;
+                const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * IM_BLK_BYTES;
                 const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
                 const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
                 const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
@@ -288,21 +299,22 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 2) k_gemv_q4_imma(ImmaArgs a) {
         // the four lanes of a row hold different groups: add them, then reduce the 8 warps through shared memory
         acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
         acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 1); acc1 += __shfl_xor_sync(0xFFFFFFFFu, acc1, 2);
-        float* rbuf = red + (size_t)parity * (IM_WARPS * 16);  // double-buffered by tile parity: one barrier per tile
+        // double-buffered by tile parity: one (group) barrier per tile
+        float* rbuf = red + ((size_t)group * 2 + parity) * (IM_WARPS * 16);
         if (t == 0) { rbuf[warp * 16 + g] = acc0; rbuf[warp * 16 + g + 8] = acc1; }
-        im_consumer_sync();
-        if (threadIdx.x < 16 && active) {
+        im_group_sync(group);
+        if (gt < 16 && active) {
             float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < IM_WARPS; ++w) v += rbuf[w * 16 + threadIdx.x];
+            for (int w = 0; w < IM_WARPS; ++w) v += rbuf[w * 16 + gt];
             if (a.epilogue == EPI_SWIGLU) {
                 // tile = 8 gate rows (mma rows 0..7) over the same 8 up rows (mma rows 8..15)
                 const float up = __shfl_down_sync(0x0000FFFFu, v, 8);
-                if (threadIdx.x < 8) a.dst[a.dst_offset + tile * 8 + threadIdx.x] = (v / (1.0f + expf(-v))) * up;
+                if (gt < 8) a.dst[a.dst_offset + tile * 8 + gt] = (v / (1.0f + expf(-v))) * up;
             } else if (a.epilogue == EPI_RESIDUAL) {
-                a.dst[a.dst_offset + tile * 16 + threadIdx.x] = resid + v;
+                a.dst[a.dst_offset + tile * 16 + gt] = resid + v;
             } else {
-                a.dst[a.dst_offset + tile * 16 + threadIdx.x] = v;
+                a.dst[a.dst_offset + tile * 16 + gt] = v;
             }
         }
     }
@@ -390,7 +402,7 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     if (swiglu && (a.w2.rows != a.w.rows || a.w2.cols != a.w.cols)) return cudaSuccess;
     const uint32_t rows = swiglu ? 2 * a.w.rows : a.w.rows;
     if (rows % 16 != 0) return cudaSuccess;
-    const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + 2 * (size_t)IM_WARPS * 16 * 4 + 256;
+    const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
     if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
     size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
     if (a.max_ring >= 2 && ns > a.max_ring) ns = a.max_ring;
@@ -408,7 +420,8 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     }
     const uint32_t n_tiles = rows / 16;
     *handled = true;
-    const dim3 grid(n_tiles < 2u * n_sm ? n_tiles : 2u * n_sm);
+    const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
+    const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
     const size_t smem = fixed + ns * IM_STAGE_BYTES;
     if (ns == 8) return launch(lc, k_gemv_q4_imma<8>, grid, dim3(IM_CONSUMERS), smem, f);
     if (ns == 4) return launch(lc, k_gemv_q4_imma<4>, grid, dim3(IM_CONSUMERS), smem, f);
