@@ -386,7 +386,11 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
 
 cudaError_t gemv_imma_init() {
     cudaError_t e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<10>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
     return cudaFuncSetAttribute(k_gemv_q4_imma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
 }
@@ -406,7 +410,7 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
     size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
     if (a.max_ring >= 2 && ns > a.max_ring) ns = a.max_ring;
-    ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : 2);  // ring depth per warp (template parameter)
+    ns = ns >= 12 ? 12 : (ns >= 10 ? 10 : (ns >= 8 ? 8 : (ns >= 6 ? 6 : (ns >= 4 ? 4 : (ns >= 3 ? 3 : 2)))));  // ring depth per warp (template parameter)
     ImmaArgs f;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
@@ -423,8 +427,12 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
     const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
     const size_t smem = fixed + ns * IM_STAGE_BYTES;
+    if (ns == 12) return launch(lc, k_gemv_q4_imma<12>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 10) return launch(lc, k_gemv_q4_imma<10>, grid, dim3(IM_CONSUMERS), smem, f);
     if (ns == 8) return launch(lc, k_gemv_q4_imma<8>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 6) return launch(lc, k_gemv_q4_imma<6>, grid, dim3(IM_CONSUMERS), smem, f);
     if (ns == 4) return launch(lc, k_gemv_q4_imma<4>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 3) return launch(lc, k_gemv_q4_imma<3>, grid, dim3(IM_CONSUMERS), smem, f);
     return launch(lc, k_gemv_q4_imma<2>, grid, dim3(IM_CONSUMERS), smem, f);
 }
 

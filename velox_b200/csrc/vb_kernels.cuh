@@ -66,8 +66,7 @@ struct GemvArgs {
     uint32_t dst_stride = 0;         // elements between batch rows of dst (0 = out_dim)
     uint32_t dst_offset = 0;         // column offset inside dst
     int epilogue = EPI_STORE;
-    uint32_t max_ring = 8;           // cap on the weight ring depth per warp (8, 4 or 2): a shallower ring leaves
-                                     // shared memory for the next kernel's blocks to start under this one
+    uint32_t max_ring = 12;          // cap on the weight ring depth per warp (12, 10, 8, 4 or 2)
     unsigned long long* trace = nullptr;  // 3-slot timestamp record of this launch (tuned kernels only)
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
