@@ -111,23 +111,48 @@ __device__ __forceinline__ void warp_transpose_reduce(float v[NV], uint32_t lane
 }
 
 
+// ---- fp16 tensor-core helpers (m16n8k16) -----------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t r[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t r[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16_16816(float c[4], const uint32_t a[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // Shared-memory plan of one block (dynamic): K/V staging for two chunks of CH tokens, the warp-merge buffer.
-template <typename KVT, int EPL, int GM>
+template <typename KVT, int EPL, int GM, bool MMA>
 struct AttnSmem {
     static constexpr int D = EPL * 32;
+    // staged row stride in elements: the tensor-core path pads rows by 16 bytes so that the 8 rows of an
+    // ldmatrix tile fall into different banks
+    static constexpr int RS = D + (MMA ? 8 : 0);
     // tokens per staged chunk: K+V of a chunk take at most 32 KB, at most 64 tokens
     static constexpr int CH = (16384 / (D * (int)sizeof(KVT))) > 64 ? 64 : (16384 / (D * (int)sizeof(KVT)));
-    static constexpr size_t kv_bytes = (size_t)2 * 2 * CH * D * sizeof(KVT);  // [buffer][K|V][CH][D]
+    static constexpr size_t kv_bytes = (size_t)2 * 2 * CH * RS * sizeof(KVT);  // [buffer][K|V][CH][RS]
     static constexpr size_t acc_bytes = (size_t)ATTN_WARPS * GM * D * sizeof(float);
     static constexpr size_t total = kv_bytes + acc_bytes;
 };
 
-template <typename KVT, int EPL, int GM>
+template <typename KVT, int EPL, int GM, bool MMA>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     const AttnArgs& a = ka.a;
-    using SM = AttnSmem<KVT, EPL, GM>;
-    constexpr int D = EPL * 32, CH = SM::CH;
-    constexpr int TCH = (EPL >= 8) ? 2 : ((GM >= 8) ? 4 : 8);  // tokens a warp handles at once
+    using SM = AttnSmem<KVT, EPL, GM, MMA>;
+    constexpr int D = EPL * 32, CH = SM::CH, RS = SM::RS;
+    static_assert(!MMA || sizeof(KVT) == 2, "the tensor-core path reads an fp16 cache");
+    constexpr int TCH = MMA ? 1 : ((EPL >= 8) ? 2 : ((GM >= 8) ? 4 : 8));  // scalar path: tokens a warp handles at once
     constexpr int NV = TCH * GM;                              // partial dot products per lane (<= 32)
     constexpr int ROW16 = D * sizeof(KVT) / 16;               // 16-byte pieces per K or V row
     static_assert(NV <= 32 && (NV & (NV - 1)) == 0, "values per lane must be a power of two <= 32");
@@ -170,6 +195,14 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     // wait just before the pushes (the barrier's latency hides behind the attention itself)
     cg::cluster_group cluster = cg::this_cluster();
     cluster.barrier_arrive();
+    // tensor-core path: S^T = K Q^T (16 tokens x 8 heads per mma) and O^T = V^T P^T (16 dims x 8 heads), so the
+    // query heads are the N = 8 columns: no padding for a group of 8, and each thread's accumulator columns are the
+    // two heads (2 * (lane & 3), +1) whose running maximum it tracks
+    constexpr int MT = D / 16;
+    float o_t[MMA ? MT : 1][4];
+    float m2[2] = {-INFINITY, -INFINITY}, l2[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < (MMA ? MT : 1); ++i) { o_t[i][0] = 0.0f; o_t[i][1] = 0.0f; o_t[i][2] = 0.0f; o_t[i][3] = 0.0f; }
     float m[GM], l[GM], acc[GM][EPL];
 #pragma unroll
     for (int g = 0; g < GM; ++g) {
@@ -182,32 +215,51 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     // announced on that buffer's transaction barrier: in the paged pool one copy moves the 16 cached rows of a
     // KV block (K or V) for this head, so a 64-token chunk is 8 copies issued by 8 threads -- the block table
     // entry each needs is read by the issuing thread itself.  The contiguous layout takes one copy per row.
-    // Called by warp 0 only; `rot` rotates the lanes so that two chunks requested back to back use different
-    // lanes (their block-table reads then overlap instead of queueing behind one another).
+    // Called by the whole block; `rot` rotates the threads so that two chunks requested back to back use
+    // different ones (their block-table reads then overlap instead of queueing behind one another).
     auto stage_chunk = [&](uint32_t c, uint32_t buf, uint32_t rot) {
         const uint32_t c0 = t_lo + c * CH;
         const uint32_t n_tok = min((uint32_t)CH, t_hi - c0);
-        KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
+        KVT* kb = kv_s + (size_t)buf * 2 * CH * RS;
         const uint32_t bar = smem_u32(&kv_bar[buf]);
-        const uint32_t me = (lane + 32 - rot) & 31;
-        if (a.block_table) {
+        const uint32_t NT = ATTN_WARPS * 32;
+        const uint32_t me = (threadIdx.x + NT - rot) % NT;
+        const uint32_t row_bytes = D * (uint32_t)sizeof(KVT);
+        if (a.block_table && !MMA) {
             const uint32_t nb = (n_tok + a.block_tokens - 1) / a.block_tokens;
-            const uint32_t blk_bytes = a.block_tokens * D * (uint32_t)sizeof(KVT);
+            const uint32_t blk_bytes = a.block_tokens * row_bytes;
             if (me == 0) mbar_expect_tx(bar, nb * 2 * blk_bytes);
-            for (uint32_t i = me; i < nb * 2; i += 32) {
+            for (uint32_t i = me; i < nb * 2; i += NT) {
                 const uint32_t kv = i & 1, j = i >> 1;
                 const uint32_t bi = c0 / a.block_tokens + j;
                 const int32_t blk = spec_table ? blk_s[bi] : a.block_table[(size_t)b * a.max_blocks + bi];
                 const KVT* src = reinterpret_cast<const KVT*>(a.k) + (((size_t)blk * 2 + kv) * a.Hkv + kvh) * a.block_tokens * D;
-                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + (size_t)j * a.block_tokens) * D), src, blk_bytes, bar);
+                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + (size_t)j * a.block_tokens) * RS), src, blk_bytes, bar);
             }
         } else {
-            const uint32_t row_bytes = D * (uint32_t)sizeof(KVT);
+            // one copy per row: the contiguous layout has no larger unit, and the tensor-core path pads the rows
             if (me == 0) mbar_expect_tx(bar, n_tok * 2 * row_bytes);
-            for (uint32_t i = me; i < n_tok * 2; i += 32) {
-                const uint32_t kv = i & 1, tok = i >> 1;
-                const size_t off = (size_t)b * ka.kv_batch_stride + (size_t)(c0 + tok) * a.Hkv * D + (size_t)kvh * D;
-                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + tok) * D), reinterpret_cast<const KVT*>(kv ? a.v : a.k) + off, row_bytes, bar);
+            for (uint32_t i = me; i < n_tok * 2; i += NT) {
+                const uint32_t kv = i & 1, tok = i >> 1, tt = c0 + tok;
+                const KVT* src;
+                if (a.block_table) {
+                    const uint32_t bi = tt / a.block_tokens;
+                    const int32_t blk = spec_table ? blk_s[bi] : a.block_table[(size_t)b * a.max_blocks + bi];
+                    src = reinterpret_cast<const KVT*>(a.k) + (((size_t)blk * 2 + kv) * a.Hkv + kvh) * a.block_tokens * D +
+                          (size_t)(tt % a.block_tokens) * D;
+                } else {
+                    src = reinterpret_cast<const KVT*>(kv ? a.v : a.k) + (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
+                }
+                tma_load_1d(smem_u32(kb + ((size_t)kv * CH + tok) * RS), src, row_bytes, bar);
+            }
+            if constexpr (MMA) {
+                // rows up to the next multiple of 16 are multiplied (with probability 0): they must hold numbers
+                const uint32_t pad_hi = min((uint32_t)CH, (n_tok + 15u) & ~15u);
+                for (uint32_t i = me; i < (pad_hi - n_tok) * 2 * (row_bytes / 16); i += NT) {
+                    const uint32_t piece = i % (row_bytes / 16), rowi = i / (row_bytes / 16);
+                    const uint32_t kv = rowi & 1, tok = n_tok + (rowi >> 1);
+                    reinterpret_cast<uint4*>(kb + ((size_t)kv * CH + tok) * RS)[piece] = make_uint4(0, 0, 0, 0);
+                }
             }
         }
     };
@@ -225,19 +277,15 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         mbar_init(smem_u32(&kv_bar[1]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (spec_table) {
-        blk_s[threadIdx.x] = my_blk;
-        __syncthreads();
+    if (spec_table) blk_s[threadIdx.x] = my_blk;
+    __syncthreads();  // barriers initialised, block table in place
+    if (early) {
+        // the requests for the first two chunks, spread over the block (one copy per thread or fewer)
+        if (n_ch > 0) stage_chunk(0, 0, 0);
+        if (n_ch > 1) stage_chunk(1, 1, ATTN_WARPS * 16);
     }
-    if (warp == 0) {
-        // warp 0: the requests for the first two chunks
-        __syncwarp();
-        if (early) {
-            if (n_ch > 0) stage_chunk(0, 0, 0);
-            if (n_ch > 1) stage_chunk(1, 1, 16);
-        }
-    } else if (a.qkv_raw) {
-        // the other warps: rotary angles of this position (one sincos per frequency, shared by all heads)
+    if (a.qkv_raw && warp != 0) {
+        // rotary angles of this position (one sincos per frequency, shared by all heads)
         for (uint32_t j = threadIdx.x - 32; j < half; j += (ATTN_WARPS - 1) * 32) {
             float sn, cs;
             sincosf((float)pos * (ka.inv_freq_n ? ka.inv_freq[j] : a.rope_inv_freq[j]), &sn, &cs);
@@ -265,9 +313,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
 
     pdl_wait();
     trace_mark(a.trace, 1);
-    if (!early && warp == 0) {
+    if (!early) {
         if (n_ch > 0) stage_chunk(0, 0, 0);
-        if (n_ch > 1) stage_chunk(1, 1, 16);
+        if (n_ch > 1) stage_chunk(1, 1, ATTN_WARPS * 16);
     }
 
     if (has_tokens) {
@@ -331,29 +379,87 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
 #pragma unroll
         for (int g = 0; g < GM; ++g)
 #pragma unroll
-            for (int e = 0; e < EPL; ++e) qr[g][e] = q_s[g][lane * EPL + e];
+            for (int e = 0; e < EPL; ++e) qr[g][e] = MMA ? 0.0f : q_s[g][lane * EPL + e];
+        // Q^T as B fragments (k = head dimension, n = query head), fp16
+        uint32_t qb[MMA ? MT : 1][2];
+        if constexpr (MMA) {
+            const uint32_t n = lane >> 2, k0 = 2 * (lane & 3);
+#pragma unroll
+            for (int ks = 0; ks < MT; ++ks) {
+                const bool on = n < (uint32_t)GM;
+                const float* qrow = q_s[on ? n : 0];
+                qb[ks][0] = on ? pack_half2(qrow[ks * 16 + k0], qrow[ks * 16 + k0 + 1]) : 0u;
+                qb[ks][1] = on ? pack_half2(qrow[ks * 16 + k0 + 8], qrow[ks * 16 + k0 + 9]) : 0u;
+            }
+        }
 
         // ---- the slice, CH tokens at a time through the two buffers (both were requested above) ----------------
         for (uint32_t c = 0; c < n_ch; ++c) {
             const uint32_t c0 = t_lo + c * CH, buf = c & 1;
             if (!mbar_wait(smem_u32(&kv_bar[buf]), (c >> 1) & 1) && a.err) atomicOr(a.err, 0x400u);
-            KVT* kb = kv_s + (size_t)buf * 2 * CH * D;
+            KVT* kb = kv_s + (size_t)buf * 2 * CH * RS;
             if (appender && c0 <= pos && pos < c0 + CH) {
                 // overwrite the staged copy of the new token's row with the values just computed
                 for (uint32_t i = threadIdx.x; i < 2 * ROW16; i += blockDim.x) {
                     const uint32_t kv = i / ROW16, piece = i % ROW16;
-                    reinterpret_cast<uint4*>(kb + ((size_t)kv * CH + (pos - c0)) * D)[piece] = reinterpret_cast<const uint4*>(new_kv[kv])[piece];
+                    reinterpret_cast<uint4*>(kb + ((size_t)kv * CH + (pos - c0)) * RS)[piece] = reinterpret_cast<const uint4*>(new_kv[kv])[piece];
                 }
                 __syncthreads();
             }
             const uint32_t c_hi = min(t_hi, c0 + CH);
+            if constexpr (MMA) {
+                const uint32_t n_tiles = (c_hi - c0 + 15) / 16;
+                const uint32_t mi = lane >> 3, r8 = lane & 7;
+                for (uint32_t tile = warp; tile < n_tiles; tile += ATTN_WARPS) {
+                    const uint32_t tok0 = tile * 16;
+                    // scores of 16 tokens x 8 heads
+                    float sc4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    const uint32_t k_addr = smem_u32(kb + (size_t)(tok0 + (mi & 1) * 8 + r8) * RS + (mi >> 1) * 8);
+#pragma unroll
+                    for (int ks = 0; ks < MT; ++ks) {
+                        uint32_t af[4];
+                        ldsm_x4(af, k_addr + ks * 32);
+                        mma_f16_16816(sc4, af, qb[ks][0], qb[ks][1]);
+                    }
+                    // this thread: tokens tA = lane / 4 and tA + 8 of the tile, heads 2 * (lane & 3) and + 1
+                    const uint32_t tA = c0 + tok0 + (lane >> 2);
+                    const bool vA = tA < c_hi, vB = tA + 8 < c_hi;
+                    const float s0 = vA ? sc4[0] * ka.scale : -INFINITY, s1 = vA ? sc4[1] * ka.scale : -INFINITY;
+                    const float s2 = vB ? sc4[2] * ka.scale : -INFINITY, s3 = vB ? sc4[3] * ka.scale : -INFINITY;
+                    float mx0 = fmaxf(s0, s2), mx1 = fmaxf(s1, s3);
+#pragma unroll
+                    for (int off = 4; off < 32; off <<= 1) {
+                        mx0 = fmaxf(mx0, __shfl_xor_sync(0xFFFFFFFFu, mx0, off));
+                        mx1 = fmaxf(mx1, __shfl_xor_sync(0xFFFFFFFFu, mx1, off));
+                    }
+                    const float nm0 = fmaxf(m2[0], mx0), nm1 = fmaxf(m2[1], mx1);
+                    const float al0 = (m2[0] == -INFINITY) ? 0.0f : __expf(m2[0] - nm0);
+                    const float al1 = (m2[1] == -INFINITY) ? 0.0f : __expf(m2[1] - nm1);
+                    const float p0 = (nm0 == -INFINITY) ? 0.0f : __expf(s0 - nm0), p2 = (nm0 == -INFINITY) ? 0.0f : __expf(s2 - nm0);
+                    const float p1 = (nm1 == -INFINITY) ? 0.0f : __expf(s1 - nm1), p3 = (nm1 == -INFINITY) ? 0.0f : __expf(s3 - nm1);
+                    l2[0] = fmaf(l2[0], al0, p0 + p2);
+                    l2[1] = fmaf(l2[1], al1, p1 + p3);
+                    m2[0] = nm0; m2[1] = nm1;
+                    // P^T as B fragments (k = token, n = head): transpose the two 8x8 halves of the score tile
+                    const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
+                    const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
+                    const uint32_t v_addr = smem_u32(kb + ((size_t)CH + tok0 + (mi >> 1) * 8 + r8) * RS + (mi & 1) * 8);
+#pragma unroll
+                    for (int mt = 0; mt < MT; ++mt) {
+                        o_t[mt][0] *= al0; o_t[mt][2] *= al0; o_t[mt][1] *= al1; o_t[mt][3] *= al1;
+                        uint32_t af[4];
+                        ldsm_x4_trans(af, v_addr + mt * 32);
+                        mma_f16_16816(o_t[mt], af, pb0, pb1);
+                    }
+                }
+            } else
             for (uint32_t t0 = c0 + warp * TCH; t0 < c_hi; t0 += ATTN_WARPS * TCH) {
                 float kr[TCH][EPL], vr[TCH][EPL];
 #pragma unroll
                 for (int i = 0; i < TCH; ++i) {
                     const uint32_t tok = min(t0 + i, c_hi - 1) - c0;  // out-of-range tokens re-read the last row, masked below
-                    load_row<KVT, EPL>(kb + (size_t)tok * D, lane, kr[i]);
-                    load_row<KVT, EPL>(kb + ((size_t)CH + tok) * D, lane, vr[i]);
+                    load_row<KVT, EPL>(kb + (size_t)tok * RS, lane, kr[i]);
+                    load_row<KVT, EPL>(kb + ((size_t)CH + tok) * RS, lane, vr[i]);
                 }
                 // partial dot products, value index = g * TCH + i
                 float pv[NV];
@@ -398,7 +504,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                 }
             }
             __syncthreads();  // every warp is done with the buffer: it takes the chunk after next
-            if (c + 2 < n_ch && warp == 0) {
+            if (c + 2 < n_ch) {
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 stage_chunk(c + 2, buf, 0);
             }
@@ -406,11 +512,32 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     }
 
     // ---- merge the warps into this block's partial (m, l, unnormalised acc) ...
+    if constexpr (MMA) {
+        // the 8 lanes that share lane & 3 hold partial sums of the same two heads
 #pragma unroll
-    for (int g = 0; g < GM; ++g) {
-        if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
+        for (int off = 4; off < 32; off <<= 1) {
+            l2[0] += __shfl_xor_sync(0xFFFFFFFFu, l2[0], off);
+            l2[1] += __shfl_xor_sync(0xFFFFFFFFu, l2[1], off);
+        }
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t h = 2 * (lane & 3) + i;
+            if (h < (uint32_t)GM) {
+                if (lane < 4) { part_ml[warp][h][0] = m2[i]; part_ml[warp][h][1] = l2[i]; }
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    part_acc[((size_t)warp * GM + h) * D + mt * 16 + (lane >> 2)] = o_t[mt][i];
+                    part_acc[((size_t)warp * GM + h) * D + mt * 16 + (lane >> 2) + 8] = o_t[mt][2 + i];
+                }
+            }
+        }
+    } else {
+#pragma unroll
+        for (int g = 0; g < GM; ++g) {
+            if (lane == 0) { part_ml[warp][g][0] = m[g]; part_ml[warp][g][1] = l[g]; }
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) part_acc[((size_t)warp * GM + g) * D + lane * EPL + e] = acc[g][e];
+        }
     }
     __syncthreads();
     // ---- ... and push it to the blocks of the cluster (the splits of one sequence and head group): block j
@@ -479,10 +606,12 @@ uint32_t attn_pick_splits(uint32_t max_seq) {
     return s < 1 ? 1 : s;
 }
 
-template <typename KVT, int EPL, int GM>
+bool attn_use_mma = true;  // fp16 caches with head_dim <= 256: QK^T and PV on the tensor cores (option "attn_mma")
+
+template <typename KVT, int EPL, int GM, bool MMA>
 static cudaError_t launch_split_g(const LaunchCfg& lc, AttnKArgs ka) {
     ka.g_chunks = (ka.G + GM - 1) / GM;
-    const size_t smem = AttnSmem<KVT, EPL, GM>::total;
+    const size_t smem = AttnSmem<KVT, EPL, GM, MMA>::total;
     dim3 grid(ka.a.Hkv * ka.g_chunks, ka.n_splits, ka.a.batch);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -500,18 +629,26 @@ static cudaError_t launch_split_g(const LaunchCfg& lc, AttnKArgs ka) {
     }
     cfg.attrs = attr;
     if (lc.counter) ++*lc.counter;
-    return cudaLaunchKernelEx(&cfg, k_attn_split<KVT, EPL, GM>, ka);
+    return cudaLaunchKernelEx(&cfg, k_attn_split<KVT, EPL, GM, MMA>, ka);
 }
 
 template <typename KVT, int EPL>
 static cudaError_t launch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
+    if constexpr (sizeof(KVT) == 2 && EPL <= 8) {
+        if (attn_use_mma) {
+            if (ka.G == 1) return launch_split_g<KVT, EPL, 1, true>(lc, ka);
+            if (ka.G == 2) return launch_split_g<KVT, EPL, 2, true>(lc, ka);
+            if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, true>(lc, ka);
+            return launch_split_g<KVT, EPL, 8, true>(lc, ka);
+        }
+    }
     if constexpr (EPL >= 8) {
-        return launch_split_g<KVT, EPL, 1>(lc, ka);  // wide heads: one query head per block keeps registers in bounds
+        return launch_split_g<KVT, EPL, 1, false>(lc, ka);  // wide heads: one query head per block keeps registers in bounds
     } else {
-        if (ka.G == 1) return launch_split_g<KVT, EPL, 1>(lc, ka);
-        if (ka.G == 2) return launch_split_g<KVT, EPL, 2>(lc, ka);
-        if (ka.G <= 4) return launch_split_g<KVT, EPL, 4>(lc, ka);
-        return launch_split_g<KVT, EPL, 8>(lc, ka);
+        if (ka.G == 1) return launch_split_g<KVT, EPL, 1, false>(lc, ka);
+        if (ka.G == 2) return launch_split_g<KVT, EPL, 2, false>(lc, ka);
+        if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, false>(lc, ka);
+        return launch_split_g<KVT, EPL, 8, false>(lc, ka);
     }
 }
 
@@ -529,8 +666,14 @@ static cudaError_t dispatch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
 
 template <typename KVT, int EPL, int GM>
 static cudaError_t opt_in_one() {
-    const size_t smem = AttnSmem<KVT, EPL, GM>::total;
-    return cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AttnSmem<KVT, EPL, GM, false>::total);
+    if constexpr (sizeof(KVT) == 2 && EPL <= 8) {
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)AttnSmem<KVT, EPL, GM, true>::total);
+    }
+    return e;
 }
 template <typename KVT>
 static cudaError_t opt_in_all() {
@@ -539,7 +682,7 @@ static cudaError_t opt_in_all() {
     VB_ATTN_OPT(1, 1); VB_ATTN_OPT(1, 2); VB_ATTN_OPT(1, 4); VB_ATTN_OPT(1, 8);
     VB_ATTN_OPT(2, 1); VB_ATTN_OPT(2, 2); VB_ATTN_OPT(2, 4); VB_ATTN_OPT(2, 8);
     VB_ATTN_OPT(4, 1); VB_ATTN_OPT(4, 2); VB_ATTN_OPT(4, 4); VB_ATTN_OPT(4, 8);
-    VB_ATTN_OPT(8, 1); VB_ATTN_OPT(16, 1);
+    VB_ATTN_OPT(8, 1); VB_ATTN_OPT(8, 2); VB_ATTN_OPT(8, 4); VB_ATTN_OPT(8, 8); VB_ATTN_OPT(16, 1);
 #undef VB_ATTN_OPT
     return cudaSuccess;
 }
