@@ -80,6 +80,26 @@ def test_smollm_135m_prompt128_32_steps():
     assert err <= LOGIT_TOL
 
 
+@pytest.mark.parametrize("mma", [1, 0])
+def test_long_context_crosses_chunk_refills(mma):
+    """A context of ~1400 tokens: every split of the attention kernel walks more than two staged chunks (the
+    refill path of its two K/V buffers), on the tensor-core and on the scalar variant."""
+    spec = SMALL_SPECS[2]  # int4, 8 q / 2 kv heads, head_dim 64
+    n_prompt, n_new = 1390, 12
+    max_seq = n_prompt + n_new + 1
+    ora, _ = H.build_oracle(spec, 31, max_seq)
+    eng = H.build_engine(spec, 31, max_seq)
+    eng.set_option("attn_mma", mma)
+    prompt = H.prompt_tokens(spec, 31, n_prompt)
+    want = ora.generate_greedy(prompt, n_new)
+    got = eng.generate_greedy(prompt, n_new)
+    err = float(np.max(np.abs(eng.logits() - ora.logits)))
+    eng.set_option("attn_mma", 1)
+    eng.close()
+    assert err <= LOGIT_TOL, "logits max-abs %g" % err
+    assert np.array_equal(got, want)
+
+
 def test_eager_graph_and_stepwise_agree():
     """Graph replay, eager launches and host-driven forward_step produce identical tokens and logits."""
     spec = SMALL_SPECS[2]

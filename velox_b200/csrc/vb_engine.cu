@@ -48,6 +48,7 @@ struct vb_ctx {
     void* nccl = nullptr;                 // communicator of the TP group
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
     bool links_open = false, use_links = true;
+    uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
     uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
     float* partial = nullptr;             // [max_batch][d_model] row-parallel partial sums (all-reduced in place)
@@ -327,7 +328,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         g.x = c->hidden; g.dst = c->qkv;
         g.norm_w = c->tensor(VB_ROLE_ATTN_NORM, L).m.data; g.norm_fmt = c->tensor(VB_ROLE_ATTN_NORM, L).m.fmt; g.eps = d.rms_eps;
         g.w = c->tensor(VB_ROLE_WQ, L).m; g.w.rows = c->qkv_rows;
-        g.trace = next_trace(); g.max_ring = c->gemv_ring;
+        g.trace = next_trace(); g.max_ring = c->ring_role[0] ? c->ring_role[0] : c->gemv_ring;
         VB_TRY(gemv(lcfg(c, true), g, c->gemv_path));
         // bias + RoPE + KV append
         __half* kv_layer = c->kv_pool + (size_t)l * c->kv_layer_elems;
@@ -353,7 +354,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         GemvArgs o;
         o.state = state; o.batch = B; o.x = c->attn_out; o.dst = row_dst; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
-        o.trace = next_trace(); o.max_ring = c->gemv_ring;
+        o.trace = next_trace(); o.max_ring = c->ring_role[1] ? c->ring_role[1] : c->gemv_ring;
         VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
         VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
@@ -361,13 +362,13 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         gu.state = state; gu.batch = B; gu.x = c->hidden; gu.dst = c->act; gu.epilogue = EPI_SWIGLU;
         gu.norm_w = c->tensor(VB_ROLE_MLP_NORM, L).m.data; gu.norm_fmt = c->tensor(VB_ROLE_MLP_NORM, L).m.fmt; gu.eps = d.rms_eps;
         gu.w = c->tensor(VB_ROLE_WGATE, L).m; gu.w2 = c->tensor(VB_ROLE_WUP, L).m;
-        gu.trace = next_trace(); gu.max_ring = c->gemv_ring;
+        gu.trace = next_trace(); gu.max_ring = c->ring_role[2] ? c->ring_role[2] : c->gemv_ring;
         VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
         // down projection + residual
         GemvArgs dn;
         dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = row_dst; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
-        dn.trace = next_trace(); dn.max_ring = c->gemv_ring;
+        dn.trace = next_trace(); dn.max_ring = c->ring_role[3] ? c->ring_role[3] : c->gemv_ring;
         VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
         VB_TRY(exchange(2 * l + 1));
     }
@@ -977,6 +978,10 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         return VB_OK;
     }
     if (!strcmp(name, "gemv_ring")) { c->gemv_ring = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "ring_qkv")) { c->ring_role[0] = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "ring_o")) { c->ring_role[1] = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "ring_gu")) { c->ring_role[2] = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "ring_down")) { c->ring_role[3] = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "head_ring")) { c->head_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
