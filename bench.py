@@ -290,7 +290,9 @@ def main():
                    "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1,
                    "tp_exchange": (args.tp_exchange if tp and world > 1 else None)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     # dram read+write of one step: ncu on the 4-layer case of this workload measured 1.006x the
+                     # algorithmic bytes per layer (profiles/k_gemv_q4_imma_llama3-8b_ncu_full.md); scaled by depth
+                     "traffic": int(step_bytes * 1.006), "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
                      "bytes_per_launch": step_bytes},
         "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch},
