@@ -867,12 +867,12 @@ int32_t vb_decode_run(vb_ctx* c, uint32_t n_steps, float* elapsed_ms) {
 
 // Reads (and clears) the device error word that bounded device-side waits set when they expire.
 static int32_t check_device_error(vb_ctx* c) {
+    // callers have synchronised the stream: the mapped word is read in place
     uint32_t* w = nullptr;
-    VB_CUDA(fast_error_word(&w));
-    uint32_t v = 0;
-    VB_CUDA(cudaMemcpy(&v, w, 4, cudaMemcpyDeviceToHost));
+    VB_CUDA(fast_error_word_host(&w));
+    const uint32_t v = *reinterpret_cast<volatile uint32_t*>(w);
     if (v != 0) {
-        cudaMemset(w, 0, 4);
+        *reinterpret_cast<volatile uint32_t*>(w) = 0;
         set_error("a bounded device-side wait expired (code 0x%x): results of the last launches are invalid", v);
         return VB_ERR_TIMEOUT;
     }

@@ -31,6 +31,8 @@
 // Overlap.  Kernels are launched with programmatic stream serialization.  Weights never depend on the
 // previous kernel, so the producer warp starts filling the ring at once, while the consumers trigger their
 // own dependents and only then wait for the producer kernel's x.
+#include <string.h>
+
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
 #include "vb_tma.cuh"
@@ -582,21 +584,29 @@ cudaError_t gemv_fast_init() {
     return cudaSuccess;
 }
 
-// device error word shared by every launch of this process on a device (bounded waits report here)
-static uint32_t* g_err_word[64] = {nullptr};
-static cudaError_t err_word(uint32_t** out) {
+// Error word shared by every launch of this process on a device (bounded waits report here).  It lives in
+// mapped pinned host memory: kernels only ever write it when a wait gives up, and the host reads it after a
+// stream synchronisation without a copy.
+static uint32_t* g_err_word[64] = {nullptr};       // device-side address
+static uint32_t* g_err_word_host[64] = {nullptr};  // the same word as the host sees it
+static cudaError_t err_word(uint32_t** out, uint32_t** out_host) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!g_err_word[dev]) {
-        if ((e = cudaMalloc((void**)&g_err_word[dev], 256)) != cudaSuccess) return e;
-        if ((e = cudaMemset(g_err_word[dev], 0, 256)) != cudaSuccess) return e;
+        uint32_t* h = nullptr;
+        if ((e = cudaHostAlloc((void**)&h, 256, cudaHostAllocMapped)) != cudaSuccess) return e;
+        memset(h, 0, 256);
+        if ((e = cudaHostGetDevicePointer((void**)&g_err_word[dev], h, 0)) != cudaSuccess) return e;
+        g_err_word_host[dev] = h;
     }
-    *out = g_err_word[dev];
+    if (out) *out = g_err_word[dev];
+    if (out_host) *out_host = g_err_word_host[dev];
     return cudaSuccess;
 }
-cudaError_t fast_error_word(uint32_t** out) { return err_word(out); }
+cudaError_t fast_error_word(uint32_t** out) { return err_word(out, nullptr); }
+cudaError_t fast_error_word_host(uint32_t** out) { return err_word(nullptr, out); }
 
 bool fast_use_tma = true;  // vb_set_option("gemv_tma", 0) selects the register-prefetch kernel for batch 1 too
 
@@ -643,7 +653,7 @@ cudaError_t gemv_fast(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
             size_t ns = ((size_t)TMA_MAX_SMEM - fixed) / TMA_STAGE_BYTES;
             if (ns > TMA_MAX_STAGES) ns = TMA_MAX_STAGES;
             f.n_stages = (uint32_t)ns;
-            cudaError_t e = err_word(&f.err);
+            cudaError_t e = err_word(&f.err, nullptr);
             if (e != cudaSuccess) return e;
             *handled = true;
             const size_t tsmem = fixed + ns * TMA_STAGE_BYTES;

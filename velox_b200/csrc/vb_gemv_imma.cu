@@ -73,7 +73,7 @@ __device__ __forceinline__ float im_norm_w(const void* w, int fmt, uint32_t i) {
 // One chunk of 8 consecutive elements of x (already multiplied by the RMSNorm factors) -> the staged form.
 // The four lanes that share a group of 32 agree on its power-of-two scale through shuffles, so all 32
 // lanes of a warp must call this together (`valid` masks the stores).
-__device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, int* __restrict__ sx, float* __restrict__ invp,
+__device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, int2* __restrict__ sxp,
                                                const float v[8], uint32_t c, bool valid) {
     float gmax = 0.0f;
 #pragma unroll
@@ -96,11 +96,15 @@ __device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, i
     s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
     s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
     if (valid) {
-        // group layout: 32 H bytes then 32 L bytes
-        unsigned char* gb = xq + (size_t)(c >> 2) * 64 + (c & 3) * 8;
-        *reinterpret_cast<uint2*>(gb) = make_uint2(hw[0], hw[1]);
-        *reinterpret_cast<uint2*>(gb + 32) = make_uint2(lw[0], lw[1]);
-        if ((c & 3) == 0) { sx[c >> 2] = s; invp[c >> 2] = 1.0f / p; }
+        // group layout: 32 H bytes then 32 L bytes, each plane ordered so that the 8 bytes lane t feeds to the mma
+        // (elements 4t..4t+3 and 16+4t..16+4t+3) are adjacent: element k sits at 8*((k&15)>>2) + 4*(k>>4) + (k&3)
+        const uint32_t q = c & 3;  // which 8 of the group's 32 elements
+        unsigned char* gb = xq + (size_t)(c >> 2) * 64 + (q & 1) * 16 + (q >> 1) * 4;
+        *reinterpret_cast<uint32_t*>(gb) = hw[0];
+        *reinterpret_cast<uint32_t*>(gb + 8) = hw[1];
+        *reinterpret_cast<uint32_t*>(gb + 32) = lw[0];
+        *reinterpret_cast<uint32_t*>(gb + 40) = lw[1];
+        if (q == 0) sxp[c >> 2] = make_int2(s, __float_as_int(1.0f / p));  // the group's sum(X) and 1/p together
     }
 }
 
@@ -143,9 +147,8 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
     unsigned char* ring = smem_raw;                                              // [IM_GROUPS * IM_WARPS][NS][IM_BLK_BYTES]
     unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * IM_BLK_BYTES; // [K/32][64]
-    int* sx = reinterpret_cast<int*>(xq + (size_t)K * 2);                        // [K/32]
-    float* invp = reinterpret_cast<float*>(sx + K / 32);                         // [K/32]
-    float* red = invp + K / 32;                                                  // [IM_GROUPS][2][IM_WARPS][16]
+    int2* sxp = reinterpret_cast<int2*>(xq + (size_t)K * 2);                     // [K/32] {sum(X), 1/p}
+    float* red = reinterpret_cast<float*>(sxp + K / 32);                         // [IM_GROUPS][2][IM_WARPS][16]
     __shared__ float ssq[IM_GROUPS * IM_WARPS];
 
     const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                             for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
                         }
                     }
-                    im_stage_chunk(xq, sx, invp, v, c, valid);
+                    im_stage_chunk(xq, sxp, v, c, valid);
                 }
             }
         }
@@ -256,7 +259,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
     uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
-    const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 4 * t;
+    const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 8 * t;
     for (uint32_t tile = vtile0; tile < n_tiles; tile += vstride, parity ^= 1) {
         // residual rows fetched early so that the epilogue does not wait on them
         float resid = 0.0f;
@@ -274,10 +277,11 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                 const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
                 const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
                 // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
-                const uint32_t bx0 = *reinterpret_cast<const uint32_t*>(xq_lane + (size_t)kk * 256);
-                const uint32_t bx1 = *reinterpret_cast<const uint32_t*>(xq_lane + (size_t)kk * 256 + 16);
-                const int sxt = sx[kk * 4 + t];
-                const float ip = invp[kk * 4 + t];
+                const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kk * 256);
+                const uint32_t bx0 = bx.x, bx1 = bx.y;
+                const int2 sp = sxp[kk * 4 + t];
+                const int sxt = sp.x;
+                const float ip = __int_as_float(sp.y);
                 const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
                 const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
                 int d[4] = {0, 0, 0, 0};

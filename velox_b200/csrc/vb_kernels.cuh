@@ -78,6 +78,7 @@ cudaError_t tile_q4_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, 
 extern bool fast_use_tma;
 extern bool attn_use_mma;
 cudaError_t fast_error_word(uint32_t** out);
+cudaError_t fast_error_word_host(uint32_t** out);
 cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const void* canon, const void* canon_scales,
                     uint32_t rows, uint32_t K);
 
