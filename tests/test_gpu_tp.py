@@ -101,3 +101,24 @@ def test_tp_create_rejects_unsplittable_models():
         Engine(TP_SPEC, max_seq_len=64, tp_rank=0, tp_size=4)      # 2 KV heads over 4 ranks
     with pytest.raises(L.VeloxError):
         Engine(TP_SPEC.scaled(weight_fmt=L.FMT_I8PC), max_seq_len=64, tp_rank=0, tp_size=2)  # per-row int8 scales
+
+
+def test_exchange_poll_is_bounded_and_reported():
+    """A rank whose peers never answer: the exchange kernels give up at their poll limit (50 ms here), the step
+    completes, the host gets VB_ERR_TIMEOUT from the next synchronisation and the context stays usable."""
+    import time
+    from velox_b200.engine import Engine
+    eng = Engine(TP_SPEC, max_seq_len=64, tp_rank=0, tp_size=2)
+    eng.load_synthetic(SEED)
+    eng.set_option("tp_poll_ms", 50)
+    eng.set_option("tp_p2p_standin", 1)  # stand-in regions: nobody pushes into them
+    eng.reserve(0, 16)
+    t0 = time.time()
+    eng.prefill(np.array([1, 2, 3], dtype=np.uint32))  # three steps, 2 exchanges per layer + the argmax exchange
+    with pytest.raises(L.VeloxError) as ei:
+        eng.sync()
+    assert ei.value.code == L.ERR_TIMEOUT
+    assert time.time() - t0 < 20.0   # one poll runs out; the others see the error word and fall through
+    eng.sync()                       # the error was reported once and cleared: the context still answers
+    assert eng.state(0)[1] == 3      # positions advanced (with meaningless tokens)
+    eng.close()

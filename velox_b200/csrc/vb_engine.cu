@@ -47,7 +47,7 @@ struct vb_ctx {
     uint32_t hq = 0, hkv = 0, ffn = 0, ffn_off = 0, vocab = 0, vocab_off = 0;
     void* nccl = nullptr;                 // communicator of the TP group
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
-    bool links_open = false, use_links = true;
+    bool links_open = false, use_links = true, links_standin = false;
     uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
     uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
@@ -536,7 +536,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->graph) cudaGraphDestroy(c->graph);
     if (c->nccl) nccl_comm_destroy(c->nccl);
     for (uint32_t r = 0; r < 8; ++r)
-        if (c->links.base[r] && r != c->links.rank) cudaIpcCloseMemHandle(c->links.base[r]);
+        if (c->links.base[r] && r != c->links.rank) { if (c->links_standin) cudaFree(c->links.base[r]); else cudaIpcCloseMemHandle(c->links.base[r]); }
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs};
@@ -984,6 +984,30 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "ring_down")) { c->ring_role[3] = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "head_ring")) { c->head_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
+    if (!strcmp(name, "tp_poll_ms")) {  // limit of one exchange poll (default ~10 s), at a nominal 2 GHz
+        VB_REQUIRE(value > 0, "vb_set_option: tp_poll_ms must be positive");
+        c->links.poll_clocks = (long long)value * 2000000LL;
+        return VB_OK;
+    }
+    if (!strcmp(name, "tp_p2p_standin")) {
+        // Diagnostic: private stand-in regions take the place of the peers', so nobody ever answers and every
+        // exchange runs into its poll limit -- how the tests exercise the bounded waits without a second GPU.
+        VB_REQUIRE(c->d.tp_size > 1 && c->d.tp_size <= 8 && !c->links_open, "vb_set_option: tp_p2p_standin needs a sharded context without peers");
+        VB_CUDA(cudaSetDevice(c->device));
+        unsigned char handle[64];
+        int32_t rc = vb_tp_p2p_export(c, handle);  // allocates this rank's own region
+        if (rc != VB_OK) return rc;
+        for (uint32_t r = 0; r < c->d.tp_size; ++r) {
+            if (r == c->d.tp_rank) continue;
+            void* p = nullptr;
+            VB_CUDA(cudaMalloc(&p, c->links.bytes));
+            VB_CUDA(cudaMemset(p, 0, c->links.bytes));
+            c->links.base[r] = (unsigned char*)p;
+        }
+        c->links_standin = true;
+        c->links_open = true;
+        return VB_OK;
+    }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "attn_mma")) { attn_use_mma = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
@@ -1074,8 +1098,12 @@ int32_t vb_tp_p2p_close(vb_ctx* c) {
     VB_CUDA(cudaStreamSynchronize(c->stream));
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     for (uint32_t r = 0; r < 8; ++r)
-        if (c->links.base[r] && r != c->links.rank) { cudaIpcCloseMemHandle(c->links.base[r]); c->links.base[r] = nullptr; }
+        if (c->links.base[r] && r != c->links.rank) {
+            if (c->links_standin) cudaFree(c->links.base[r]); else cudaIpcCloseMemHandle(c->links.base[r]);
+            c->links.base[r] = nullptr;
+        }
     c->links_open = false;
+    c->links_standin = false;
     return VB_OK;
 }
 

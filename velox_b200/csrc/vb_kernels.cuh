@@ -34,6 +34,7 @@ struct TpLinks {
     unsigned char* base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     uint32_t rank = 0, size = 1, max_batch = 0, max_pairs = 0;
     uint64_t epoch_off = 0, pair_off = 0, data_off = 0, bytes = 0;
+    long long poll_clocks = 20000000000LL;  // limit of one poll in SM clocks (~10 s): covers host-side skew between ranks
 };
 void tp_links_layout(TpLinks* l, uint32_t rank, uint32_t size, uint32_t max_elems, uint32_t max_batch);
 cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l);

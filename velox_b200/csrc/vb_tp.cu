@@ -16,7 +16,6 @@ namespace vb {
 namespace {
 
 constexpr uint32_t TP_BUFS = 4;
-constexpr long long TP_POLL_CLOCKS = 20000000000LL;  // ~10 s at 2 GHz: covers host-side skew between ranks, still bounded
 
 __device__ __forceinline__ void st_ll(uint4* p, uint32_t a, uint32_t b, uint32_t seq) {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(seq), "r"(b), "r"(seq) : "memory");
@@ -27,7 +26,7 @@ __device__ __forceinline__ uint4 ld_ll(const uint4* p) {
     return v;
 }
 // Polls one slot; false (and the error word set) when the limit is reached.
-__device__ __forceinline__ bool poll_ll(const uint4* p, uint32_t seq, uint4* out, uint32_t* err, uint32_t code) {
+__device__ __forceinline__ bool poll_ll(const uint4* p, uint32_t seq, uint4* out, uint32_t* err, uint32_t code, long long limit) {
     uint4 v = ld_ll(p);
     if (v.y == seq && v.w == seq) { *out = v; return true; }
     const long long t0 = clock64();
@@ -36,7 +35,7 @@ __device__ __forceinline__ bool poll_ll(const uint4* p, uint32_t seq, uint4* out
         if (v.y == seq && v.w == seq) { *out = v; return true; }
         // give up at the limit, or at once when an earlier wait already did (the step is lost anyway)
         const bool lost = (spin & 1023u) == 1023u && *reinterpret_cast<volatile uint32_t*>(err) != 0;
-        if (lost || clock64() - t0 > TP_POLL_CLOCKS) { atomicOr(err, code); *out = make_uint4(0, 0, 0, 0); return false; }
+        if (lost || clock64() - t0 > limit) { atomicOr(err, code); *out = make_uint4(0, 0, 0, 0); return false; }
     }
 }
 
@@ -73,7 +72,7 @@ __global__ void __launch_bounds__(256) k_tp_reduce_ll(TpLinks links, float* __re
         float2 v = mine;
         if (p != links.rank) {
             uint4 raw;
-            poll_ll(recv + p * slot_elems, seq, &raw, err, 0x100u | p);
+            poll_ll(recv + p * slot_elems, seq, &raw, err, 0x100u | p, links.poll_clocks);
             v = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.z));
         }
         acc.x += v.x;
@@ -104,7 +103,7 @@ __global__ void k_tp_argmax_ll(TpLinks links, const uint2* __restrict__ pairs, u
         uint2 c = mine;
         if (p != links.rank) {
             uint4 raw;
-            if (!poll_ll(recv + (size_t)p * links.max_batch, seq, &raw, err, 0x200u | p)) continue;
+            if (!poll_ll(recv + (size_t)p * links.max_batch, seq, &raw, err, 0x200u | p, links.poll_clocks)) continue;
             c = make_uint2(raw.x, raw.z);
         }
         const float v = __uint_as_float(c.x);
