@@ -2,13 +2,18 @@
 //
 // Grid (kv_head x q-head chunk, split, sequence).  A block owns one KV head, the (up to 8) query heads that
 // share it and one slice of the context (a whole number of 16-token KV blocks).  The kernel is latency-bound
-// at decode sizes, so it makes as few dependent memory trips as it can: (1) the sequence's position, (2) the
-// slice's block-table entries together with the query heads, (3) per chunk of up to 64 tokens ALL K and V
-// rows at once, bulk copies (TMA) into two shared-memory buffers, requested before the grid-dependency wait
-// because cached rows do not depend on this step's projections.  Each of the 8 warps then takes 4 or 8 tokens
-// at a time, uses every row for all query heads of the group, reduces the per-lane partial dot products
-// with a transposing butterfly (one value per lane instead of one reduction per value) and keeps an
-// online-softmax state (m, l, acc) per query head.  The splits of one (sequence, head group) form a
+// at decode sizes, so it makes as few dependent memory trips as it can: (1) the sequence's position together
+// with its (short) block-table row, (2) per chunk of up to 64 tokens ALL K and V rows at once, bulk copies
+// (TMA) into two shared-memory buffers, requested before the grid-dependency wait because cached rows do not
+// depend on this step's projections, (3) after the wait only the query heads.
+// fp16 caches: the products run on the tensor cores (mma.sync m16n8k16).  A warp takes 16 tokens: S^T = K Q^T
+// (tokens x heads) and O^T += V^T P^T (dims x heads) put the GROUP's query heads on the N = 8 columns, so a
+// group of 8 fills the instruction and every thread's accumulator columns are the two heads whose running
+// maximum it keeps; K comes in with ldmatrix, V with ldmatrix.trans, P is transposed in registers (movmatrix).
+// fp32 caches (the reference's layout): each warp takes 4 or 8 tokens at a time, uses every row for all query
+// heads of the group, reduces the per-lane partial dot products with a transposing butterfly (one value per
+// lane instead of one reduction per value); online-softmax state (m, l, acc) per query head in fp32 throughout.
+// The splits of one (sequence, head group) form a
 // thread-block cluster: each block pushes slice j of its partial into block j's shared memory (distributed
 // shared memory stores) and, after one cluster barrier, every block merges its slice of the head dimension
 // locally -- no global round trip, no atomics, a fixed merge order.
@@ -212,9 +217,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     }
 
     // Chunk c = tokens [t_lo + c*CH, +CH) of the slice, fetched by bulk copies (TMA) into buffer c & 1 and
-    // announced on that buffer's transaction barrier: in the paged pool one copy moves the 16 cached rows of a
-    // KV block (K or V) for this head, so a 64-token chunk is 8 copies issued by 8 threads -- the block table
-    // entry each needs is read by the issuing thread itself.  The contiguous layout takes one copy per row.
+    // announced on that buffer's transaction barrier.  Scalar path on the paged pool: one copy moves the 16 cached
+    // rows of a KV block (K or V) for this head.  Tensor-core path (rows padded in shared memory) and contiguous
+    // layout: one copy per row.  Each copy is issued by a different thread of the block.
     // Called by the whole block; `rot` rotates the threads so that two chunks requested back to back use
     // different ones (their block-table reads then overlap instead of queueing behind one another).
     auto stage_chunk = [&](uint32_t c, uint32_t buf, uint32_t rot) {

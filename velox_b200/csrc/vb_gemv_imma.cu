@@ -21,13 +21,19 @@
 // element 4t+b of the group in its low nibble and element 16+4t+b in its high nibble -- the A fragment of
 // m16n8k32 after the two ANDs.  At byte 1024 + 4*L: half2(scale[row g][group t], scale[row g+8][group t]).
 //
-// Data movement.  Blocks are persistent (two per SM, 8 warps); the 8 warps split the K extent of the current
-// 16-row tile.  Each warp streams ITS blocks through a private shared-memory ring with cp.async (16-byte
-// asynchronous copies that bypass L1 and need no registers): ~130 KB per SM stay in flight, which is what it
-// takes to pull >6 TB/s, and the data path has no block-wide barrier and no spin-wait at all.  (A ring fed by
-// one producer thread with cp.async.bulk + mbarriers measured ~4.4 TB/s at any depth on this part and was
-// dropped here.)  Kernels are launched with programmatic stream serialization: weights never depend on the
-// previous kernel, so every warp fills its ring BEFORE the grid-dependency wait and only then reads x.
+// Data movement.  Blocks are persistent, one of 16 warps per SM: two groups of 8 warps, each group on its own
+// 16-row tile whose K extent its 8 warps split; both groups share one staged copy of x.  Each warp streams ITS
+// blocks through a private shared-memory ring with cp.async (16-byte asynchronous copies that bypass L1 and
+// need no registers); the data path has no block-wide barrier and no spin-wait at all.  Four slots per warp
+// (three blocks in flight, ~55 KB per SM) measured fastest: rings of 6 to 12 slots were each slower in the
+// captured graph, 3 and 2 slower too.  (A ring fed by one producer thread with cp.async.bulk + mbarriers measured
+// ~4.4 TB/s at any depth on this part and was dropped here.)  Kernels are launched with programmatic stream
+// serialization: weights never depend on the previous kernel, so every warp fills its ring BEFORE the
+// grid-dependency wait and only then reads x.
+//
+// The inner loop is instruction-bound (ALU pipe 53 % busy at 42 % of DRAM peak in isolation, ~149 warp
+// instructions per 16x128 block): anything added per block shows up directly -- a generalised block cursor for
+// multi-product launches or for splitting a last partial tile round cost more than it saved.
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
 
@@ -138,7 +144,7 @@ __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w,
 // grid: one persistent block of 16 warps per SM.  The block stages x once (all 512 threads) and then works as
 // two independent groups of 8 warps, each on its own row tile; each warp streams its own blocks through a
 // private ring of NS slots with cp.async (16-byte asynchronous copies, L1 bypassed): no block-wide
-// synchronisation on the data path, ~130 KB per SM in flight, started before the grid-dependency wait.
+// synchronisation on the data path, ring filled before the grid-dependency wait.
 // (Two blocks of 8 warps per SM move the same bytes but each stages its own copy of x: twice the L2 reads
 // and twice the conversion work in the serial part of the kernel.)
 template <int NS>
