@@ -98,9 +98,11 @@ def is_tp(name: str) -> bool:
 
 
 def workload_spec(name: str):
-    from velox_b200.modelspec import LLAMA3_8B_INT4, QWEN2_72B_INT4
+    from velox_b200.modelspec import LLAMA3_8B_INT4, QWEN2_72B_INT4, QWEN25_7B_INT8
     if name == "llama3-8b-int4-bs1":
         return LLAMA3_8B_INT4, 1
+    if name == "qwen2.5-7b-int8-bs1":  # the int8 per-channel model shape, one sequence
+        return QWEN25_7B_INT8, 1
     if name == "qwen2-72b-int4-tp-bs1":
         return QWEN2_72B_INT4, 1
     if name == "qwen2-72b-int4-tp-bs1-8layers":  # quick check of the sharded path
@@ -285,7 +287,8 @@ def main():
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len,
-                   "weights": "int4 g32 + fp16 scales, fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
+                   "weights": ("int8 per output channel + fp16 scales" if "int8" in spec.name else "int4 g32 + fp16 scales") +
+                              ", fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
                    "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),
                    "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1,
                    "tp_exchange": (args.tp_exchange if tp and world > 1 else None)},

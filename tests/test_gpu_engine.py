@@ -24,6 +24,8 @@ SMALL_SPECS = [
                           weight_fmt=L.FMT_Q4G64REF, head_fmt=L.FMT_Q4G64REF, embed_fmt=L.FMT_Q4G64REF, tied_lm_head=True),
     LLAMA3_8B_INT4.scaled(name="llama-bf16-small", d_model=256, n_layers=2, n_q_heads=4, n_kv_heads=4, head_dim=64, ffn_dim=512, vocab=1024,
                           weight_fmt=L.FMT_BF16, head_fmt=L.FMT_BF16, embed_fmt=L.FMT_BF16),
+    # int8 per-channel in shapes the integer tensor-core kernel tiles (K multiples of 128, rows of 16)
+    QWEN25_7B_INT8.scaled(name="qwen-int8-tiled", d_model=512, n_layers=3, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1408, vocab=4096),
 ]
 
 

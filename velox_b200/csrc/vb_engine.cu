@@ -147,7 +147,7 @@ void set_tied_head(vb_ctx* c) {
     h.m.rows = c->vocab;
     h.m.data = (const unsigned char*)h.m.data + wmat_data_bytes(h.m.fmt, c->vocab_off, h.m.cols);
     if (h.m.scales) h.m.scales = (const unsigned char*)h.m.scales + wmat_scale_bytes(h.m.fmt, c->vocab_off, h.m.cols);
-    h.m.tiled = h.m.tiled_scales = h.m.v3 = nullptr;
+    h.m.tiled = h.m.tiled_scales = h.m.v3 = h.m.v3_scales = nullptr;
 }
 
 // Lay the arena out in execution order.  Wq|Wk|Wv (and their scales) are adjacent so that the fused QKV
@@ -155,13 +155,13 @@ void set_tied_head(vb_ctx* c) {
 int32_t plan_arena(vb_ctx* c) {
     uint64_t off = 0;
     // pass 1: compute offsets; pass 2 (after allocation) turns them into pointers
-    struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales, v3; bool has_tiled; };
+    struct Slot { int role, layer; uint64_t data, scales, tiled, tiled_scales, v3; bool has_tiled; uint64_t v3_scales = ~0ULL; };
     std::vector<Slot> slots;
     std::vector<uint64_t> swiglu_off, swiglu_v3_off;
     const bool lean = (c->d.flags & VB_FLAG_LEAN_WEIGHTS) != 0;
     auto add_group = [&](std::initializer_list<int> roles, int layer) {
         std::vector<Slot> g;
-        bool tile_all = true;
+        bool tile_all = true, i8_all = true;  // all members int4 g32 / all int8 per-channel, in tileable shapes
         for (int role : roles) {
             uint32_t rows, cols; int32_t fmt;
             if (!role_shape(c, role, &rows, &cols, &fmt)) continue;
@@ -169,9 +169,10 @@ int32_t plan_arena(vb_ctx* c) {
             t.m.fmt = fmt; t.m.rows = rows; t.m.cols = cols;
             g.push_back({role, layer, ~0ULL, ~0ULL, 0, 0, ~0ULL, false});
             if (fmt != VB_FMT_Q4G32 || !tile_q4_supported(rows, cols)) tile_all = false;
+            if (fmt != VB_FMT_I8PC || !tile_q4_supported(rows, cols)) i8_all = false;
         }
         if (g.empty()) return;
-        const bool lean_group = lean && tile_all;  // only the integer tensor-core layout is kept
+        const bool lean_group = lean && (tile_all || i8_all);  // only the integer tensor-core layout is kept
         auto packed_bytes = [&](const Slot& s) {
             const Tensor& t = c->tensor(s.role, s.layer);
             return wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols) + wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols);
@@ -203,6 +204,12 @@ int32_t plan_arena(vb_ctx* c) {
                 off = align256(off);
             }
         }
+        if (i8_all) {
+            // int8: the members' blocks back to back (fused QKV = one tiled matrix), then their row scales back to back
+            for (Slot& s : g) { const Tensor& t = c->tensor(s.role, s.layer); s.v3 = off; off += wmat_data_bytes(t.m.fmt, t.m.rows, t.m.cols); }
+            for (Slot& s : g) { const Tensor& t = c->tensor(s.role, s.layer); s.v3_scales = off; off += wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols); }
+            off = align256(off);
+        }
         for (Slot& s : g) slots.push_back(s);
     };
     for (uint32_t l = 0; l < c->d.n_layers; ++l) {
@@ -227,6 +234,11 @@ int32_t plan_arena(vb_ctx* c) {
                 swiglu_v3_off.push_back(off);
                 off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
                 off = align256(off);
+            } else if (tg.m.fmt == VB_FMT_I8PC && tile_q4_supported(tg.m.rows, tg.m.cols)) {
+                swiglu_off.push_back(~0ULL);
+                swiglu_v3_off.push_back(off);  // 2*rows x cols of blocks, then 2*rows scales
+                off += 2 * (wmat_data_bytes(tg.m.fmt, tg.m.rows, tg.m.cols) + wmat_scale_bytes(tg.m.fmt, tg.m.rows, tg.m.cols));
+                off = align256(off);
             } else {
                 swiglu_off.push_back(~0ULL);
                 swiglu_v3_off.push_back(~0ULL);
@@ -246,6 +258,7 @@ int32_t plan_arena(vb_ctx* c) {
         t.m.scales = (s.scales != ~0ULL && wmat_scale_bytes(t.m.fmt, t.m.rows, t.m.cols)) ? c->arena + s.scales : nullptr;
         if (s.has_tiled) { t.m.tiled = c->arena + s.tiled; t.m.tiled_scales = c->arena + s.tiled_scales; }
         if (s.v3 != ~0ULL) t.m.v3 = c->arena + s.v3;
+        if (s.v3_scales != ~0ULL) t.m.v3_scales = c->arena + s.v3_scales;
     }
     for (uint32_t l = 0; l < c->d.n_layers; ++l) {
         if (swiglu_off[l] != ~0ULL) c->tensor(VB_ROLE_WGATE, (int)l).m.tiled_swiglu = c->arena + swiglu_off[l];
@@ -601,13 +614,19 @@ static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer, co
     LaunchCfg lc = lcfg(c, false);
     lc.counter = nullptr;
     if (t->m.tiled) VB_CUDA(tile_q4(lc, const_cast<void*>(t->m.tiled), const_cast<void*>(t->m.tiled_scales), cn.data, cn.scales, t->m.rows, t->m.cols));
-    if (t->m.v3) VB_CUDA(tile_q4_v3(lc, const_cast<void*>(t->m.v3), cn.data, cn.scales, t->m.rows, t->m.cols));
+    if (t->m.v3 && t->m.fmt == VB_FMT_Q4G32) VB_CUDA(tile_q4_v3(lc, const_cast<void*>(t->m.v3), cn.data, cn.scales, t->m.rows, t->m.cols));
+    if (t->m.v3 && t->m.fmt == VB_FMT_I8PC)
+        VB_CUDA(tile_i8_v3(lc, const_cast<void*>(t->m.v3), const_cast<void*>(t->m.v3_scales), cn.data, cn.scales, t->m.rows, t->m.cols));
     if (role == VB_ROLE_WGATE || role == VB_ROLE_WUP) {
         const int which = role == VB_ROLE_WUP ? 1 : 0;
         const void* il = c->tensor(VB_ROLE_WGATE, layer).m.tiled_swiglu;
         if (il) VB_CUDA(tile_q4_swiglu(lc, const_cast<void*>(il), cn.data, cn.scales, t->m.rows, t->m.cols, which));
         const void* il3 = c->tensor(VB_ROLE_WGATE, layer).m.v3_swiglu;
-        if (il3) VB_CUDA(tile_q4_v3_swiglu(lc, const_cast<void*>(il3), cn.data, cn.scales, t->m.rows, t->m.cols, which));
+        if (il3 && t->m.fmt == VB_FMT_Q4G32) VB_CUDA(tile_q4_v3_swiglu(lc, const_cast<void*>(il3), cn.data, cn.scales, t->m.rows, t->m.cols, which));
+        if (il3 && t->m.fmt == VB_FMT_I8PC) {
+            unsigned char* sc = (unsigned char*)const_cast<void*>(il3) + 2 * wmat_data_bytes(t->m.fmt, t->m.rows, t->m.cols);
+            VB_CUDA(tile_i8_v3_swiglu(lc, const_cast<void*>(il3), sc, cn.data, cn.scales, t->m.rows, t->m.cols, which));
+        }
     }
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;

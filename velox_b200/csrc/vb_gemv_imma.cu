@@ -42,12 +42,14 @@ namespace vb {
 constexpr int IM_WARPS = 8;                              // warps that share one 16-row tile (they split its K extent)
 constexpr int IM_GROUPS = 2;                             // tile groups per block: they share the staged x, nothing else
 constexpr int IM_CONSUMERS = IM_GROUPS * IM_WARPS * 32;  // threads per block
-constexpr int IM_BLK_BYTES = 1152;
-constexpr int IM_STAGE_BYTES = IM_GROUPS * IM_WARPS * IM_BLK_BYTES;  // one ring slot of every warp
+constexpr int IM_BLK_BYTES = 1152;     // int4: 16 rows x 128 columns of nibbles + the block's 64 fp16 scales
+constexpr int IM_BLK_BYTES_I8 = 2048;  // int8 per-channel: 16 rows x 128 columns of bytes (row scales live apart)
 constexpr int IM_MAX_SMEM = 216 * 1024;
+template <bool I8> struct ImBlk { static constexpr int bytes = I8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES; };
 
 struct ImmaArgs {
     const unsigned char* w;  // v3 tile-major blocks
+    const __half* wscales;   // int8 weights: one scale per row, in tile order
     uint32_t rows, K;        // rows of the (possibly gate/up-interleaved) matrix
     const float* x;
     float* dst;
@@ -133,12 +135,18 @@ struct BlockCursor {
 };
 
 // One warp requests one block (1152 bytes) into its private ring slot: 72 asynchronous 16-byte copies.
+template <bool I8>
 __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w, uint32_t KT, const BlockCursor& cur, uint32_t slot_smem,
                                             uint32_t lane) {
-    const unsigned char* src = w + ((size_t)cur.tile * KT + cur.kk) * IM_BLK_BYTES;
+    const unsigned char* src = w + ((size_t)cur.tile * KT + cur.kk) * ImBlk<I8>::bytes;
     cp_async16(slot_smem + lane * 16, src + lane * 16);
     cp_async16(slot_smem + 512 + lane * 16, src + 512 + lane * 16);
-    if (lane < 8) cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
+    if constexpr (I8) {
+        cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
+        cp_async16(slot_smem + 1536 + lane * 16, src + 1536 + lane * 16);
+    } else {
+        if (lane < 8) cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
+    }
 }
 
 // grid: one persistent block of 16 warps per SM.  The block stages x once (all 512 threads) and then works as
@@ -147,12 +155,16 @@ __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w,
 // synchronisation on the data path, ring filled before the grid-dependency wait.
 // (Two blocks of 8 warps per SM move the same bytes but each stages its own copy of x: twice the L2 reads
 // and twice the conversion work in the serial part of the kernel.)
-template <int NS>
+// I8 selects the int8 per-channel weight format: blocks of 2048 bytes whose 16-byte pieces ARE the A fragments
+// (lane L of k-step j at 512*j + 16*L: rows g and g+8, columns 4t..4t+3 and 16+4t..16+4t+3 of the step), no
+// unpacking and no per-group weight scale -- the row scale is applied once in the epilogue.
+template <int NS, bool I8>
 __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
+    constexpr int BLK = ImBlk<I8>::bytes;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
     unsigned char* ring = smem_raw;                                              // [IM_GROUPS * IM_WARPS][NS][IM_BLK_BYTES]
-    unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * IM_BLK_BYTES; // [K/32][64]
+    unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * BLK;          // [K/32][64]
     int2* sxp = reinterpret_cast<int2*>(xq + (size_t)K * 2);                     // [K/32] {sum(X), 1/p}
     float* red = reinterpret_cast<float*>(sxp + K / 32);                         // [IM_GROUPS][2][IM_WARPS][16]
     __shared__ float ssq[IM_GROUPS * IM_WARPS];
@@ -165,13 +177,13 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     pdl_launch_dependents();
 
     // ---- prologue: weights do not depend on the previous kernel; fill the ring before waiting for x ----------
-    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)wid * NS * IM_BLK_BYTES);
+    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)wid * NS * BLK);
     BlockCursor icur{vtile0, warp};  // next block to request
     uint32_t issued = 0;
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
 #pragma unroll
     for (int i = 0; i < NS - 1; ++i) {
-        if (icur.valid(n_tiles)) { issue_block(a.w, KT, icur, my_ring + (issued % NS) * IM_BLK_BYTES, lane); icur.advance(KT, warp); ++issued; }
+        if (icur.valid(n_tiles)) { issue_block<I8>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
         cp_async_commit();
     }
 
@@ -270,39 +282,55 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         // residual rows fetched early so that the epilogue does not wait on them
         float resid = 0.0f;
         if (a.epilogue == EPI_RESIDUAL && gt < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + gt];
+        float row_scale = 1.0f;
+        if (I8 && gt < 16) row_scale = __half2float(a.wscales[(size_t)tile * 16 + gt]);
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
         for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
-            if (icur.valid(n_tiles)) { issue_block(a.w, KT, icur, my_ring + (issued % NS) * IM_BLK_BYTES, lane); icur.advance(KT, warp); ++issued; }
+            if (icur.valid(n_tiles)) { issue_block<I8>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
             cp_async_commit();
             cp_async_wait<NS - 1>();
             __syncwarp();
             if (active) {
-                const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * IM_BLK_BYTES;
-                const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
-                const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
-                const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
+                const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * BLK;
                 // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
                 const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kk * 256);
                 const uint32_t bx0 = bx.x, bx1 = bx.y;
                 const int2 sp = sxp[kk * 4 + t];
                 const int sxt = sp.x;
                 const float ip = __int_as_float(sp.y);
-                const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
-                const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
                 int d[4] = {0, 0, 0, 0};
+                if constexpr (I8) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t msk = 0x0F0F0F0Fu;
-                    const uint32_t b0 = (gj == (uint32_t)j) ? bx0 : 0u, b1 = (gj == (uint32_t)j) ? bx1 : 0u;
-                    imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, b0, b1, d);
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const uint4 af = reinterpret_cast<const uint4*>(blk + jj * 512)[lane];
+                        const uint32_t b0 = (gj == (uint32_t)jj) ? bx0 : 0u, b1 = (gj == (uint32_t)jj) ? bx1 : 0u;
+                        imma_16832(d, af.x, af.y, af.z, af.w, b0, b1, d);
+                    }
+                    // lane (g,t): exact sums of q * X over group t for rows g and g+8 (no zero point)
+                    const int r0 = d[0] * 256 + d[1];
+                    const int r1 = d[2] * 256 + d[3];
+                    acc0 = fmaf((float)r0, ip, acc0);
+                    acc1 = fmaf((float)r1, ip, acc1);
+                } else {
+                    const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
+                    const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
+                    const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
+                    const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
+                    const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t msk = 0x0F0F0F0Fu;
+                        const uint32_t b0 = (gj == (uint32_t)j) ? bx0 : 0u, b1 = (gj == (uint32_t)j) ? bx1 : 0u;
+                        imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, b0, b1, d);
+                    }
+                    // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
+                    const int r0 = d[0] * 256 + d[1] - 8 * sxt;
+                    const int r1 = d[2] * 256 + d[3] - 8 * sxt;
+                    const float2 s2 = __half22float2(sc);
+                    acc0 = fmaf((float)r0 * ip, s2.x, acc0);
+                    acc1 = fmaf((float)r1 * ip, s2.y, acc1);
                 }
-                // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
-                const int r0 = d[0] * 256 + d[1] - 8 * sxt;
-                const int r1 = d[2] * 256 + d[3] - 8 * sxt;
-                const float2 s2 = __half22float2(sc);
-                acc0 = fmaf((float)r0 * ip, s2.x, acc0);
-                acc1 = fmaf((float)r1 * ip, s2.y, acc1);
             }
             __syncwarp();  // every lane is done with the slot before the next iteration overwrites its predecessor
         }
@@ -317,6 +345,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < IM_WARPS; ++w) v += rbuf[w * 16 + gt];
+            if constexpr (I8) v *= row_scale;
             if (a.epilogue == EPI_SWIGLU) {
                 // tile = 8 gate rows (mma rows 0..7) over the same 8 up rows (mma rows 8..15)
                 const float up = __shfl_down_sync(0x0000FFFFu, v, 8);
@@ -394,22 +423,47 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
     return tile_v3_half(lc, tiled, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
 }
 
-cudaError_t gemv_imma_init() {
+template <bool I8>
+static cudaError_t imma_opt_in() {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<10>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_gemv_q4_imma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_gemv_q4_imma<2, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+}
+cudaError_t gemv_imma_init() {
+    cudaError_t e = imma_opt_in<false>();
+    return e != cudaSuccess ? e : imma_opt_in<true>();
 }
 
 bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
 
+template <bool I8>
+static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t max_ring) {
+    const size_t fixed = (size_t)f.K * 2 + (size_t)(f.K / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
+    const size_t stage = (size_t)IM_GROUPS * IM_WARPS * ImBlk<I8>::bytes;  // one ring slot of every warp
+    if (fixed + 2 * stage > (size_t)IM_MAX_SMEM) return cudaErrorInvalidConfiguration;
+    size_t ns = ((size_t)IM_MAX_SMEM - fixed) / stage;
+    if (max_ring >= 2 && ns > max_ring) ns = max_ring;
+    ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : 2);  // ring depth per warp (template parameter); 4 measured fastest
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    const uint32_t n_tiles = f.rows / 16;
+    const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
+    const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
+    const size_t smem = fixed + ns * stage;
+    if (ns == 8) return launch(lc, k_gemv_q4_imma<8, I8>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 4) return launch(lc, k_gemv_q4_imma<4, I8>, grid, dim3(IM_CONSUMERS), smem, f);
+    return launch(lc, k_gemv_q4_imma<2, I8>, grid, dim3(IM_CONSUMERS), smem, f);
+}
+
 cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     *handled = false;
-    if (!imma_enabled || a.batch != 1 || a.w.fmt != VB_FMT_Q4G32) return cudaSuccess;
+    const bool i8 = a.w.fmt == VB_FMT_I8PC;
+    if (!imma_enabled || a.batch != 1 || !(a.w.fmt == VB_FMT_Q4G32 || i8)) return cudaSuccess;
     const bool swiglu = a.epilogue == EPI_SWIGLU;
     const void* w = swiglu ? a.w.v3_swiglu : a.w.v3;
     if (!w || a.w.cols % 128 != 0) return cudaSuccess;
@@ -417,33 +471,65 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     const uint32_t rows = swiglu ? 2 * a.w.rows : a.w.rows;
     if (rows % 16 != 0) return cudaSuccess;
     const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
-    if (fixed + 2 * (size_t)IM_STAGE_BYTES > (size_t)IM_MAX_SMEM) return cudaSuccess;
-    size_t ns = ((size_t)IM_MAX_SMEM - fixed) / IM_STAGE_BYTES;
-    if (a.max_ring >= 2 && ns > a.max_ring) ns = a.max_ring;
-    ns = ns >= 12 ? 12 : (ns >= 10 ? 10 : (ns >= 8 ? 8 : (ns >= 6 ? 6 : (ns >= 4 ? 4 : (ns >= 3 ? 3 : 2)))));  // ring depth per warp (template parameter)
+    if (fixed + 2 * (size_t)IM_GROUPS * IM_WARPS * (i8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES) > (size_t)IM_MAX_SMEM) return cudaSuccess;
     ImmaArgs f;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
+    // int8: the row scales follow the blocks of the (whole, possibly fused or interleaved) matrix
+    f.wscales = i8 ? reinterpret_cast<const __half*>((const unsigned char*)w + (size_t)rows * a.w.cols) : nullptr;
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
     f.dst_offset = a.dst_offset; f.epilogue = a.epilogue;
     f.trace = a.trace;
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
-    }
-    const uint32_t n_tiles = rows / 16;
     *handled = true;
-    const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
-    const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
-    const size_t smem = fixed + ns * IM_STAGE_BYTES;
-    if (ns == 12) return launch(lc, k_gemv_q4_imma<12>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 10) return launch(lc, k_gemv_q4_imma<10>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 8) return launch(lc, k_gemv_q4_imma<8>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 6) return launch(lc, k_gemv_q4_imma<6>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 4) return launch(lc, k_gemv_q4_imma<4>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 3) return launch(lc, k_gemv_q4_imma<3>, grid, dim3(IM_CONSUMERS), smem, f);
-    return launch(lc, k_gemv_q4_imma<2>, grid, dim3(IM_CONSUMERS), smem, f);
+    return i8 ? imma_launch<true>(lc, f, a.max_ring) : imma_launch<false>(lc, f, a.max_ring);
+}
+
+// ---- int8 per-channel: canonical [rows][K] bytes + fp16 row scales -> tile-major blocks, then the scales ----
+// one thread per output word (4 consecutive k of one row)
+__global__ void k_tile_i8_v3(uint32_t* __restrict__ out, const uint32_t* __restrict__ canon, uint32_t n_tiles, uint32_t K,
+                             uint32_t rows_per_tile, uint32_t row_off, uint32_t half) {
+    const uint32_t KT = K / 128;
+    const uint64_t n = (uint64_t)n_tiles * KT * 256;  // words of one half (8 rows) of every block
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        // i -> (block, k-step j, lane L, upper/lower column half c)
+        const uint32_t c = i & 1, L = (i >> 1) & 31, j = (i >> 6) & 3;
+        const uint64_t blk = i >> 8;
+        const uint32_t kt = blk % KT, rt = blk / KT, g = L >> 2, t = L & 3;
+        const uint64_t row = (uint64_t)rt * rows_per_tile + row_off + g;
+        const uint32_t k = kt * 128 + j * 32 + c * 16 + 4 * t;
+        // fragment register r = 2*c + half: rows g (half 0) / g+8 (half 1), columns 4t.. (c 0) / 16+4t.. (c 1)
+        out[blk * (IM_BLK_BYTES_I8 / 4) + j * 128 + L * 4 + 2 * c + half] = canon[(row * K + k) >> 2];
+    }
+}
+__global__ void k_tile_i8_scales(__half* __restrict__ out, const __half* __restrict__ canon, uint32_t n_tiles, uint32_t rows_per_tile,
+                                 uint32_t row_off, uint32_t half) {
+    const uint32_t n = n_tiles * 8;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const uint32_t g = i & 7, rt = i >> 3;
+        out[(size_t)rt * 16 + half * 8 + g] = canon[(size_t)rt * rows_per_tile + row_off + g];
+    }
+}
+static cudaError_t tile_i8_half(const LaunchCfg& lc, void* blocks, void* scales, const void* canon, const void* canon_scales,
+                                uint32_t n_tiles, uint32_t K, uint32_t rows_per_tile, uint32_t row_off, uint32_t half) {
+    const uint64_t nw = (uint64_t)n_tiles * (K / 128) * 256;
+    unsigned nb = (unsigned)((nw + 255) / 256 > 148 * 32 ? 148 * 32 : (nw + 255) / 256);
+    cudaError_t e = launch(lc, k_tile_i8_v3, dim3(nb), dim3(256), 0, (uint32_t*)blocks, (const uint32_t*)canon, n_tiles, K, rows_per_tile,
+                           row_off, half);
+    if (e != cudaSuccess) return e;
+    nb = (n_tiles * 8 + 255) / 256;
+    return launch(lc, k_tile_i8_scales, dim3(nb ? nb : 1), dim3(256), 0, (__half*)scales, (const __half*)canon_scales, n_tiles, rows_per_tile,
+                  row_off, half);
+}
+// plain matrix: tile i = rows 16i..16i+15
+cudaError_t tile_i8_v3(const LaunchCfg& lc, void* blocks, void* scales, const void* canon, const void* canon_scales, uint32_t rows,
+                       uint32_t K) {
+    cudaError_t e = tile_i8_half(lc, blocks, scales, canon, canon_scales, rows / 16, K, 16, 0, 0);
+    if (e != cudaSuccess) return e;
+    return tile_i8_half(lc, blocks, scales, canon, canon_scales, rows / 16, K, 16, 8, 1);
+}
+// gate (which = 0) or up (which = 1) into the interleaved SwiGLU matrix: tile i = gate rows 8i..8i+7 | up rows 8i..8i+7
+cudaError_t tile_i8_v3_swiglu(const LaunchCfg& lc, void* blocks, void* scales, const void* canon, const void* canon_scales, uint32_t rows,
+                              uint32_t K, int which) {
+    return tile_i8_half(lc, blocks, scales, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
 }
 
 }  // namespace vb

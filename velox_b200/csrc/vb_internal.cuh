@@ -47,7 +47,10 @@ struct WMat {
     // gate matrices only: gate and up interleaved 8 rows by 8 rows in one tile-major matrix of 2*rows rows
     const void* tiled_swiglu = nullptr;
     // the same two copies in the byte-per-nibble-pair block layout of the integer tensor-core kernel (vb_gemv_imma.cu)
+    // (int8 per-channel weights: v3 = 2048-byte blocks; the row scales of the whole matrix follow its last block,
+    // v3_scales points at this tensor's slice of them -- used while loading)
     const void* v3 = nullptr;
+    const void* v3_scales = nullptr;
     const void* v3_swiglu = nullptr;
 };
 

@@ -86,6 +86,10 @@ cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const 
 // vb_gemv_imma.cu
 cudaError_t gemv_imma_init();
 cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled);
+cudaError_t tile_i8_v3(const LaunchCfg& lc, void* blocks, void* scales, const void* canon, const void* canon_scales, uint32_t rows,
+                       uint32_t K);
+cudaError_t tile_i8_v3_swiglu(const LaunchCfg& lc, void* blocks, void* scales, const void* canon, const void* canon_scales, uint32_t rows,
+                              uint32_t K, int which);
 cudaError_t tile_q4_v3(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K);
 cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K,
                               int which);
