@@ -1027,6 +1027,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         c->links_open = true;
         return VB_OK;
     }
+    if (!strcmp(name, "gemv_pair_ring")) { imma_pair_ring = (int)value; return VB_OK; }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "attn_mma")) { attn_use_mma = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }

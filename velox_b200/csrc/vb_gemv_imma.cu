@@ -45,7 +45,9 @@ constexpr int IM_CONSUMERS = IM_GROUPS * IM_WARPS * 32;  // threads per block
 constexpr int IM_BLK_BYTES = 1152;     // int4: 16 rows x 128 columns of nibbles + the block's 64 fp16 scales
 constexpr int IM_BLK_BYTES_I8 = 2048;  // int8 per-channel: 16 rows x 128 columns of bytes (row scales live apart)
 constexpr int IM_MAX_SMEM = 216 * 1024;
-template <bool I8> struct ImBlk { static constexpr int bytes = I8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES; };
+// kernel flavours: int4 one block per step, int8, int4 two consecutive k-blocks per step (halves the per-step overhead)
+enum { IM_Q4 = 0, IM_I8 = 1, IM_Q4X2 = 2 };
+template <int W> struct ImBlk { static constexpr int bytes = W == IM_I8 ? IM_BLK_BYTES_I8 : (W == IM_Q4X2 ? 2 * IM_BLK_BYTES : IM_BLK_BYTES); };
 
 struct ImmaArgs {
     const unsigned char* w;  // v3 tile-major blocks
@@ -135,15 +137,20 @@ struct BlockCursor {
 };
 
 // One warp requests one block (1152 bytes) into its private ring slot: 72 asynchronous 16-byte copies.
-template <bool I8>
+// `KT` and `cur.kk` count steps: blocks, or pairs of blocks for IM_Q4X2 (a pair is contiguous in memory)
+template <int W>
 __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w, uint32_t KT, const BlockCursor& cur, uint32_t slot_smem,
                                             uint32_t lane) {
-    const unsigned char* src = w + ((size_t)cur.tile * KT + cur.kk) * ImBlk<I8>::bytes;
+    const unsigned char* src = w + ((size_t)cur.tile * KT + cur.kk) * ImBlk<W>::bytes;
     cp_async16(slot_smem + lane * 16, src + lane * 16);
     cp_async16(slot_smem + 512 + lane * 16, src + 512 + lane * 16);
-    if constexpr (I8) {
+    if constexpr (W == IM_I8) {
         cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
         cp_async16(slot_smem + 1536 + lane * 16, src + 1536 + lane * 16);
+    } else if constexpr (W == IM_Q4X2) {
+        cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
+        cp_async16(slot_smem + 1536 + lane * 16, src + 1536 + lane * 16);
+        if (lane < 16) cp_async16(slot_smem + 2048 + lane * 16, src + 2048 + lane * 16);
     } else {
         if (lane < 8) cp_async16(slot_smem + 1024 + lane * 16, src + 1024 + lane * 16);
     }
@@ -158,11 +165,13 @@ __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w,
 // I8 selects the int8 per-channel weight format: blocks of 2048 bytes whose 16-byte pieces ARE the A fragments
 // (lane L of k-step j at 512*j + 16*L: rows g and g+8, columns 4t..4t+3 and 16+4t..16+4t+3 of the step), no
 // unpacking and no per-group weight scale -- the row scale is applied once in the epilogue.
-template <int NS, bool I8>
+template <int NS, int W>
 __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
-    constexpr int BLK = ImBlk<I8>::bytes;
+    constexpr int BLK = ImBlk<W>::bytes;
+    constexpr bool I8 = W == IM_I8;
+    constexpr int SUB = W == IM_Q4X2 ? 2 : 1;  // 16x128 blocks per ring slot / loop step
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
+    const uint32_t K = a.K, KT = K / (128 * SUB), n_tiles = a.rows / 16;  // KT: steps along K of one tile
     unsigned char* ring = smem_raw;                                              // [IM_GROUPS * IM_WARPS][NS][IM_BLK_BYTES]
     unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * BLK;          // [K/32][64]
     int2* sxp = reinterpret_cast<int2*>(xq + (size_t)K * 2);                     // [K/32] {sum(X), 1/p}
@@ -183,7 +192,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
 #pragma unroll
     for (int i = 0; i < NS - 1; ++i) {
-        if (icur.valid(n_tiles)) { issue_block<I8>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
+        if (icur.valid(n_tiles)) { issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
         cp_async_commit();
     }
 
@@ -287,24 +296,21 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
         for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
-            if (icur.valid(n_tiles)) { issue_block<I8>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
+            if (icur.valid(n_tiles)) { issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
             cp_async_commit();
             cp_async_wait<NS - 1>();
             __syncwarp();
             if (active) {
                 const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * BLK;
-                // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
-                const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kk * 256);
-                const uint32_t bx0 = bx.x, bx1 = bx.y;
-                const int2 sp = sxp[kk * 4 + t];
-                const int sxt = sp.x;
-                const float ip = __int_as_float(sp.y);
-                int d[4] = {0, 0, 0, 0};
                 if constexpr (I8) {
+                    // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
+                    const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kk * 256);
+                    const float ip = __int_as_float(sxp[kk * 4 + t].y);
+                    int d[4] = {0, 0, 0, 0};
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj) {
                         const uint4 af = reinterpret_cast<const uint4*>(blk + jj * 512)[lane];
-                        const uint32_t b0 = (gj == (uint32_t)jj) ? bx0 : 0u, b1 = (gj == (uint32_t)jj) ? bx1 : 0u;
+                        const uint32_t b0 = (gj == (uint32_t)jj) ? bx.x : 0u, b1 = (gj == (uint32_t)jj) ? bx.y : 0u;
                         imma_16832(d, af.x, af.y, af.z, af.w, b0, b1, d);
                     }
                     // lane (g,t): exact sums of q * X over group t for rows g and g+8 (no zero point)
@@ -313,23 +319,32 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                     acc0 = fmaf((float)r0, ip, acc0);
                     acc1 = fmaf((float)r1, ip, acc1);
                 } else {
-                    const uint4 wa = reinterpret_cast<const uint4*>(blk)[lane];
-                    const uint4 wb = reinterpret_cast<const uint4*>(blk + 512)[lane];
-                    const __half2 sc = reinterpret_cast<const __half2*>(blk + 1024)[lane];
-                    const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
-                    const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t msk = 0x0F0F0F0Fu;
-                        const uint32_t b0 = (gj == (uint32_t)j) ? bx0 : 0u, b1 = (gj == (uint32_t)j) ? bx1 : 0u;
-                        imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, b0, b1, d);
+                    for (int sub = 0; sub < SUB; ++sub) {
+                        const unsigned char* sb = blk + sub * IM_BLK_BYTES;
+                        const uint32_t kb = kk * SUB + sub;  // 16x128 block index along K
+                        const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kb * 256);
+                        const int2 sp = sxp[kb * 4 + t];
+                        const float ip = __int_as_float(sp.y);
+                        const uint4 wa = reinterpret_cast<const uint4*>(sb)[lane];
+                        const uint4 wb = reinterpret_cast<const uint4*>(sb + 512)[lane];
+                        const __half2 sc = reinterpret_cast<const __half2*>(sb + 1024)[lane];
+                        const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
+                        const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
+                        int d[4] = {0, 0, 0, 0};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t msk = 0x0F0F0F0Fu;
+                            const uint32_t b0 = (gj == (uint32_t)j) ? bx.x : 0u, b1 = (gj == (uint32_t)j) ? bx.y : 0u;
+                            imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, b0, b1, d);
+                        }
+                        // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
+                        const int r0 = d[0] * 256 + d[1] - 8 * sp.x;
+                        const int r1 = d[2] * 256 + d[3] - 8 * sp.x;
+                        const float2 s2 = __half22float2(sc);
+                        acc0 = fmaf((float)r0 * ip, s2.x, acc0);
+                        acc1 = fmaf((float)r1 * ip, s2.y, acc1);
                     }
-                    // lane (g,t): d[0],d[1] = sums against H and L of group t for row g; d[2],d[3] for row g+8
-                    const int r0 = d[0] * 256 + d[1] - 8 * sxt;
-                    const int r1 = d[2] * 256 + d[3] - 8 * sxt;
-                    const float2 s2 = __half22float2(sc);
-                    acc0 = fmaf((float)r0 * ip, s2.x, acc0);
-                    acc1 = fmaf((float)r1 * ip, s2.y, acc1);
                 }
             }
             __syncwarp();  // every lane is done with the slot before the next iteration overwrites its predecessor
@@ -423,28 +438,31 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
     return tile_v3_half(lc, tiled, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
 }
 
-template <bool I8>
+template <int W>
 static cudaError_t imma_opt_in() {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_gemv_q4_imma<2, I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
 }
 cudaError_t gemv_imma_init() {
-    cudaError_t e = imma_opt_in<false>();
-    return e != cudaSuccess ? e : imma_opt_in<true>();
+    cudaError_t e = imma_opt_in<IM_Q4>();
+    if (e == cudaSuccess) e = imma_opt_in<IM_I8>();
+    return e != cudaSuccess ? e : imma_opt_in<IM_Q4X2>();
 }
+int imma_pair_ring = 3;  // int4, even number of k-blocks: two blocks per step with this ring depth (0 = one block per step)
 
 bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
 
-template <bool I8>
+template <int W>
 static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t max_ring) {
     const size_t fixed = (size_t)f.K * 2 + (size_t)(f.K / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
-    const size_t stage = (size_t)IM_GROUPS * IM_WARPS * ImBlk<I8>::bytes;  // one ring slot of every warp
+    const size_t stage = (size_t)IM_GROUPS * IM_WARPS * ImBlk<W>::bytes;  // one ring slot of every warp
     if (fixed + 2 * stage > (size_t)IM_MAX_SMEM) return cudaErrorInvalidConfiguration;
     size_t ns = ((size_t)IM_MAX_SMEM - fixed) / stage;
     if (max_ring >= 2 && ns > max_ring) ns = max_ring;
-    ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : 2);  // ring depth per warp (template parameter); 4 measured fastest
+    ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : (ns >= 3 ? 3 : 2));  // ring depth per warp (template parameter); 4 measured fastest
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;
@@ -455,9 +473,10 @@ static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t 
     const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
     const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
     const size_t smem = fixed + ns * stage;
-    if (ns == 8) return launch(lc, k_gemv_q4_imma<8, I8>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 4) return launch(lc, k_gemv_q4_imma<4, I8>, grid, dim3(IM_CONSUMERS), smem, f);
-    return launch(lc, k_gemv_q4_imma<2, I8>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 8) return launch(lc, k_gemv_q4_imma<8, W>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 4) return launch(lc, k_gemv_q4_imma<4, W>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 3) return launch(lc, k_gemv_q4_imma<3, W>, grid, dim3(IM_CONSUMERS), smem, f);
+    return launch(lc, k_gemv_q4_imma<2, W>, grid, dim3(IM_CONSUMERS), smem, f);
 }
 
 cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
@@ -480,7 +499,10 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     f.dst_offset = a.dst_offset; f.epilogue = a.epilogue;
     f.trace = a.trace;
     *handled = true;
-    return i8 ? imma_launch<true>(lc, f, a.max_ring) : imma_launch<false>(lc, f, a.max_ring);
+    if (i8) return imma_launch<IM_I8>(lc, f, a.max_ring);
+    // two blocks per step when every warp's share of a tile is a whole number of pairs
+    if (imma_pair_ring >= 2 && (a.w.cols / 128) % (2 * IM_WARPS) == 0) return imma_launch<IM_Q4X2>(lc, f, (uint32_t)imma_pair_ring);
+    return imma_launch<IM_Q4>(lc, f, a.max_ring);
 }
 
 // ---- int8 per-channel: canonical [rows][K] bytes + fp16 row scales -> tile-major blocks, then the scales ----
