@@ -160,7 +160,21 @@ int32_t vb_step_bytes(vb_ctx* ctx, uint64_t* weight_bytes, uint64_t* kv_bytes);
  * with host timers and cudaEvent pairs around whole phases (velox_cuda_runner.cu:39-49, :494-563); this is
  * the per-kernel view of the same thing.  Reading clears the records. */
 int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t* n_records);
-/* Tuning knobs (name/value), e.g. "gemv_path"; returns VB_ERR_INVALID for unknown names. */
+/* Tuning and diagnostic knobs (name/value); VB_ERR_INVALID for unknown names.  Changing one drops the captured
+ * decode graph (build it again).  Defaults are what measured fastest.
+ *   "gemv_path"      0: exact fp32 kernels for every product; 1 (default): the tuned kernels where they apply
+ *   "gemv_imma"      1: integer tensor-core kernel for int4 g32 / int8 per-channel at batch 1; 0: fp16-mma kernels
+ *   "gemv_tma"       with gemv_imma = 0: bulk-copy (TMA) ring instead of the register-prefetch kernel
+ *   "gemv_ring", "head_ring", "ring_qkv|o|gu|down"   weight ring depth per warp (4); "gemv_pair_ring" (3, 0 = off):
+ *                    ring depth when an int4 step takes two k-blocks
+ *   "attn_mma"       1: tensor-core attention for the fp16 cache; 0: the scalar fp32 path
+ *   "fuse_append"    1: bias + RoPE + KV append inside the attention kernel
+ *   "pdl"            1: programmatic dependent launch between the kernels of a step
+ *   "trace"          1: device time stamps per kernel (vb_trace_read)
+ *   "tp_p2p"         1: NVLink push exchange when peer regions are open, 0: NCCL
+ *   "tp_poll_ms"     limit of one exchange poll (default ~10000)
+ *   "tp_p2p_standin" diagnostic: private stand-in regions instead of peers (every exchange then runs into its
+ *                    poll limit; used by the time-out test) */
 int32_t vb_set_option(vb_ctx* ctx, const char* name, int64_t value);
 
 /* Tensor parallel set-up (tp_size>1): every rank calls vb_tp_unique_id on rank 0's buffer contents
