@@ -13,6 +13,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB = os.path.join(_HERE, "libvelox_b200.so")
+RUNNER = os.path.join(_HERE, "velox_b200_runner")
 SOURCES = ["vb_basic.cu", "vb_gemv.cu", "vb_gemv_fast.cu", "vb_gemv_imma.cu", "vb_attn.cu", "vb_mla.cu", "vb_engine.cu", "vb_nccl.cu", "vb_tp.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--use_fast_math=false", "-Xptxas", "-v"]
@@ -29,7 +30,10 @@ def _stale() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(_HERE, "..", "include", "velox_b200.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(_HERE, "..", "include", "velox_b200.h"),
+                                                                  os.path.join(_HERE, "runner", "velox_b200_runner.cpp")]
+    if not os.path.exists(RUNNER):
+        return True
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -58,7 +62,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     link = [_nvcc(), "-shared", "-ccbin", "/usr/bin/g++", "-o", LIB, *objs, "-lcudart", "-ldl"]
     subprocess.check_call(link, env=env)
+    build_runner()
     return LIB
+
+
+def build_runner() -> str:
+    """The stand-alone C++ runner over the C ABI (plain g++; it links against the shared library only)."""
+    src = os.path.join(_HERE, "runner", "velox_b200_runner.cpp")
+    cmd = ["/usr/bin/g++", "-O2", "-std=c++17", "-Wall", "-I", os.path.join(_HERE, "..", "include"), src, "-o", RUNNER,
+           "-L", _HERE, "-lvelox_b200", "-Wl,-rpath,$ORIGIN"]
+    subprocess.check_call(cmd)
+    return RUNNER
 
 
 if __name__ == "__main__":
