@@ -105,6 +105,8 @@ def workload_spec(name: str):
         return QWEN25_7B_INT8, 1
     if name == "qwen2-72b-int4-tp-bs1":
         return QWEN2_72B_INT4, 1
+    if name == "qwen2-72b-int4-tp-bs16":  # 16 sequences per step (sharded: the unsharded model only fits with one)
+        return QWEN2_72B_INT4, 16
     if name == "qwen2-72b-int4-tp-bs1-8layers":  # quick check of the sharded path
         return QWEN2_72B_INT4.scaled(name="qwen2-72b-int4g32-8layers", n_layers=8), 1
     if name == "llama3-8b-int4-bs1-4layers":  # quick functional check of the bench itself
@@ -209,10 +211,11 @@ def main():
     if tp and world > 1:
         # one model over all ranks; the 72B shape only fits one GPU with the single-layout arena
         from velox_b200.tp import connect
-        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, tp_rank=rank, tp_size=world, lean_weights=True)
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, tp_rank=rank, tp_size=world,
+                     lean_weights=batch == 1)
         connect(eng, args.tp_exchange)
     else:
-        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp)
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp and batch == 1)
     eng.set_option("gemv_path", args.gemv_path)
     if args.no_pdl:
         eng.set_option("pdl", 0)
@@ -224,10 +227,17 @@ def main():
 
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import helpers as H
-    prompt = H.prompt_tokens(spec, SEED, args.prompt_len)
-    eng.reserve(0, max_seq)
     t0 = time.perf_counter()
-    eng.prefill(prompt, 0)
+    if batch == 1:
+        prompt = H.prompt_tokens(spec, SEED, args.prompt_len)
+        eng.reserve(0, max_seq)
+        eng.prefill(prompt, 0)
+    else:
+        # every slot its own prompt of the same length, prefilled in lockstep (one step per position)
+        from velox_b200.modelspec import PROMPT_STREAM
+        for slot in range(batch):
+            eng.reserve(slot, max_seq)
+        eng.prefill_lockstep([H.prompt_tokens(spec, SEED, args.prompt_len, stream=PROMPT_STREAM + slot) for slot in range(batch)])
     eng.sync()
     ttft_s = time.perf_counter() - t0
     eng.build_graph()
@@ -262,9 +272,16 @@ def main():
     tok, pos = eng.state(0)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        tok = eng.forward_step(tok, pos, 0)   # sends (token,pos), replays one step, reads the token back
-        pos += 1
+    if batch == 1:
+        for _ in range(args.steps):
+            tok = eng.forward_step(tok, pos, 0)   # sends (token,pos), replays one step, reads the token back
+            pos += 1
+    else:
+        for _ in range(args.steps):               # tokens feed back on the device; the host reads every slot's token
+            eng.decode(1)
+            for slot in range(batch):
+                eng.read_tokens(slot, pos, 1)
+            pos += 1
     e2e_s = time.perf_counter() - t0
     if sampler.rows == []:
         # very short runs: keep the GPU busy until the sampler has something to report
@@ -298,7 +315,7 @@ def main():
                      "traffic": int(step_bytes * 1.006), "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
                      "bytes_per_launch": step_bytes},
-        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 * batch, "d2h_bytes_per_step": 4 * batch},
+        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 if batch == 1 else 0, "d2h_bytes_per_step": 4 * batch},
         "gpu_launches": int(launches), "clocks": clocks,
         "ttft_ms": 1e3 * ttft_s, "load_s": load_s,
     }

@@ -173,6 +173,26 @@ def test_batched_variable_length_sequences():
     eng.close()
 
 
+def test_lockstep_prefill_matches_the_checker():
+    """All slots prefilled together, one step per prompt position (right-aligned), then decoded together."""
+    spec = SMALL_SPECS[2]
+    seed, n_new = 17, 8
+    lens = [12, 7, 12]
+    max_seq = max(lens) + n_new + 1
+    ora, _ = H.build_oracle(spec, seed, max_seq, n_seqs=len(lens))
+    eng = H.build_engine(spec, seed, max_seq, max_batch=len(lens))
+    prompts = [H.prompt_tokens(spec, seed, n, stream=(1 << 20) + i) for i, n in enumerate(lens)]
+    for i, p in enumerate(prompts):
+        eng.reserve(i, len(p) + n_new)
+    eng.prefill_lockstep(prompts)
+    eng.build_graph()
+    eng.decode(n_new - 1)
+    for i, p in enumerate(prompts):
+        want = ora.generate_greedy(p, n_new, seq=i)
+        assert np.array_equal(eng.read_tokens(i, len(p) - 1, n_new), want), i
+    eng.close()
+
+
 def test_engine_argument_errors():
     spec = H.TINY
     eng = H.build_engine(spec, 1, 32)

@@ -165,6 +165,20 @@ class Engine:
         prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
         L.check(self._lib.vb_prefill(self.h, slot, _ptr(prompt), len(prompt)))
 
+    def prefill_lockstep(self, prompts):
+        """Prefills several slots together, one decode step per prompt position (prompts right-aligned so that all
+        end at the same step): slot i gets prompts[i].  The reference has no batched prefill; this is its
+        token-by-token prefill run for all sequences at once."""
+        prompts = [np.ascontiguousarray(p, dtype=np.uint32) for p in prompts]
+        n = max(len(p) for p in prompts)
+        for step in range(n):
+            for slot, pr in enumerate(prompts):
+                k = step - (n - len(pr))
+                if k >= 0:
+                    self.set_state(slot, int(pr[k]), k, True)
+            L.check(self._lib.vb_decode_step(self.h))
+        self.sync()
+
     def decode(self, n_steps: int, timed: bool = False):
         ms = C.c_float(0.0)
         L.check(self._lib.vb_decode_run(self.h, n_steps, C.byref(ms) if timed else None))
