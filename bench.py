@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--gemv-path", type=int, default=1)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="tensor-parallel workloads: NVLink peer pushes inside the library's own kernels, or NCCL")
     args = ap.parse_args()
@@ -217,6 +218,9 @@ def main():
     else:
         eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp and batch == 1)
     eng.set_option("gemv_path", args.gemv_path)
+    for kv in args.set:
+        name, _, val = kv.partition("=")
+        eng.set_option(name, int(val))
     if args.no_pdl:
         eng.set_option("pdl", 0)
     t0 = time.perf_counter()

@@ -39,12 +39,13 @@ def _run_group(tmp_path, world: int, extra=()):
     return [np.load(os.path.join(str(tmp_path), f"rank{k}.npz")) for k in range(world)]
 
 
-@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
+@pytest.mark.parametrize("exchange", ["p2p", "p2p-fused", "nccl"])
 @pytest.mark.parametrize("graph", [True, False])
 def test_tp2_matches_unsharded_and_checker(tmp_path, graph, exchange):
     if _gpu_count() < 2:
         pytest.skip("needs 2 GPUs")
-    ranks = _run_group(tmp_path, 2, ("--exchange", exchange) + (() if graph else ("--no-graph",)))
+    extra = ("--exchange", "p2p", "--fused-push", "1") if exchange == "p2p-fused" else ("--exchange", exchange, "--fused-push", "0")
+    ranks = _run_group(tmp_path, 2, extra + (() if graph else ("--no-graph",)))
     prompt = prompt_tokens(TP_SPEC, SEED, N_PROMPT)
     # unsharded engine on this process's GPU
     eng = build_engine(TP_SPEC, SEED, N_PROMPT + N_NEW + 8)

@@ -31,10 +31,13 @@ def main():
     ap.add_argument("--new", type=int, default=40)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--fused-push", type=int, default=-1, help="0/1: override the engine's default")
     a = ap.parse_args()
     rank, world, _ = env_rank()
     import torch.distributed as dist
     eng = create_tp_engine(TP_SPEC, max_seq_len=a.prompt + a.new + 8, exchange=a.exchange)
+    if a.fused_push >= 0:
+        eng.set_option("tp_fused_push", a.fused_push)
     eng.load_synthetic(a.seed)
     dist.barrier()  # the exchange waits ~10 s at most for a peer: start the steps together
     prompt = np.load(os.path.join(a.out, "prompt.npy"))

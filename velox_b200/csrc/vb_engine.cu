@@ -48,6 +48,7 @@ struct vb_ctx {
     void* nccl = nullptr;                 // communicator of the TP group
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
     bool links_open = false, use_links = true, links_standin = false;
+    bool tp_fused_push = false;           // row-parallel products send their rows to the peers from their own epilogue
     uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
     uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
@@ -328,9 +329,10 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     const int row_epi = (!tp || (!p2p && d.tp_rank == 0)) ? EPI_RESIDUAL : EPI_STORE;
     float* row_dst = p2p ? c->partial : c->hidden;
     if (p2p) VB_TRY(tp_epoch_advance(lcfg(c, false), c->links));
+    bool pushed = false;  // set by the row-parallel product when its own epilogue sent the rows to the peers
     auto exchange = [&](uint32_t site) -> cudaError_t {
         if (!tp) return cudaSuccess;
-        if (p2p) return tp_reduce(lcfg(c, true), c->links, c->hidden, c->partial, B * d.d_model, site, n_sites, c->err_word);
+        if (p2p) return tp_reduce(lcfg(c, true), c->links, c->hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed);
         return nccl_allreduce_sum_f32(c->nccl, c->hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
@@ -368,6 +370,8 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         o.state = state; o.batch = B; o.x = c->attn_out; o.dst = row_dst; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
         o.trace = next_trace(); o.max_ring = c->ring_role[1] ? c->ring_role[1] : c->gemv_ring;
+        pushed = false;
+        if (p2p && c->tp_fused_push) { o.push.links = &c->links; o.push.site = 2 * l; o.push.n_sites = n_sites; o.pushed = &pushed; }
         VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
         VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
@@ -382,6 +386,8 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = row_dst; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
         dn.trace = next_trace(); dn.max_ring = c->ring_role[3] ? c->ring_role[3] : c->gemv_ring;
+        pushed = false;
+        if (p2p && c->tp_fused_push) { dn.push.links = &c->links; dn.push.site = 2 * l + 1; dn.push.n_sites = n_sites; dn.pushed = &pushed; }
         VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
         VB_TRY(exchange(2 * l + 1));
     }
@@ -1003,6 +1009,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "ring_down")) { c->ring_role[3] = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "head_ring")) { c->head_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
+    if (!strcmp(name, "tp_fused_push")) { c->tp_fused_push = value != 0; return VB_OK; }
     if (!strcmp(name, "tp_poll_ms")) {  // limit of one exchange poll (default ~10 s), at a nominal 2 GHz
         VB_REQUIRE(value > 0, "vb_set_option: tp_poll_ms must be positive");
         c->links.poll_clocks = (long long)value * 2000000LL;
@@ -1027,6 +1034,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         c->links_open = true;
         return VB_OK;
     }
+    if (!strcmp(name, "gemv_spread")) { imma_spread = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_pair_ring")) { imma_pair_ring = (int)value; return VB_OK; }
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "attn_mma")) { attn_use_mma = value != 0; return VB_OK; }

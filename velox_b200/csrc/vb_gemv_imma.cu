@@ -60,6 +60,12 @@ struct ImmaArgs {
     uint32_t dst_offset;
     int epilogue;            // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU (interleaved 8+8 tiles)
     unsigned long long* trace;  // optional timestamp record
+    uint32_t spread;            // tile -> (block, group) mapping, see the kernel
+    // tensor parallel (EPI_STORE of a row-parallel product): the output rows also go to every peer's receive
+    // region as sequence-tagged 16-byte words {row 2i, seq, row 2i+1, seq}; push_size == 0: no push
+    unsigned char* push_base[8];
+    uint32_t push_rank, push_size, push_site, push_n_sites, push_max_pairs;
+    uint64_t push_epoch_off, push_data_off;
 };
 
 __device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
@@ -126,7 +132,7 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // The sequence of 16x128 blocks one warp works through: block `kk` (kk = warp, warp+8, ...) of row tile `tile`
-// (tile = 2 * blockIdx.x + group, += 2 * gridDim.x).
+// (tile = blockIdx.x + group * gridDim.x, += 2 * gridDim.x).
 struct BlockCursor {
     uint32_t tile, kk;
     __device__ __forceinline__ bool valid(uint32_t n_tiles) const { return tile < n_tiles; }
@@ -181,7 +187,9 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t group = wid / IM_WARPS, warp = wid % IM_WARPS;  // tile group, warp within the group
     const uint32_t gt = threadIdx.x % (IM_WARPS * 32);            // thread within the group
-    const uint32_t vtile0 = IM_GROUPS * blockIdx.x + group, vstride = IM_GROUPS * gridDim.x;
+    // tile t of a round belongs to block t % gridDim.x, group t / gridDim.x: a short last (or only) round spreads
+    // over as many SMs as it has tiles instead of filling both groups of half as many
+    const uint32_t vtile0 = a.spread ? blockIdx.x + group * gridDim.x : IM_GROUPS * blockIdx.x + group, vstride = IM_GROUPS * gridDim.x;
     trace_mark(a.trace, 0);
     pdl_launch_dependents();
 
@@ -212,6 +220,9 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     pdl_wait();
     trace_mark(a.trace, 1);
     const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
+    // the step's exchange counter (advanced once at the start of the step), for the sequence tags of pushed rows
+    unsigned long long push_epoch = 0;
+    if (a.push_size > 1) push_epoch = *reinterpret_cast<const volatile unsigned long long*>(a.push_base[a.push_rank] + a.push_epoch_off);
 
     // x -> shared memory.  All of a thread's loads of a batch are issued before any value is used: one memory
     // trip per batch of XC * 4096 elements (the whole row up to 16384 elements), not one per chunk.
@@ -369,6 +380,21 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                 a.dst[a.dst_offset + tile * 16 + gt] = resid + v;
             } else {
                 a.dst[a.dst_offset + tile * 16 + gt] = v;
+                if (a.push_size > 1) {
+                    // rows 2i and 2i+1 travel together: the even thread of each pair sends to all peers
+                    const float other = __shfl_xor_sync(0x0000FFFFu, v, 1);
+                    if ((gt & 1) == 0) {
+                        const uint32_t seq = (uint32_t)(push_epoch * a.push_n_sites + a.push_site) + 1u;
+                        const size_t slot = ((size_t)(a.push_site % TP_BUFS) * a.push_size + a.push_rank) * a.push_max_pairs +
+                                            ((a.dst_offset + tile * 16 + gt) >> 1);
+                        for (uint32_t p = 0; p < a.push_size; ++p) {
+                            if (p == a.push_rank) continue;
+                            uint4* dst = reinterpret_cast<uint4*>(a.push_base[p] + a.push_data_off) + slot;
+                            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(seq),
+                                         "r"(__float_as_uint(other)), "r"(seq) : "memory");
+                        }
+                    }
+                }
             }
         }
     }
@@ -451,6 +477,7 @@ cudaError_t gemv_imma_init() {
     if (e == cudaSuccess) e = imma_opt_in<IM_I8>();
     return e != cudaSuccess ? e : imma_opt_in<IM_Q4X2>();
 }
+bool imma_spread = false;  // deal a round's tiles to blocks first, then to the second group of each block
 int imma_pair_ring = 3;  // int4, even number of k-blocks: two blocks per step with this ring depth (0 = one block per step)
 
 bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
@@ -470,7 +497,7 @@ static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t 
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     const uint32_t n_tiles = f.rows / 16;
-    const uint32_t want = (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
+    const uint32_t want = f.spread ? n_tiles : (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
     const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
     const size_t smem = fixed + ns * stage;
     if (ns == 8) return launch(lc, k_gemv_q4_imma<8, W>, grid, dim3(IM_CONSUMERS), smem, f);
@@ -498,6 +525,15 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
     f.dst_offset = a.dst_offset; f.epilogue = a.epilogue;
     f.trace = a.trace;
+    f.spread = imma_spread ? 1u : 0u;
+    f.push_size = 0;
+    if (a.push.links && a.epilogue == EPI_STORE && a.push.links->size > 1 && a.dst_offset % 2 == 0) {
+        const TpLinks& l = *a.push.links;
+        for (int r = 0; r < 8; ++r) f.push_base[r] = l.base[r];
+        f.push_rank = l.rank; f.push_size = l.size; f.push_site = a.push.site; f.push_n_sites = a.push.n_sites;
+        f.push_max_pairs = l.max_pairs; f.push_epoch_off = l.epoch_off; f.push_data_off = l.data_off;
+        if (a.pushed) *a.pushed = true;
+    }
     *handled = true;
     if (i8) return imma_launch<IM_I8>(lc, f, a.max_ring);
     // two blocks per step when every warp's share of a tile is a whole number of pairs

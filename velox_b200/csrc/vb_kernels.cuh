@@ -38,8 +38,16 @@ struct TpLinks {
 };
 void tp_links_layout(TpLinks* l, uint32_t rank, uint32_t size, uint32_t max_elems, uint32_t max_batch);
 cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l);
+// `pushed`: the producing kernel already stored the partial into the peers' regions (TpPush); only poll and sum
 cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, const float* partial, uint32_t n, uint32_t site,
-                      uint32_t n_sites, uint32_t* err);
+                      uint32_t n_sites, uint32_t* err, bool pushed = false);
+// Exchange `site` of a step: where the epilogue of a row-parallel product sends its output rows (pairs of rows,
+// sequence-tagged 16-byte words, see vb_tp.cu) besides storing them locally.
+struct TpPush {
+    const TpLinks* links = nullptr;  // null: no push
+    uint32_t site = 0, n_sites = 1;
+};
+constexpr uint32_t TP_BUFS = 4;  // receive buffers used round-robin by consecutive exchange sites
 cudaError_t tp_argmax(const LaunchCfg& lc, const TpLinks& l, const void* pairs, uint32_t batch, uint32_t site, uint32_t n_sites,
                       SeqState* state, uint32_t* ring, uint32_t ring_slots, uint32_t* err);
 cudaError_t argmax_shard(const LaunchCfg& lc, void* pair_out, const float* logits, uint32_t n, uint32_t idx_offset, uint32_t batch,
@@ -67,7 +75,9 @@ struct GemvArgs {
     uint32_t dst_stride = 0;         // elements between batch rows of dst (0 = out_dim)
     uint32_t dst_offset = 0;         // column offset inside dst
     int epilogue = EPI_STORE;
-    uint32_t max_ring = 12;          // cap on the weight ring depth per warp (12, 10, 8, 4 or 2)
+    uint32_t max_ring = 12;          // cap on the weight ring depth per warp
+    TpPush push;                     // EPI_STORE only: also send the rows to the tensor-parallel peers
+    bool* pushed = nullptr;          // out: set when the kernel that ran did send them
     unsigned long long* trace = nullptr;  // 3-slot timestamp record of this launch (tuned kernels only)
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
@@ -95,6 +105,7 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
                               int which);
 extern bool imma_enabled;
 extern int imma_pair_ring;
+extern bool imma_spread;
 
 // vb_attn.cu
 struct AttnArgs {

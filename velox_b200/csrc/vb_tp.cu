@@ -15,7 +15,6 @@ namespace vb {
 
 namespace {
 
-constexpr uint32_t TP_BUFS = 4;
 
 __device__ __forceinline__ void st_ll(uint4* p, uint32_t a, uint32_t b, uint32_t seq) {
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(seq), "r"(b), "r"(seq) : "memory");
@@ -46,6 +45,7 @@ __global__ void k_tp_epoch(unsigned long long* epoch) {
 
 // hidden[i] += sum over ranks of partial_r[i], identical bits on every rank (fixed summation order).
 // One thread per pair of elements; grid = ceil(n/2/256).
+template <bool PUSHED>
 __global__ void __launch_bounds__(256) k_tp_reduce_ll(TpLinks links, float* __restrict__ hidden, const float* __restrict__ partial,
                                                        uint32_t n, uint32_t site, uint32_t n_sites, uint32_t* __restrict__ err) {
     pdl_wait();
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(256) k_tp_reduce_ll(TpLinks links, float* __re
     float2 mine = make_float2(0.f, 0.f);
     if (valid) {
         mine = *reinterpret_cast<const float2*>(partial + 2 * (size_t)i);
-        for (uint32_t p = 0; p < links.size; ++p) {
+        for (uint32_t p = 0; p < links.size && !PUSHED; ++p) {  // PUSHED: the product's epilogue sent them already
             if (p == links.rank) continue;
             uint4* dst = reinterpret_cast<uint4*>(links.base[p] + links.data_off) + (buf * links.size + links.rank) * slot_elems + i;
             st_ll(dst, __float_as_uint(mine.x), __float_as_uint(mine.y), seq);
@@ -133,11 +133,12 @@ cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l) {
 }
 
 cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, const float* partial, uint32_t n, uint32_t site,
-                      uint32_t n_sites, uint32_t* err) {
+                      uint32_t n_sites, uint32_t* err, bool pushed) {
     if (n == 0) return cudaSuccess;
     if (n % 2 != 0 || (n + 1) / 2 > l.max_pairs) return cudaErrorInvalidValue;
     const uint32_t pairs = n / 2;
-    return launch(lc, k_tp_reduce_ll, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err);
+    if (pushed) return launch(lc, k_tp_reduce_ll<true>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err);
+    return launch(lc, k_tp_reduce_ll<false>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err);
 }
 
 cudaError_t tp_argmax(const LaunchCfg& lc, const TpLinks& l, const void* pairs, uint32_t batch, uint32_t site, uint32_t n_sites,
