@@ -48,7 +48,7 @@ struct vb_ctx {
     void* nccl = nullptr;                 // communicator of the TP group
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
     bool links_open = false, use_links = true, links_standin = false;
-    bool tp_fused_push = false;           // row-parallel products send their rows to the peers from their own epilogue
+    bool tp_fused_push = true;            // row-parallel products send their rows to the peers from their own epilogue
     uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
     uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
