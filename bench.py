@@ -183,6 +183,7 @@ def main():
     ap.add_argument("--gemv-path", type=int, default=1)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (quick checks)")
     ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="tensor-parallel workloads: NVLink peer pushes inside the library's own kernels, or NCCL")
@@ -194,6 +195,8 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     spec, batch = workload_spec(args.workload)
+    if args.layers > 0:
+        spec = spec.scaled(name="%s-%dlayers" % (spec.name, args.layers), n_layers=args.layers)
 
     if args.impl == "reference":
         run_reference(args, spec, batch, rank, world)

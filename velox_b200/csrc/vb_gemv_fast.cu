@@ -42,7 +42,7 @@ namespace vb {
 constexpr int FAST_WARPS = 8;
 constexpr int FAST_THREADS = FAST_WARPS * 32;
 constexpr int FAST_PF = 2;            // blocks in flight per warp and buffer
-constexpr int FAST_KC_BATCHED = 4096; // x columns staged at a time when 8 sequences share a block
+constexpr int FAST_KC_BATCHED = 4096; // x columns staged at a time when 8 sequences share a block and the row is too long to stage whole
 constexpr int FAST_XPAD = 32;         // halves of padding between staged x rows (bank spread)
 constexpr int BLK_U4 = 72;            // uint4 per 16x128 block: 64 of packed weights + 8 of scales (1152 bytes)
 constexpr int BLK_BYTES = BLK_U4 * 16;
@@ -62,6 +62,7 @@ struct FastArgs {
     const SeqState* state;
     uint32_t batch, dst_stride, dst_offset;
     int epilogue;
+    uint32_t kc;           // batched: x columns staged at a time (== K: staged once, persistent loop over the tiles)
 };
 
 __device__ __forceinline__ void mma16816(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(FAST_THREADS, 2) k_gemv_q4_mma(FastArgs a) {
     constexpr int NM = DUAL ? 2 : 1;
     constexpr int RED = FAST_WARPS * NM * 16 * NB;
     const uint32_t K = a.K, KT = K / 128, n_tiles = a.rows / 16;
-    const uint32_t kc_max = BATCHED ? min(K, (uint32_t)FAST_KC_BATCHED) : K;
+    const uint32_t kc_max = BATCHED ? min(K, a.kc) : K;
     const bool single = (kc_max == K);  // the whole row fits the staging buffer: stage once, loop over tiles
     const uint32_t xstride = kc_max + FAST_XPAD;
     __half* xs = reinterpret_cast<__half*>(smem_raw);                         // [NB][xstride]
@@ -565,20 +566,23 @@ __global__ void __launch_bounds__(TMA_THREADS, 2) k_gemv_q4_tma(FastArgs a) {
 }
 
 
-static size_t fast_smem_bytes(uint32_t K, bool batched, bool dual) {
+static size_t fast_smem_bytes(uint32_t K, bool batched, bool dual, uint32_t kc_batched) {
     const uint32_t nb = batched ? 8 : 1, nm = dual ? 2 : 1;
-    const uint32_t kc = batched ? (K < (uint32_t)FAST_KC_BATCHED ? K : (uint32_t)FAST_KC_BATCHED) : K;
+    const uint32_t kc = batched ? (K < kc_batched ? K : kc_batched) : K;
     return (size_t)nb * (kc + FAST_XPAD) * 2 + (size_t)nb * (kc / 32) * 4 + 2 * (size_t)FAST_WARPS * nm * 16 * nb * 4;
 }
 
-constexpr int FAST_MAX_SMEM = 100 * 1024;
+constexpr int FAST_MAX_SMEM = 100 * 1024;         // two blocks per SM
+constexpr int FAST_MAX_SMEM_BATCHED = 200 * 1024; // batched: one block per SM may stage rows of up to ~12k elements whole
 constexpr int TMA_MAX_SMEM = 112 * 1024;  // two blocks per SM
 
 cudaError_t gemv_fast_init() {
     cudaError_t e;
 #define VB_OPT_IN(B, D) if ((e = cudaFuncSetAttribute(k_gemv_q4_mma<B, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_MAX_SMEM)) != cudaSuccess) return e
-    VB_OPT_IN(false, false); VB_OPT_IN(false, true); VB_OPT_IN(true, false); VB_OPT_IN(true, true);
+    VB_OPT_IN(false, false); VB_OPT_IN(false, true);
 #undef VB_OPT_IN
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_mma<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_MAX_SMEM_BATCHED)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_mma<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FAST_MAX_SMEM_BATCHED)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_tma<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_MAX_SMEM)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_tma<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TMA_MAX_SMEM)) != cudaSuccess) return e;
     return cudaSuccess;
@@ -618,7 +622,10 @@ cudaError_t gemv_fast(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     const bool dual = dual_in;
     if (dual && (!a.w2.tiled || a.w2.rows != a.w.rows || a.w2.cols != a.w.cols)) return cudaSuccess;
     const bool batched = a.batch > 1;
-    const size_t smem = fast_smem_bytes(a.w.cols, batched, dual);
+    // batched: stage the whole row when one block per SM can hold it (then the block is persistent over its tiles)
+    uint32_t kc = (uint32_t)FAST_KC_BATCHED;
+    if (batched && fast_smem_bytes(a.w.cols, true, dual, a.w.cols) <= (size_t)FAST_MAX_SMEM_BATCHED) kc = a.w.cols;
+    const size_t smem = fast_smem_bytes(a.w.cols, batched, dual, kc);
     FastArgs f;
     f.w[0] = (const uint4*)a.w.tiled;
     f.w[1] = dual ? (const uint4*)a.w2.tiled : f.w[0];
@@ -626,6 +633,7 @@ cudaError_t gemv_fast(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     f.rows = a.w.rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
     f.norm_w = a.norm_w; f.norm_fmt = a.norm_fmt; f.eps = a.eps; f.state = a.state;
     f.batch = a.batch; f.dst_stride = a.dst_stride; f.dst_offset = a.dst_offset; f.epilogue = a.epilogue;
+    f.kc = kc;
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;
@@ -633,9 +641,13 @@ cudaError_t gemv_fast(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
     }
     const uint32_t n_tiles = a.w.rows / 16;
-    const bool single = !batched || a.w.cols <= (uint32_t)FAST_KC_BATCHED;
-    const uint32_t gx = single ? (n_tiles < 2u * n_sm ? n_tiles : 2u * n_sm) : n_tiles;
-    const dim3 grid(gx, batched ? (a.batch + 7) / 8 : 1);
+    const bool single = !batched || a.w.cols <= kc;
+    // persistent blocks: as many as are resident at once over all batch groups
+    const uint32_t gy = batched ? (a.batch + 7) / 8 : 1;
+    const uint32_t resident = (uint32_t)n_sm * (smem > (size_t)FAST_MAX_SMEM ? 1u : 2u);
+    const uint32_t per_group = resident / gy ? resident / gy : 1u;
+    const uint32_t gx = single ? (n_tiles < per_group ? n_tiles : per_group) : n_tiles;
+    const dim3 grid(gx, gy);
     bool interleaved = false;
     if (!batched && fast_use_tma && dual && a.w.tiled_swiglu) {
         // gate and up share 16-row tiles: one matrix of 2*rows rows, half the tile size, SwiGLU in the epilogue
@@ -662,7 +674,7 @@ cudaError_t gemv_fast(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
                         : launch(lc, k_gemv_q4_tma<false>, tgrid, dim3(TMA_THREADS), tsmem, f);
         }
     }
-    if (smem > (size_t)FAST_MAX_SMEM) return cudaSuccess;
+    if (smem > (size_t)(batched ? FAST_MAX_SMEM_BATCHED : FAST_MAX_SMEM)) return cudaSuccess;
     *handled = true;
     if (batched) {
         return dual ? launch(lc, k_gemv_q4_mma<true, true>, grid, dim3(FAST_THREADS), smem, f)
