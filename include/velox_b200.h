@@ -169,6 +169,7 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *                    ring depth when an int4 step takes two k-blocks
  *   "attn_mma"       1: tensor-core attention for the fp16 cache; 0: the scalar fp32 path
  *   "fuse_append"    1: bias + RoPE + KV append inside the attention kernel
+ *   "prefill_chunk"  prompt tokens that go through the layers together in vb_prefill (16; 1 = token by token)
  *   "pdl"            1: programmatic dependent launch between the kernels of a step
  *   "trace"          1: device time stamps per kernel (vb_trace_read)
  *   "tp_p2p"         1: NVLink push exchange when peer regions are open, 0: NCCL

@@ -77,6 +77,13 @@ struct vb_ctx {
     uint32_t* ring_dev = nullptr;
     uint32_t* pf_tokens = nullptr;  // device copy of the prompt being prefilled
     uint32_t pf_tokens_cap = 0;
+    // chunked prefill: `prefill_chunk` prompt tokens go through the layers together as rows of one step (weights are
+    // read once per chunk by the batched kernels); all rows live on the prefilled sequence's KV blocks
+    uint32_t prefill_chunk = 16;
+    SeqState* pfc_state = nullptr;        // [chunk]
+    int32_t* pfc_table = nullptr;         // [chunk][max_blocks], every row = the sequence's block-table row
+    float *pfc_hidden = nullptr, *pfc_qkv = nullptr, *pfc_q = nullptr, *pfc_attn = nullptr, *pfc_act = nullptr;
+    uint32_t pfc_rows = 0;                // rows the buffers above hold
 
     // activations
     float *hidden = nullptr, *qkv = nullptr, *q = nullptr, *attn_out = nullptr, *act = nullptr, *logits = nullptr;
@@ -294,6 +301,17 @@ __global__ void k_set_state(SeqState* state, uint32_t slot, const uint32_t* toke
     }
 }
 
+// rows j < n of a prefill chunk: prompt token first + j at position first + j; rows beyond n inactive
+__global__ void k_set_chunk_state(SeqState* state, const uint32_t* tokens, uint32_t first, uint32_t n, uint32_t rows) {
+    const uint32_t j = threadIdx.x;
+    if (j < rows) {
+        state[j].token = j < n ? tokens[first + j] : 0u;
+        state[j].pos = first + j;
+        state[j].active = j < n ? 1u : 0u;
+        state[j].pad = 0;
+    }
+}
+
 bool all_loaded(vb_ctx* c, const char** missing) {
     static const char* names[] = {"embed", "attn_norm", "wq", "wk", "wv", "wo", "mlp_norm", "wgate", "wup", "wdown",
                                   "final_norm", "lm_head", "bq", "bk", "bv"};
@@ -307,17 +325,29 @@ bool all_loaded(vb_ctx* c, const char** missing) {
     return true;
 }
 
-// The launch sequence of one token for every active slot of `state`.
-cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
+// Activation buffers and block table one launch sequence works on: the context's own (decode, one row per slot)
+// or the prefill chunk's (one row per prompt token of the chunk, all rows on the same sequence's KV blocks).
+struct StepIO {
+    float *hidden, *qkv, *q, *attn_out, *act, *logits;
+    const int32_t* block_table;
+    uint32_t B;
+    bool fused_append;  // false: K/V of all rows are appended by a kernel of their own before attention
+};
+StepIO decode_io(vb_ctx* c) {
+    return StepIO{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
+}
+
+// The launch sequence of one token for every active row of `state`.
+cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepIO& io) {
     const vb_model_desc& d = c->d;
-    const uint32_t B = d.max_batch;
+    const uint32_t B = io.B;
     cudaError_t e;
     uint32_t tn = 0;
     auto next_trace = [&]() -> unsigned long long* { return (c->trace && tn < 1024) ? c->trace + 4 * (size_t)(tn++) : nullptr; };
 #define VB_TRY(x) do { e = (x); if (e != cudaSuccess) return e; } while (0)
     Tensor& emb = c->tensor(VB_ROLE_EMBED, 0);
     // the first kernel of a step must not overlap the previous step's tail: launched without PDL
-    VB_TRY(embed(lcfg(c, false), c->hidden, nullptr, state, emb.m.data, emb.m.scales, emb.m.fmt, d.d_model, d.vocab, B));
+    VB_TRY(embed(lcfg(c, false), io.hidden, nullptr, state, emb.m.data, emb.m.scales, emb.m.fmt, d.d_model, d.vocab, B));
     // Tensor parallel: O and down are row-parallel.  Rank 0 adds its partial product onto the residual stream,
     // the other ranks overwrite theirs with the bare partial; one in-place sum all-reduce then leaves the new
     // residual stream, bit-identical, on every rank (no separate residual-add pass).
@@ -327,20 +357,20 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     const bool p2p = tp && c->links_open && c->use_links;
     const uint32_t n_sites = 2 * d.n_layers + 1;
     const int row_epi = (!tp || (!p2p && d.tp_rank == 0)) ? EPI_RESIDUAL : EPI_STORE;
-    float* row_dst = p2p ? c->partial : c->hidden;
+    float* row_dst = p2p ? c->partial : io.hidden;
     if (p2p) VB_TRY(tp_epoch_advance(lcfg(c, false), c->links));
     bool pushed = false;  // set by the row-parallel product when its own epilogue sent the rows to the peers
     auto exchange = [&](uint32_t site) -> cudaError_t {
         if (!tp) return cudaSuccess;
-        if (p2p) return tp_reduce(lcfg(c, true), c->links, c->hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed);
-        return nccl_allreduce_sum_f32(c->nccl, c->hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
+        if (p2p) return tp_reduce(lcfg(c, true), c->links, io.hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed);
+        return nccl_allreduce_sum_f32(c->nccl, io.hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
         const int L = (int)l;
         // RMSNorm + fused QKV projection
         GemvArgs g;
         g.state = state; g.batch = B;
-        g.x = c->hidden; g.dst = c->qkv;
+        g.x = io.hidden; g.dst = io.qkv;
         g.norm_w = c->tensor(VB_ROLE_ATTN_NORM, L).m.data; g.norm_fmt = c->tensor(VB_ROLE_ATTN_NORM, L).m.fmt; g.eps = d.rms_eps;
         g.w = c->tensor(VB_ROLE_WQ, L).m; g.w.rows = c->qkv_rows;
         g.trace = next_trace(); g.max_ring = c->ring_role[0] ? c->ring_role[0] : c->gemv_ring;
@@ -352,22 +382,22 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
             bq = c->tensor(VB_ROLE_BQ, L).m.data; bk = c->tensor(VB_ROLE_BK, L).m.data; bv = c->tensor(VB_ROLE_BV, L).m.data;
             bf = c->tensor(VB_ROLE_BQ, L).m.fmt;
         }
-        const bool fused_append = (c->hq / c->hkv) <= 8 && c->fuse_append;
+        const bool fused_append = (c->hq / c->hkv) <= 8 && c->fuse_append && io.fused_append;
         if (!fused_append)
-            VB_TRY(bias_rope_kv_append(lcfg(c, true), c->q, c->qkv, state, bq, bk, bv, bf, kv_layer, c->block_table_dev,
+            VB_TRY(bias_rope_kv_append(lcfg(c, true), io.q, io.qkv, state, bq, bk, bv, bf, kv_layer, io.block_table,
                                        c->max_blocks, c->hq, c->hkv, d.head_dim, d.kv_block_tokens, d.rope_theta, B));
         // split-K attention over the paged cache (with the bias + RoPE + KV append fused in when possible)
         AttnArgs a;
-        a.out = c->attn_out; a.q = c->q; a.k = kv_layer; a.kv_fp16 = 1;
-        if (fused_append) { a.qkv_raw = c->qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; a.rope_inv_freq_host = c->rope_inv_freq_host.data(); }
-        a.block_table = c->block_table_dev; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
+        a.out = io.attn_out; a.q = io.q; a.k = kv_layer; a.kv_fp16 = 1;
+        if (fused_append) { a.qkv_raw = io.qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; a.rope_inv_freq_host = c->rope_inv_freq_host.data(); }
+        a.block_table = io.block_table; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
         a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         a.trace = next_trace(); a.err = c->err_word;
         VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
-        o.state = state; o.batch = B; o.x = c->attn_out; o.dst = row_dst; o.epilogue = row_epi;
+        o.state = state; o.batch = B; o.x = io.attn_out; o.dst = row_dst; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
         o.trace = next_trace(); o.max_ring = c->ring_role[1] ? c->ring_role[1] : c->gemv_ring;
         pushed = false;
@@ -376,14 +406,14 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
         VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
         GemvArgs gu;
-        gu.state = state; gu.batch = B; gu.x = c->hidden; gu.dst = c->act; gu.epilogue = EPI_SWIGLU;
+        gu.state = state; gu.batch = B; gu.x = io.hidden; gu.dst = io.act; gu.epilogue = EPI_SWIGLU;
         gu.norm_w = c->tensor(VB_ROLE_MLP_NORM, L).m.data; gu.norm_fmt = c->tensor(VB_ROLE_MLP_NORM, L).m.fmt; gu.eps = d.rms_eps;
         gu.w = c->tensor(VB_ROLE_WGATE, L).m; gu.w2 = c->tensor(VB_ROLE_WUP, L).m;
         gu.trace = next_trace(); gu.max_ring = c->ring_role[2] ? c->ring_role[2] : c->gemv_ring;
         VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
         // down projection + residual
         GemvArgs dn;
-        dn.state = state; dn.batch = B; dn.x = c->act; dn.dst = row_dst; dn.epilogue = row_epi;
+        dn.state = state; dn.batch = B; dn.x = io.act; dn.dst = row_dst; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
         dn.trace = next_trace(); dn.max_ring = c->ring_role[3] ? c->ring_role[3] : c->gemv_ring;
         pushed = false;
@@ -393,16 +423,16 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head) {
     }
     if (with_head) {
         GemvArgs h;
-        h.state = state; h.batch = B; h.x = c->hidden; h.dst = c->logits;
+        h.state = state; h.batch = B; h.x = io.hidden; h.dst = io.logits;
         h.norm_w = c->tensor(VB_ROLE_FINAL_NORM, 0).m.data; h.norm_fmt = c->tensor(VB_ROLE_FINAL_NORM, 0).m.fmt; h.eps = d.rms_eps;
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
         h.trace = next_trace(); h.max_ring = c->head_ring;
         VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
         if (!tp) {
-            VB_TRY(argmax(lcfg(c, true), nullptr, c->logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
+            VB_TRY(argmax(lcfg(c, true), nullptr, io.logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
         } else {
             // vocab-parallel head: best (value, global index) per rank, gathered, same tie rule over the ranks
-            VB_TRY(argmax_shard(lcfg(c, true), c->tp_pair, c->logits, c->vocab, c->vocab_off, B, c->cand_v, c->cand_i, state));
+            VB_TRY(argmax_shard(lcfg(c, true), c->tp_pair, io.logits, c->vocab, c->vocab_off, B, c->cand_v, c->cand_i, state));
             if (p2p) {
                 VB_TRY(tp_argmax(lcfg(c, true), c->links, c->tp_pair, B, 2 * d.n_layers, n_sites, state, c->ring_dev, RING_SLOTS, c->err_word));
             } else {
@@ -558,7 +588,8 @@ int32_t vb_destroy(vb_ctx* c) {
         if (c->links.base[r] && r != c->links.rank) { if (c->links_standin) cudaFree(c->links.base[r]); else cudaIpcCloseMemHandle(c->links.base[r]); }
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
-                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs};
+                     c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
+                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -816,10 +847,39 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
     }
     VB_CUDA(cudaMemcpyAsync(c->pf_tokens, tokens, (size_t)n_tokens * 4, cudaMemcpyHostToDevice, c->stream));
     VB_CUDA(cudaMemsetAsync(c->pf_state, 0, c->d.max_batch * sizeof(SeqState), c->stream));
+    // Chunked part: all but the last token, `prefill_chunk` at a time.  Every token of a chunk is a row of one step:
+    // the batched kernels read the weights once for the chunk, K/V of all rows are appended before attention and row
+    // j attends positions 0..first+j, so the result is the causal one.  (The reference's batched prefill driver:
+    // velox_cuda_runner_k2.cu:1614-1704.)  Sharded contexts and the last token take the per-token path below.
+    uint32_t done = 0;
+    const uint32_t P = c->prefill_chunk;
+    if (P >= 2 && P <= 32 && c->d.tp_size <= 1 && n_tokens > P) {
+        if (c->pfc_rows != P) {
+            void* old[] = {c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
+            for (void* p : old) if (p) cudaFree(p);
+            c->pfc_state = nullptr; c->pfc_table = nullptr; c->pfc_hidden = c->pfc_qkv = c->pfc_q = c->pfc_attn = c->pfc_act = nullptr;
+            c->pfc_rows = 0;
+            if ((rc = dev_alloc(&c->pfc_state, P)) != VB_OK || (rc = dev_alloc(&c->pfc_table, (uint64_t)P * c->max_blocks)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_hidden, (uint64_t)P * c->d.d_model)) != VB_OK || (rc = dev_alloc(&c->pfc_qkv, (uint64_t)P * c->qkv_rows)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_q, (uint64_t)P * c->qdim)) != VB_OK || (rc = dev_alloc(&c->pfc_attn, (uint64_t)P * c->qdim)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_act, (uint64_t)P * c->ffn)) != VB_OK)
+                return rc;
+            c->pfc_rows = P;
+        }
+        for (uint32_t j = 0; j < P; ++j)
+            VB_CUDA(cudaMemcpyAsync(c->pfc_table + (size_t)j * c->max_blocks, c->block_table_dev + (size_t)slot * c->max_blocks,
+                                    (size_t)c->max_blocks * 4, cudaMemcpyDeviceToDevice, c->stream));
+        const StepIO io{c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, nullptr, c->pfc_table, P, false};
+        while (done + P < n_tokens) {  // leaves at least one token for the per-token path (it produces the logits)
+            VB_CUDA(launch(lcfg(c, false), k_set_chunk_state, dim3(1), dim3(32), 0, c->pfc_state, (const uint32_t*)c->pf_tokens, done, P, P));
+            VB_CUDA(enqueue_step(c, c->pfc_state, false, io));
+            done += P;
+        }
+    }
     // the reference prefills one token per forward pass (velox_cuda_runner.cu:504-506)
-    for (uint32_t i = 0; i < n_tokens; ++i) {
+    for (uint32_t i = done; i < n_tokens; ++i) {
         VB_CUDA(launch(lcfg(c, false), k_set_state, dim3(1), dim3(32), 0, c->pf_state, (uint32_t)slot, (const uint32_t*)c->pf_tokens, i, 0u, i, 1u));
-        VB_CUDA(enqueue_step(c, c->pf_state, i + 1 == n_tokens));
+        VB_CUDA(enqueue_step(c, c->pf_state, i + 1 == n_tokens, decode_io(c)));
     }
     // hand the slot over to the decode state: first generated token at position n_tokens
     VB_CUDA(cudaMemcpyAsync(c->state + slot, c->pf_state + slot, sizeof(SeqState), cudaMemcpyDeviceToDevice, c->stream));
@@ -831,7 +891,7 @@ int32_t vb_decode_step(vb_ctx* c) {
     int32_t rc = check_ready(c, "vb_decode_step");
     if (rc != VB_OK) return rc;
     VB_CUDA(cudaSetDevice(c->device));
-    VB_CUDA(enqueue_step(c, c->state, true));
+    VB_CUDA(enqueue_step(c, c->state, true, decode_io(c)));
     return VB_OK;
 }
 
@@ -844,7 +904,7 @@ int32_t vb_decode_graph_build(vb_ctx* c) {
     for (int attempt = 0; attempt < 2; ++attempt) {
         const uint64_t before = c->launches;
         VB_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
-        cudaError_t e = enqueue_step(c, c->state, true);
+        cudaError_t e = enqueue_step(c, c->state, true, decode_io(c));
         cudaGraph_t g = nullptr;
         cudaError_t e2 = cudaStreamEndCapture(c->stream, &g);
         c->graph_nodes = c->launches - before;
@@ -879,7 +939,7 @@ int32_t vb_decode_run(vb_ctx* c, uint32_t n_steps, float* elapsed_ms) {
             VB_CUDA(cudaGraphLaunch(c->graph_exec, c->stream));
             c->launches += c->graph_nodes;
         } else {
-            VB_CUDA(enqueue_step(c, c->state, true));
+            VB_CUDA(enqueue_step(c, c->state, true, decode_io(c)));
         }
     }
     if (elapsed_ms) {
@@ -992,6 +1052,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "gemv_path")) { c->gemv_path = (int)value; return VB_OK; }
     if (!strcmp(name, "pdl")) { c->use_pdl = value != 0; return VB_OK; }
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
+    if (!strcmp(name, "prefill_chunk")) { c->prefill_chunk = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "trace")) {
         if (value && !c->trace) {
             VB_CUDA(cudaMalloc((void**)&c->trace, 1024 * 4 * sizeof(unsigned long long)));
