@@ -193,6 +193,23 @@ def test_lockstep_prefill_matches_the_checker():
     eng.close()
 
 
+@pytest.mark.parametrize("spec_i", [0, 2, 7])
+def test_chunked_prefill_agrees_with_token_by_token(spec_i):
+    """Prompt tokens sent through the layers 16 (or 5) at a time give the tokens of the one-by-one prefill, and
+    logits within the path's tolerance (the batched kernels sum in another order)."""
+    spec = SMALL_SPECS[spec_i]
+    prompt = H.prompt_tokens(spec, 3, 71)
+    outs = []
+    for chunk in (1, 16, 5):
+        eng = H.build_engine(spec, 3, 96)
+        eng.set_option("prefill_chunk", chunk)
+        outs.append((eng.generate_greedy(prompt, 10), eng.logits()))
+        eng.close()
+    for toks, lg in outs[1:]:
+        assert np.array_equal(toks, outs[0][0])
+        assert float(np.max(np.abs(lg - outs[0][1]))) <= LOGIT_TOL
+
+
 def test_engine_argument_errors():
     spec = H.TINY
     eng = H.build_engine(spec, 1, 32)
