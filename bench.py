@@ -103,6 +103,8 @@ def workload_spec(name: str):
         return LLAMA3_8B_INT4, 1
     if name == "qwen2.5-7b-int8-bs1":  # the int8 per-channel model shape, one sequence
         return QWEN25_7B_INT8, 1
+    if name == "qwen2.5-7b-int8-bs32":  # 32 sequences, prompt lengths uniform in [256, 2048]
+        return QWEN25_7B_INT8, 32
     if name == "qwen2-72b-int4-tp-bs1":
         return QWEN2_72B_INT4, 1
     if name == "qwen2-72b-int4-tp-bs16":  # 16 sequences per step (sharded: the unsharded model only fits with one)
@@ -210,7 +212,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from velox_b200.engine import Engine
-    max_seq = args.prompt_len + args.warmup + 2 * args.steps + 16
+    # prompt length per slot: all equal, except the variable-length batch workload
+    prompt_lens = [args.prompt_len] * batch
+    if args.workload == "qwen2.5-7b-int8-bs32":
+        prompt_lens = [int(x) for x in np.random.default_rng(SEED).integers(256, 2049, size=batch)]
+    max_seq = max(prompt_lens) + args.warmup + 2 * args.steps + 16
     tp = is_tp(args.workload)
     if tp and world > 1:
         # one model over all ranks; the 72B shape only fits one GPU with the single-layout arena
@@ -244,7 +250,7 @@ def main():
         from velox_b200.modelspec import PROMPT_STREAM
         for slot in range(batch):
             eng.reserve(slot, max_seq)
-        eng.prefill_lockstep([H.prompt_tokens(spec, SEED, args.prompt_len, stream=PROMPT_STREAM + slot) for slot in range(batch)])
+        eng.prefill_lockstep([H.prompt_tokens(spec, SEED, prompt_lens[slot], stream=PROMPT_STREAM + slot) for slot in range(batch)])
     eng.sync()
     ttft_s = time.perf_counter() - t0
     eng.build_graph()
@@ -277,6 +283,7 @@ def main():
 
     # ---- end to end: every step driven from the host through the C ABI ----------------------------------
     tok, pos = eng.state(0)
+    eng_pos = [eng.state(slot)[1] for slot in range(batch)]  # position of every slot's next token
     barrier()
     t0 = time.perf_counter()
     if batch == 1:
@@ -287,8 +294,8 @@ def main():
         for _ in range(args.steps):               # tokens feed back on the device; the host reads every slot's token
             eng.decode(1)
             for slot in range(batch):
-                eng.read_tokens(slot, pos, 1)
-            pos += 1
+                eng.read_tokens(slot, eng_pos[slot], 1)
+                eng_pos[slot] += 1
     e2e_s = time.perf_counter() - t0
     if sampler.rows == []:
         # very short runs: keep the GPU busy until the sampler has something to report
@@ -310,7 +317,7 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len,
+        "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len if len(set(prompt_lens)) == 1 else "uniform in [256, 2048]",
                    "weights": ("int8 per output channel + fp16 scales" if "int8" in spec.name else "int4 g32 + fp16 scales") +
                               ", fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
                    "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),

@@ -24,6 +24,10 @@ SMALL_SPECS = [
                           weight_fmt=L.FMT_Q4G64REF, head_fmt=L.FMT_Q4G64REF, embed_fmt=L.FMT_Q4G64REF, tied_lm_head=True),
     LLAMA3_8B_INT4.scaled(name="llama-bf16-small", d_model=256, n_layers=2, n_q_heads=4, n_kv_heads=4, head_dim=64, ffn_dim=512, vocab=1024,
                           weight_fmt=L.FMT_BF16, head_fmt=L.FMT_BF16, embed_fmt=L.FMT_BF16),
+    # a GQA group of 8 with QKV bias (the tensor-core attention's full N = 8) and a 256-wide head
+    LLAMA3_8B_INT4.scaled(name="gqa8-bias-int4-small", d_model=512, n_layers=2, n_q_heads=8, n_kv_heads=1, head_dim=64, ffn_dim=1408, vocab=4096,
+                          qkv_bias=True),
+    LLAMA3_8B_INT4.scaled(name="head256-int4-small", d_model=512, n_layers=2, n_q_heads=2, n_kv_heads=1, head_dim=256, ffn_dim=1408, vocab=4096),
     # int8 per-channel in shapes the integer tensor-core kernel tiles (K multiples of 128, rows of 16)
     QWEN25_7B_INT8.scaled(name="qwen-int8-tiled", d_model=512, n_layers=3, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1408, vocab=4096),
 ]
@@ -193,7 +197,7 @@ def test_lockstep_prefill_matches_the_checker():
     eng.close()
 
 
-@pytest.mark.parametrize("spec_i", [0, 2, 7])
+@pytest.mark.parametrize("spec_i", [0, 2, 9])
 def test_chunked_prefill_agrees_with_token_by_token(spec_i):
     """Prompt tokens sent through the layers 16 (or 5) at a time give the tokens of the one-by-one prefill, and
     logits within the path's tolerance (the batched kernels sum in another order)."""
