@@ -155,11 +155,13 @@ def test_lean_weight_layout_is_bit_identical_and_smaller():
     lean.close()
 
 
-def test_batched_variable_length_sequences():
-    """Several slots with different prompt lengths decode together; each matches its own CPU run."""
-    spec = SMALL_SPECS[4]
+@pytest.mark.parametrize("spec_i", [4, 2, 9])
+def test_batched_variable_length_sequences(spec_i):
+    """Several slots with different prompt lengths decode together; each matches its own CPU run.  Six slots are
+    two weight passes of the multi-row integer kernel (four rows, then one active and one inactive row)."""
+    spec = SMALL_SPECS[spec_i]
     seed, n_new = 31, 10
-    lens = [5, 23, 16, 1]
+    lens = [5, 23, 16, 1, 9]
     max_seq = max(lens) + n_new + 1
     ora, _ = H.build_oracle(spec, seed, max_seq, n_seqs=len(lens))
     eng = H.build_engine(spec, seed, max_seq, max_batch=len(lens) + 1)  # one slot stays inactive

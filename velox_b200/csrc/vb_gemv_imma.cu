@@ -61,6 +61,8 @@ struct ImmaArgs {
     int epilogue;            // EPI_STORE / EPI_RESIDUAL / EPI_SWIGLU (interleaved 8+8 tiles)
     unsigned long long* trace;  // optional timestamp record
     uint32_t spread;            // tile -> (block, group) mapping, see the kernel
+    uint32_t nb_rows;           // multi-row flavour: rows of x / dst / state this launch serves (1..4)
+    uint32_t dst_stride;        // multi-row flavour: elements between the rows of dst
     // tensor parallel (EPI_STORE of a row-parallel product): the output rows also go to every peer's receive
     // region as sequence-tagged 16-byte words {row 2i, seq, row 2i+1, seq}; push_size == 0: no push
     unsigned char* push_base[8];
@@ -171,7 +173,12 @@ __device__ __forceinline__ void issue_block(const unsigned char* __restrict__ w,
 // I8 selects the int8 per-channel weight format: blocks of 2048 bytes whose 16-byte pieces ARE the A fragments
 // (lane L of k-step j at 512*j + 16*L: rows g and g+8, columns 4t..4t+3 and 16+4t..16+4t+3 of the step), no
 // unpacking and no per-group weight scale -- the row scale is applied once in the epilogue.
-template <int NS, int W>
+// NB = 4 is the multi-row flavour: up to four rows of x (sequences of a batch, or prompt tokens of a prefill
+// chunk) share one pass over the weights.  The eight B columns of an mma then carry (row r, H|L) for r = 0..3 of
+// ONE quantization group, so every group needs its own mma and its own rescale (the four-groups-in-one-
+// accumulator trick of the single-row kernel needs the columns for itself): ~1.3-1.6x the instructions of a
+// single-row pass for four times the rows.
+template <int NS, int W, int NB>
 __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     constexpr int BLK = ImBlk<W>::bytes;
     constexpr bool I8 = W == IM_I8;
@@ -179,9 +186,12 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t K = a.K, KT = K / (128 * SUB), n_tiles = a.rows / 16;  // KT: steps along K of one tile
     unsigned char* ring = smem_raw;                                              // [IM_GROUPS * IM_WARPS][NS][IM_BLK_BYTES]
-    unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * BLK;          // [K/32][64]
-    int2* sxp = reinterpret_cast<int2*>(xq + (size_t)K * 2);                     // [K/32] {sum(X), 1/p}
-    float* red = reinterpret_cast<float*>(sxp + K / 32);                         // [IM_GROUPS][2][IM_WARPS][16]
+    // the rows of the multi-row flavour are padded so that the four rows a warp reads together fall into different banks
+    constexpr uint32_t XPAD = NB > 1 ? 64 : 0, SPAD = NB > 1 ? 4 : 0;  // bytes per row of xq, int2 per row of sxp
+    const uint32_t xrow = K * 2 + XPAD, srow = K / 32 + SPAD;
+    unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * BLK;          // [NB][K/32][64] (+ pad)
+    int2* sxp = reinterpret_cast<int2*>(xq + (size_t)NB * xrow);                 // [NB][K/32] {sum(X), 1/p} (+ pad)
+    float* red = reinterpret_cast<float*>(sxp + (size_t)NB * srow);              // [IM_GROUPS][2][IM_WARPS][16][NB]
     __shared__ float ssq[IM_GROUPS * IM_WARPS];
 
     const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -219,22 +229,34 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     // ---- x: only now wait for the producer kernel ----------------------------------------------------------------
     pdl_wait();
     trace_mark(a.trace, 1);
-    const bool active = !a.state || a.state[0].active;  // an inactive slot still drains the pipeline, skipping x
+    bool act[NB];  // an inactive row still drains the pipeline, skipping x
+    bool active = false;
+#pragma unroll
+    for (int r = 0; r < NB; ++r) {
+        act[r] = (NB == 1 || (uint32_t)r < a.nb_rows) && (!a.state || a.state[r].active);
+        active = active || act[r];
+    }
     // the step's exchange counter (advanced once at the start of the step), for the sequence tags of pushed rows
     unsigned long long push_epoch = 0;
     if (a.push_size > 1) push_epoch = *reinterpret_cast<const volatile unsigned long long*>(a.push_base[a.push_rank] + a.push_epoch_off);
 
     // x -> shared memory.  All of a thread's loads of a batch are issued before any value is used: one memory
     // trip per batch of XC * 4096 elements (the whole row up to 16384 elements), not one per chunk.
-    {
-        const float* x = a.x;
+#pragma unroll 1
+    for (int row = 0; row < NB; ++row) {
+        const float* x = a.x + (size_t)row * K;
+        unsigned char* xq_r = xq + (size_t)row * xrow;
+        int2* sxp_r = sxp + (size_t)row * srow;
+        bool active_r = act[0];
+#pragma unroll
+        for (int r = 1; r < NB; ++r) if (r == row) active_r = act[r];
         float xr[XC][8];
         auto load_batch = [&](uint32_t it0) {
 #pragma unroll
             for (int i = 0; i < XC; ++i) {
                 const uint32_t c = threadIdx.x + (it0 + i) * IM_CONSUMERS;
                 float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-                if (active && c < n_chunks) { v0 = *reinterpret_cast<const float4*>(x + c * 8); v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4); }
+                if (active_r && c < n_chunks) { v0 = *reinterpret_cast<const float4*>(x + c * 8); v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4); }
                 xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
                 xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
             }
@@ -242,7 +264,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         const uint32_t n_it = (n_chunks + IM_CONSUMERS - 1) / IM_CONSUMERS;  // chunk rounds of the whole block
         float ss = 0.0f;
         if (in_regs) load_batch(0);
-        if (active && a.norm_w) {
+        if (active_r && a.norm_w) {
             for (uint32_t it0 = 0; it0 < n_it; it0 += XC) {
                 if (!in_regs) load_batch(it0);
 #pragma unroll
@@ -255,7 +277,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         }
         im_consumer_sync();
         float inv = 1.0f;
-        if (a.norm_w && active) {
+        if (a.norm_w && active_r) {
             float tot = 0.0f;
 #pragma unroll
             for (int w = 0; w < IM_GROUPS * IM_WARPS; ++w) tot += ssq[w];
@@ -267,7 +289,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
             for (int i = 0; i < XC; ++i) {
                 if (it0 + i < n_it) {  // uniform over the block: every lane of a warp stages together
                     const uint32_t c = threadIdx.x + (it0 + i) * IM_CONSUMERS;
-                    const bool valid = active && c < n_chunks;  // groups of 4 lanes are valid together
+                    const bool valid = active_r && c < n_chunks;  // groups of 4 lanes are valid together
                     float v[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) v[e] = xr[i][e];
@@ -287,7 +309,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                             for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
                         }
                     }
-                    im_stage_chunk(xq, sxp, v, c, valid);
+                    im_stage_chunk(xq_r, sxp_r, v, c, valid);
                 }
             }
         }
@@ -297,13 +319,30 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
     uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
-    const unsigned char* xq_lane = xq + (size_t)gj * 64 + plane * 32 + 8 * t;
+    // single row: column g of B is (group gj of a block, plane); multi-row: (row gj of x, plane) of one group at a time
+    const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)gj * xrow + plane * 32 + 8 * t;
+    const int2* sxp_lane = sxp + (size_t)t * srow;  // multi-row: lane (g,t) ends up with the sums of row t of x
+    // multi-row epilogue: thread gt < 32 of a group owns mma rows e_row and e_row + 8 of row e_seq of x
+    const uint32_t e_row = gt >> 2, e_seq = gt & 3;
+    bool e_act = act[0];
+#pragma unroll
+    for (int r = 1; r < NB; ++r) if ((uint32_t)r == e_seq) e_act = act[r];
+    e_act = e_act && gt < 32;
+    float* e_dst = a.dst + (size_t)e_seq * a.dst_stride + a.dst_offset;
     for (uint32_t tile = vtile0; tile < n_tiles; tile += vstride, parity ^= 1) {
         // residual rows fetched early so that the epilogue does not wait on them
-        float resid = 0.0f;
-        if (a.epilogue == EPI_RESIDUAL && gt < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + gt];
-        float row_scale = 1.0f;
-        if (I8 && gt < 16) row_scale = __half2float(a.wscales[(size_t)tile * 16 + gt]);
+        float resid = 0.0f, resid1 = 0.0f;
+        float row_scale = 1.0f, row_scale1 = 1.0f;
+        if constexpr (NB == 1) {
+            if (a.epilogue == EPI_RESIDUAL && gt < 16 && active) resid = a.dst[a.dst_offset + tile * 16 + gt];
+            if (I8 && gt < 16) row_scale = __half2float(a.wscales[(size_t)tile * 16 + gt]);
+        } else {
+            if (a.epilogue == EPI_RESIDUAL && e_act) { resid = e_dst[tile * 16 + e_row]; resid1 = e_dst[tile * 16 + e_row + 8]; }
+            if (I8 && gt < 32) {
+                row_scale = __half2float(a.wscales[(size_t)tile * 16 + e_row]);
+                row_scale1 = __half2float(a.wscales[(size_t)tile * 16 + e_row + 8]);
+            }
+        }
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
         for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
@@ -313,7 +352,51 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
             __syncwarp();
             if (active) {
                 const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * BLK;
-                if constexpr (I8) {
+                if constexpr (NB > 1) {
+#pragma unroll
+                    for (int sub = 0; sub < SUB; ++sub) {
+                        const unsigned char* sb = blk + sub * IM_BLK_BYTES;  // SUB == 1 for int8
+                        const uint32_t kb = kk * SUB + sub;                  // 16x128 block index along K
+                        const unsigned char* xb = xq_lane + (size_t)kb * 256;
+                        // {sum(X), 1/p} of this lane's row of x for the block's four groups
+                        const int4 s01 = reinterpret_cast<const int4*>(sxp_lane + kb * 4)[0];
+                        const int4 s23 = reinterpret_cast<const int4*>(sxp_lane + kb * 4)[1];
+                        const int sx[4] = {s01.x, s01.z, s23.x, s23.z};
+                        const float ip[4] = {__int_as_float(s01.y), __int_as_float(s01.w), __int_as_float(s23.y), __int_as_float(s23.w)};
+                        if constexpr (I8) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint4 af = reinterpret_cast<const uint4*>(sb + j * 512)[lane];
+                                const uint2 bx = *reinterpret_cast<const uint2*>(xb + j * 64);
+                                int d[4] = {0, 0, 0, 0};
+                                imma_16832(d, af.x, af.y, af.z, af.w, bx.x, bx.y, d);
+                                // lane (g,t): sums of q * H and q * L of row t of x over group j, for weight rows g and g+8
+                                acc0 = fmaf((float)(d[0] * 256 + d[1]), ip[j], acc0);
+                                acc1 = fmaf((float)(d[2] * 256 + d[3]), ip[j], acc1);
+                            }
+                        } else {
+                            const uint4 wa = reinterpret_cast<const uint4*>(sb)[lane];
+                            const uint4 wb = reinterpret_cast<const uint4*>(sb + 512)[lane];
+                            // scales of rows g and g+8 for the four groups: 16 consecutive bytes
+                            const uint4 sq = *reinterpret_cast<const uint4*>(sb + 1024 + 16 * g);
+                            const uint32_t war[4] = {wa.x, wa.y, wa.z, wa.w};
+                            const uint32_t wbr[4] = {wb.x, wb.y, wb.z, wb.w};
+                            const uint32_t scr[4] = {sq.x, sq.y, sq.z, sq.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t msk = 0x0F0F0F0Fu;
+                                const uint2 bx = *reinterpret_cast<const uint2*>(xb + j * 64);
+                                int d[4] = {0, 0, 0, 0};
+                                imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, bx.x, bx.y, d);
+                                const int r0 = d[0] * 256 + d[1] - 8 * sx[j];
+                                const int r1 = d[2] * 256 + d[3] - 8 * sx[j];
+                                const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&scr[j]));
+                                acc0 = fmaf((float)r0 * ip[j], s2.x, acc0);
+                                acc1 = fmaf((float)r1 * ip[j], s2.y, acc1);
+                            }
+                        }
+                    }
+                } else if constexpr (I8) {
                     // B operand: bytes of group gj of this block (k = 4t..4t+3 and 16+4t..16+4t+3), zero for the other groups
                     const uint2 bx = *reinterpret_cast<const uint2*>(xq_lane + (size_t)kk * 256);
                     const float ip = __int_as_float(sxp[kk * 4 + t].y);
@@ -359,6 +442,29 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                 }
             }
             __syncwarp();  // every lane is done with the slot before the next iteration overwrites its predecessor
+        }
+        if constexpr (NB > 1) {
+            // every lane holds its own (weight row, row of x): only the 8 warps remain to be added
+            float* rbuf = red + ((size_t)group * 2 + parity) * (IM_WARPS * 16 * NB);
+            rbuf[warp * 64 + g * 4 + t] = acc0;
+            rbuf[warp * 64 + 32 + g * 4 + t] = acc1;
+            im_group_sync(group);
+            if (e_act) {
+                float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+                for (int w = 0; w < IM_WARPS; ++w) { v0 += rbuf[w * 64 + gt]; v1 += rbuf[w * 64 + 32 + gt]; }
+                if constexpr (I8) { v0 *= row_scale; v1 *= row_scale1; }
+                if (a.epilogue == EPI_SWIGLU) {
+                    e_dst[tile * 8 + e_row] = (v0 / (1.0f + expf(-v0))) * v1;  // mma rows 0..7 gate, 8..15 up
+                } else if (a.epilogue == EPI_RESIDUAL) {
+                    e_dst[tile * 16 + e_row] = resid + v0;
+                    e_dst[tile * 16 + e_row + 8] = resid1 + v1;
+                } else {
+                    e_dst[tile * 16 + e_row] = v0;
+                    e_dst[tile * 16 + e_row + 8] = v1;
+                }
+            }
+            continue;
         }
         // the four lanes of a row hold different groups: add them, then reduce the 8 warps through shared memory
         acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 1); acc0 += __shfl_xor_sync(0xFFFFFFFFu, acc0, 2);
@@ -464,13 +570,18 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
     return tile_v3_half(lc, tiled, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
 }
 
+constexpr int IM_NB = 4;  // rows of x per weight pass of the multi-row flavour
+
 template <int W>
 static cudaError_t imma_opt_in() {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<2, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
 }
 cudaError_t gemv_imma_init() {
     cudaError_t e = imma_opt_in<IM_Q4>();
@@ -481,14 +592,28 @@ bool imma_spread = false;  // deal a round's tiles to blocks first, then to the 
 int imma_pair_ring = 3;  // int4, even number of k-blocks: two blocks per step with this ring depth (0 = one block per step)
 
 bool imma_enabled = true;  // vb_set_option("gemv_imma", 0) routes batch 1 to the fp16-mma kernels
+bool imma_multirow = true; // vb_set_option("gemv_multirow", 0) routes batch > 1 to the fp16-mma kernels
 
-template <int W>
+// shared memory besides the ring: staged x (+ row padding), group sums, the reduction buffers, slack for alignment
+static size_t imma_fixed_smem(uint32_t K, int nb) {
+    const size_t xrow = (size_t)K * 2 + (nb > 1 ? 64 : 0), srow = (size_t)(K / 32 + (nb > 1 ? 4 : 0)) * 8;
+    return (size_t)nb * (xrow + srow) + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 * nb + 256;
+}
+// ring depth that fits (0: none)
+static size_t imma_ring_depth(uint32_t K, int nb, size_t blk_bytes) {
+    const size_t fixed = imma_fixed_smem(K, nb), stage = (size_t)IM_GROUPS * IM_WARPS * blk_bytes;
+    if (fixed + 2 * stage > (size_t)IM_MAX_SMEM) return 0;
+    return ((size_t)IM_MAX_SMEM - fixed) / stage;
+}
+
+template <int W, int NB>
 static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t max_ring) {
-    const size_t fixed = (size_t)f.K * 2 + (size_t)(f.K / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
+    const size_t fixed = imma_fixed_smem(f.K, NB);
     const size_t stage = (size_t)IM_GROUPS * IM_WARPS * ImBlk<W>::bytes;  // one ring slot of every warp
-    if (fixed + 2 * stage > (size_t)IM_MAX_SMEM) return cudaErrorInvalidConfiguration;
-    size_t ns = ((size_t)IM_MAX_SMEM - fixed) / stage;
+    size_t ns = imma_ring_depth(f.K, NB, ImBlk<W>::bytes);
+    if (ns == 0) return cudaErrorInvalidConfiguration;
     if (max_ring >= 2 && ns > max_ring) ns = max_ring;
+    if (NB > 1 && ns > 4) ns = 4;
     ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : (ns >= 3 ? 3 : 2));  // ring depth per warp (template parameter); 4 measured fastest
     static int n_sm = 0;
     if (n_sm == 0) {
@@ -500,25 +625,30 @@ static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t 
     const uint32_t want = f.spread ? n_tiles : (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
     const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
     const size_t smem = fixed + ns * stage;
-    if (ns == 8) return launch(lc, k_gemv_q4_imma<8, W>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 4) return launch(lc, k_gemv_q4_imma<4, W>, grid, dim3(IM_CONSUMERS), smem, f);
-    if (ns == 3) return launch(lc, k_gemv_q4_imma<3, W>, grid, dim3(IM_CONSUMERS), smem, f);
-    return launch(lc, k_gemv_q4_imma<2, W>, grid, dim3(IM_CONSUMERS), smem, f);
+    if constexpr (NB == 1) {
+        if (ns == 8) return launch(lc, k_gemv_q4_imma<8, W, 1>, grid, dim3(IM_CONSUMERS), smem, f);
+    }
+    if (ns == 4) return launch(lc, k_gemv_q4_imma<4, W, NB>, grid, dim3(IM_CONSUMERS), smem, f);
+    if (ns == 3) return launch(lc, k_gemv_q4_imma<3, W, NB>, grid, dim3(IM_CONSUMERS), smem, f);
+    return launch(lc, k_gemv_q4_imma<2, W, NB>, grid, dim3(IM_CONSUMERS), smem, f);
 }
 
 cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     *handled = false;
     const bool i8 = a.w.fmt == VB_FMT_I8PC;
-    if (!imma_enabled || a.batch != 1 || !(a.w.fmt == VB_FMT_Q4G32 || i8)) return cudaSuccess;
+    if (!imma_enabled || !(a.w.fmt == VB_FMT_Q4G32 || i8)) return cudaSuccess;
+    const bool multi = a.batch > 1;
+    if (multi && !imma_multirow) return cudaSuccess;
     const bool swiglu = a.epilogue == EPI_SWIGLU;
     const void* w = swiglu ? a.w.v3_swiglu : a.w.v3;
     if (!w || a.w.cols % 128 != 0) return cudaSuccess;
     if (swiglu && (a.w2.rows != a.w.rows || a.w2.cols != a.w.cols)) return cudaSuccess;
     const uint32_t rows = swiglu ? 2 * a.w.rows : a.w.rows;
     if (rows % 16 != 0) return cudaSuccess;
-    const size_t fixed = (size_t)a.w.cols * 2 + (size_t)(a.w.cols / 32) * 8 + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 + 256;
-    if (fixed + 2 * (size_t)IM_GROUPS * IM_WARPS * (i8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES) > (size_t)IM_MAX_SMEM) return cudaSuccess;
+    if (imma_ring_depth(a.w.cols, multi ? IM_NB : 1, i8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES) == 0) return cudaSuccess;
     ImmaArgs f;
+    f.nb_rows = 1;
+    f.dst_stride = a.dst_stride ? a.dst_stride : a.w.rows;
     f.w = (const unsigned char*)w; f.rows = rows; f.K = a.w.cols; f.x = a.x; f.dst = a.dst;
     // int8: the row scales follow the blocks of the (whole, possibly fused or interleaved) matrix
     f.wscales = i8 ? reinterpret_cast<const __half*>((const unsigned char*)w + (size_t)rows * a.w.cols) : nullptr;
@@ -527,7 +657,7 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     f.trace = a.trace;
     f.spread = imma_spread ? 1u : 0u;
     f.push_size = 0;
-    if (a.push.links && a.epilogue == EPI_STORE && a.push.links->size > 1 && a.dst_offset % 2 == 0) {
+    if (!multi && a.push.links && a.epilogue == EPI_STORE && a.push.links->size > 1 && a.dst_offset % 2 == 0) {
         const TpLinks& l = *a.push.links;
         for (int r = 0; r < 8; ++r) f.push_base[r] = l.base[r];
         f.push_rank = l.rank; f.push_size = l.size; f.push_site = a.push.site; f.push_n_sites = a.push.n_sites;
@@ -535,10 +665,27 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
         if (a.pushed) *a.pushed = true;
     }
     *handled = true;
-    if (i8) return imma_launch<IM_I8>(lc, f, a.max_ring);
     // two blocks per step when every warp's share of a tile is a whole number of pairs
-    if (imma_pair_ring >= 2 && (a.w.cols / 128) % (2 * IM_WARPS) == 0) return imma_launch<IM_Q4X2>(lc, f, (uint32_t)imma_pair_ring);
-    return imma_launch<IM_Q4>(lc, f, a.max_ring);
+    const bool pairs = !i8 && imma_pair_ring >= 2 && (a.w.cols / 128) % (2 * IM_WARPS) == 0;
+    if (!multi) {
+        if (i8) return imma_launch<IM_I8, 1>(lc, f, a.max_ring);
+        if (pairs) return imma_launch<IM_Q4X2, 1>(lc, f, (uint32_t)imma_pair_ring);
+        return imma_launch<IM_Q4, 1>(lc, f, a.max_ring);
+    }
+    // batch > 1: passes of up to IM_NB rows of x, each one trip over the weights
+    const bool pairs_fit = pairs && imma_ring_depth(a.w.cols, IM_NB, 2 * IM_BLK_BYTES) >= 3;
+    for (uint32_t b0 = 0; b0 < a.batch; b0 += IM_NB) {
+        ImmaArgs p = f;
+        p.nb_rows = a.batch - b0 < (uint32_t)IM_NB ? a.batch - b0 : (uint32_t)IM_NB;
+        p.x = a.x + (size_t)b0 * a.w.cols;
+        p.dst = a.dst + (size_t)b0 * f.dst_stride;
+        p.state = a.state ? a.state + b0 : nullptr;
+        const cudaError_t e = i8 ? imma_launch<IM_I8, IM_NB>(lc, p, a.max_ring)
+                            : pairs_fit ? imma_launch<IM_Q4X2, IM_NB>(lc, p, (uint32_t)imma_pair_ring)
+                                        : imma_launch<IM_Q4, IM_NB>(lc, p, a.max_ring);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 // ---- int8 per-channel: canonical [rows][K] bytes + fp16 row scales -> tile-major blocks, then the scales ----

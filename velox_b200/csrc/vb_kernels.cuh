@@ -104,6 +104,7 @@ cudaError_t tile_q4_v3(const LaunchCfg& lc, void* tiled, const void* canon, cons
 cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, const void* canon_scales, uint32_t rows, uint32_t K,
                               int which);
 extern bool imma_enabled;
+extern bool imma_multirow;
 extern int imma_pair_ring;
 extern bool imma_spread;
 
