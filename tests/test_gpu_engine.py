@@ -30,6 +30,9 @@ SMALL_SPECS = [
     LLAMA3_8B_INT4.scaled(name="head256-int4-small", d_model=512, n_layers=2, n_q_heads=2, n_kv_heads=1, head_dim=256, ffn_dim=1408, vocab=4096),
     # int8 per-channel in shapes the integer tensor-core kernel tiles (K multiples of 128, rows of 16)
     QWEN25_7B_INT8.scaled(name="qwen-int8-tiled", d_model=512, n_layers=3, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=1408, vocab=4096),
+    # FFN rows so long that the multi-row integer kernel stages two rows of x per weight pass instead of four
+    QWEN25_7B_INT8.scaled(name="qwen-int8-longk", d_model=512, n_layers=1, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=18944, vocab=2048),
+    LLAMA3_8B_INT4.scaled(name="llama-int4-longk", d_model=512, n_layers=1, n_q_heads=8, n_kv_heads=2, head_dim=64, ffn_dim=20480, vocab=2048),
 ]
 
 
@@ -155,7 +158,7 @@ def test_lean_weight_layout_is_bit_identical_and_smaller():
     lean.close()
 
 
-@pytest.mark.parametrize("spec_i", [4, 2, 9])
+@pytest.mark.parametrize("spec_i", [4, 2, 9, 10, 11])
 def test_batched_variable_length_sequences(spec_i):
     """Several slots with different prompt lengths decode together; each matches its own CPU run.  Six slots are
     two weight passes of the multi-row integer kernel (four rows, then one active and one inactive row)."""

@@ -34,6 +34,8 @@
 // The inner loop is instruction-bound (ALU pipe 53 % busy at 42 % of DRAM peak in isolation, ~149 warp
 // instructions per 16x128 block): anything added per block shows up directly -- a generalised block cursor for
 // multi-product launches or for splitting a last partial tile round cost more than it saved.
+#include <type_traits>
+
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
 
@@ -191,8 +193,8 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     const uint32_t xrow = K * 2 + XPAD, srow = K / 32 + SPAD;
     unsigned char* xq = ring + (size_t)IM_GROUPS * IM_WARPS * NS * BLK;          // [NB][K/32][64] (+ pad)
     int2* sxp = reinterpret_cast<int2*>(xq + (size_t)NB * xrow);                 // [NB][K/32] {sum(X), 1/p} (+ pad)
-    float* red = reinterpret_cast<float*>(sxp + (size_t)NB * srow);              // [IM_GROUPS][2][IM_WARPS][16][NB]
-    __shared__ float ssq[IM_GROUPS * IM_WARPS];
+    float* red = reinterpret_cast<float*>(sxp + (size_t)NB * srow);              // [IM_GROUPS][2][IM_WARPS][16] ([..][64] multi-row)
+    __shared__ float ssq[NB * IM_GROUPS * IM_WARPS];
 
     const uint32_t lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const uint32_t group = wid / IM_WARPS, warp = wid % IM_WARPS;  // tile group, warp within the group
@@ -242,8 +244,86 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
 
     // x -> shared memory.  All of a thread's loads of a batch are issued before any value is used: one memory
     // trip per batch of XC * 4096 elements (the whole row up to 16384 elements), not one per chunk.
+    bool staged = false;
+    if constexpr (NB > 1) {
+        // Rows short enough that all NB of them fit a thread's registers (up to 4096 elements each, 8192 for two
+        // rounds of chunks): ONE memory trip and one pair of barriers for all rows instead of one per row.
+        auto stage_rows = [&](auto prs_c) {
+            constexpr int PRS = decltype(prs_c)::value;  // rounds of 512 chunks per row
+            constexpr int SL = NB * PRS;
+            float xr[SL][8];
+#pragma unroll
+            for (int i = 0; i < SL; ++i) {
+                const int row = i / PRS;
+                const uint32_t c = threadIdx.x + (i % PRS) * IM_CONSUMERS;
+                float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+                if (act[row] && c < n_chunks) {
+                    const float* x = a.x + (size_t)row * K + c * 8;
+                    v0 = *reinterpret_cast<const float4*>(x); v1 = *reinterpret_cast<const float4*>(x + 4);
+                }
+                xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
+                xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
+            }
+            if (a.norm_w) {
+#pragma unroll
+                for (int row = 0; row < NB; ++row) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int sub = 0; sub < PRS; ++sub)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ss = fmaf(xr[row * PRS + sub][e], xr[row * PRS + sub][e], ss);
+                    ss = warp_sum(ss);
+                    if (lane == 0) ssq[row * (IM_GROUPS * IM_WARPS) + wid] = ss;
+                }
+            }
+            im_consumer_sync();
+            float inv[NB];
+#pragma unroll
+            for (int row = 0; row < NB; ++row) {
+                inv[row] = 1.0f;
+                if (a.norm_w && act[row]) {
+                    float tot = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < IM_GROUPS * IM_WARPS; ++w) tot += ssq[row * (IM_GROUPS * IM_WARPS) + w];
+                    inv[row] = 1.0f / sqrtf(tot / (float)K + a.eps);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < SL; ++i) {
+                const int row = i / PRS, sub = i % PRS;
+                const uint32_t c = threadIdx.x + sub * IM_CONSUMERS;
+                if ((uint32_t)sub * IM_CONSUMERS < n_chunks) {  // uniform over the block: every lane of a warp stages together
+                    const bool valid = act[row] && c < n_chunks;
+                    float v[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[e] = xr[i][e];
+                    if (a.norm_w && valid) {
+                        if (nw_pre) {
+                            const uint32_t pk[4] = {nw[sub].x, nw[sub].y, nw[sub].z, nw[sub].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                float2 f;
+                                if (a.norm_fmt == VB_FMT_F16) f = __half22float2(*reinterpret_cast<const __half2*>(&pk[e]));
+                                else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[e]));
+                                v[2 * e] = (v[2 * e] * inv[row]) * f.x;
+                                v[2 * e + 1] = (v[2 * e + 1] * inv[row]) * f.y;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e] = (v[e] * inv[row]) * im_norm_w(a.norm_w, a.norm_fmt, c * 8 + e);
+                        }
+                    }
+                    im_stage_chunk(xq + (size_t)row * xrow, sxp + (size_t)row * srow, v, c, valid);
+                }
+            }
+            im_consumer_sync();
+        };
+        const uint32_t prs = (n_chunks + IM_CONSUMERS - 1) / IM_CONSUMERS;
+        if (prs == 1) { stage_rows(std::integral_constant<int, 1>{}); staged = true; }
+        else if (prs == 2 && NB * 2 <= 8) { stage_rows(std::integral_constant<int, 2>{}); staged = true; }
+    }
 #pragma unroll 1
-    for (int row = 0; row < NB; ++row) {
+    for (int row = 0; row < NB && !staged; ++row) {
         const float* x = a.x + (size_t)row * K;
         unsigned char* xq_r = xq + (size_t)row * xrow;
         int2* sxp_r = sxp + (size_t)row * srow;
@@ -320,14 +400,14 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     // single row: column g of B is (group gj of a block, plane); multi-row: (row gj of x, plane) of one group at a time
-    const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)gj * xrow + plane * 32 + 8 * t;
-    const int2* sxp_lane = sxp + (size_t)t * srow;  // multi-row: lane (g,t) ends up with the sums of row t of x
+    const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)(gj % NB) * xrow + plane * 32 + 8 * t;
+    const int2* sxp_lane = sxp + (size_t)(t % NB) * srow;  // multi-row: lane (g,t) ends up with the sums of row t of x
     // multi-row epilogue: thread gt < 32 of a group owns mma rows e_row and e_row + 8 of row e_seq of x
     const uint32_t e_row = gt >> 2, e_seq = gt & 3;
     bool e_act = act[0];
 #pragma unroll
     for (int r = 1; r < NB; ++r) if ((uint32_t)r == e_seq) e_act = act[r];
-    e_act = e_act && gt < 32;
+    e_act = e_act && gt < 32 && e_seq < (uint32_t)NB;  // with two rows of x, columns 4..7 of the mma repeat 0..3
     float* e_dst = a.dst + (size_t)e_seq * a.dst_stride + a.dst_offset;
     for (uint32_t tile = vtile0; tile < n_tiles; tile += vstride, parity ^= 1) {
         // residual rows fetched early so that the epilogue does not wait on them
@@ -371,6 +451,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                                 int d[4] = {0, 0, 0, 0};
                                 imma_16832(d, af.x, af.y, af.z, af.w, bx.x, bx.y, d);
                                 // lane (g,t): sums of q * H and q * L of row t of x over group j, for weight rows g and g+8
+                                // (replacing the two I2F by integer/float adds of 1.5 * 2^23 measured no faster)
                                 acc0 = fmaf((float)(d[0] * 256 + d[1]), ip[j], acc0);
                                 acc1 = fmaf((float)(d[2] * 256 + d[3]), ip[j], acc1);
                             }
@@ -388,7 +469,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                                 const uint2 bx = *reinterpret_cast<const uint2*>(xb + j * 64);
                                 int d[4] = {0, 0, 0, 0};
                                 imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, bx.x, bx.y, d);
-                                const int r0 = d[0] * 256 + d[1] - 8 * sx[j];
+                                const int r0 = d[0] * 256 + d[1] - 8 * sx[j];  // |r| <= 32 * 8 * 16383 < 2^22
                                 const int r1 = d[2] * 256 + d[3] - 8 * sx[j];
                                 const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&scr[j]));
                                 acc0 = fmaf((float)r0 * ip[j], s2.x, acc0);
@@ -445,7 +526,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         }
         if constexpr (NB > 1) {
             // every lane holds its own (weight row, row of x): only the 8 warps remain to be added
-            float* rbuf = red + ((size_t)group * 2 + parity) * (IM_WARPS * 16 * NB);
+            float* rbuf = red + ((size_t)group * 2 + parity) * (IM_WARPS * 64);
             rbuf[warp * 64 + g * 4 + t] = acc0;
             rbuf[warp * 64 + 32 + g * 4 + t] = acc1;
             im_group_sync(group);
@@ -570,7 +651,8 @@ cudaError_t tile_q4_v3_swiglu(const LaunchCfg& lc, void* tiled, const void* cano
     return tile_v3_half(lc, tiled, canon, canon_scales, rows / 8, K, 8, 0, (uint32_t)which);
 }
 
-constexpr int IM_NB = 4;  // rows of x per weight pass of the multi-row flavour
+constexpr int IM_NB = 4;   // rows of x per weight pass of the multi-row flavour ...
+constexpr int IM_NB2 = 2;  // ... and for rows of x too long for four of them to fit beside a ring (K > ~15k)
 
 template <int W>
 static cudaError_t imma_opt_in() {
@@ -581,7 +663,10 @@ static cudaError_t imma_opt_in() {
     if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<2, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
     if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
 }
 cudaError_t gemv_imma_init() {
     cudaError_t e = imma_opt_in<IM_Q4>();
@@ -597,7 +682,7 @@ bool imma_multirow = true; // vb_set_option("gemv_multirow", 0) routes batch > 1
 // shared memory besides the ring: staged x (+ row padding), group sums, the reduction buffers, slack for alignment
 static size_t imma_fixed_smem(uint32_t K, int nb) {
     const size_t xrow = (size_t)K * 2 + (nb > 1 ? 64 : 0), srow = (size_t)(K / 32 + (nb > 1 ? 4 : 0)) * 8;
-    return (size_t)nb * (xrow + srow) + (size_t)IM_GROUPS * 2 * IM_WARPS * 16 * 4 * nb + 256;
+    return (size_t)nb * (xrow + srow) + (size_t)IM_GROUPS * 2 * IM_WARPS * (nb > 1 ? 64 : 16) * 4 + 256;
 }
 // ring depth that fits (0: none)
 static size_t imma_ring_depth(uint32_t K, int nb, size_t blk_bytes) {
@@ -645,7 +730,10 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     if (swiglu && (a.w2.rows != a.w.rows || a.w2.cols != a.w.cols)) return cudaSuccess;
     const uint32_t rows = swiglu ? 2 * a.w.rows : a.w.rows;
     if (rows % 16 != 0) return cudaSuccess;
-    if (imma_ring_depth(a.w.cols, multi ? IM_NB : 1, i8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES) == 0) return cudaSuccess;
+    const size_t blk_bytes = i8 ? IM_BLK_BYTES_I8 : IM_BLK_BYTES;
+    // rows of x per pass: four when they fit beside a ring of two slots, else two
+    const int nb = !multi ? 1 : (imma_ring_depth(a.w.cols, IM_NB, blk_bytes) >= 2 ? IM_NB : IM_NB2);
+    if (imma_ring_depth(a.w.cols, nb, blk_bytes) == 0) return cudaSuccess;
     ImmaArgs f;
     f.nb_rows = 1;
     f.dst_stride = a.dst_stride ? a.dst_stride : a.w.rows;
@@ -672,17 +760,22 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
         if (pairs) return imma_launch<IM_Q4X2, 1>(lc, f, (uint32_t)imma_pair_ring);
         return imma_launch<IM_Q4, 1>(lc, f, a.max_ring);
     }
-    // batch > 1: passes of up to IM_NB rows of x, each one trip over the weights
-    const bool pairs_fit = pairs && imma_ring_depth(a.w.cols, IM_NB, 2 * IM_BLK_BYTES) >= 3;
-    for (uint32_t b0 = 0; b0 < a.batch; b0 += IM_NB) {
+    // batch > 1: passes of up to nb rows of x, each one trip over the weights
+    const bool pairs_fit = pairs && imma_ring_depth(a.w.cols, nb, 2 * IM_BLK_BYTES) >= 3;
+    for (uint32_t b0 = 0; b0 < a.batch; b0 += (uint32_t)nb) {
         ImmaArgs p = f;
-        p.nb_rows = a.batch - b0 < (uint32_t)IM_NB ? a.batch - b0 : (uint32_t)IM_NB;
+        p.nb_rows = a.batch - b0 < (uint32_t)nb ? a.batch - b0 : (uint32_t)nb;
         p.x = a.x + (size_t)b0 * a.w.cols;
         p.dst = a.dst + (size_t)b0 * f.dst_stride;
         p.state = a.state ? a.state + b0 : nullptr;
-        const cudaError_t e = i8 ? imma_launch<IM_I8, IM_NB>(lc, p, a.max_ring)
-                            : pairs_fit ? imma_launch<IM_Q4X2, IM_NB>(lc, p, (uint32_t)imma_pair_ring)
-                                        : imma_launch<IM_Q4, IM_NB>(lc, p, a.max_ring);
+        cudaError_t e;
+        if (nb == IM_NB) {
+            e = i8 ? imma_launch<IM_I8, IM_NB>(lc, p, a.max_ring)
+              : pairs_fit ? imma_launch<IM_Q4X2, IM_NB>(lc, p, (uint32_t)imma_pair_ring) : imma_launch<IM_Q4, IM_NB>(lc, p, a.max_ring);
+        } else {
+            e = i8 ? imma_launch<IM_I8, IM_NB2>(lc, p, a.max_ring)
+              : pairs_fit ? imma_launch<IM_Q4X2, IM_NB2>(lc, p, (uint32_t)imma_pair_ring) : imma_launch<IM_Q4, IM_NB2>(lc, p, a.max_ring);
+        }
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
