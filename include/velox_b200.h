@@ -170,6 +170,8 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "attn_mma"       1: tensor-core attention for the fp16 cache; 0: the scalar fp32 path
  *   "fuse_append"    1: bias + RoPE + KV append inside the attention kernel
  *   "prefill_chunk"  prompt tokens that go through the layers together in vb_prefill (16; 1 = token by token)
+ *   "prefill_gemm"   1: prompts longer than "prefill_gemm_min" (48) tokens go through the layers in chunks of up to
+ *                    "prefill_rows" (512) tokens whose products run on the tcgen05 tensor cores; 0: batched kernels
  *   "pdl"            1: programmatic dependent launch between the kernels of a step
  *   "trace"          1: device time stamps per kernel (vb_trace_read)
  *   "tp_p2p"         1: NVLink push exchange when peer regions are open, 0: NCCL
@@ -205,6 +207,15 @@ int32_t vb_op_rmsnorm(float* dst, const float* x, const void* w, int32_t w_fmt, 
 /* Matmul (src/runtime.rs:702-740): dst[b][o] = sum_k x[b][k] * W[o][k], W in canonical layout. */
 int32_t vb_op_matmul(float* dst, const float* x, const void* w, const void* scales, int32_t fmt,
                      uint32_t in_dim, uint32_t out_dim, uint32_t batch, void* stream);
+/* Multi-row Matmul on the tcgen05 tensor cores (the reference's multi-token kernels for prefill chunks and
+ * speculative-verify rows, src/runners/velox_cuda_runner_k2.cu:480-1085): dst[r][o] = sum_k x[r][k] * W[o][k]
+ * for r < n_rows, same W layouts as vb_op_matmul.  x and W are rounded to fp16 for the product (int8 weights
+ * exactly, with their row scale applied in fp32), accumulation is fp32.  `workspace`: device memory, 1024-byte
+ * aligned, of at least vb_op_matmul_rows_workspace_bytes(in_dim, out_dim, n_rows) bytes; the call allocates nothing. */
+uint64_t vb_op_matmul_rows_workspace_bytes(uint32_t in_dim, uint32_t out_dim, uint32_t n_rows);
+int32_t vb_op_matmul_rows(float* dst, const float* x, const void* w, const void* scales, int32_t fmt,
+                          uint32_t in_dim, uint32_t out_dim, uint32_t n_rows, void* workspace,
+                          uint64_t workspace_bytes, void* stream);
 /* RoPE, rotate-half convention (src/runtime.rs:745-768), in place on t[n_heads][head_dim]. */
 int32_t vb_op_rope(float* t, uint32_t n_heads, uint32_t head_dim, uint32_t pos, float theta, void* stream);
 /* Decode attention over a contiguous fp32 cache laid out as the reference's

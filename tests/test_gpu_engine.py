@@ -204,19 +204,39 @@ def test_lockstep_prefill_matches_the_checker():
 
 @pytest.mark.parametrize("spec_i", [0, 2, 9])
 def test_chunked_prefill_agrees_with_token_by_token(spec_i):
-    """Prompt tokens sent through the layers 16 (or 5) at a time give the tokens of the one-by-one prefill, and
-    logits within the path's tolerance (the batched kernels sum in another order)."""
+    """Prompt tokens sent through the layers 16 (or 5) at a time by the batched kernels, or in tensor-core chunks
+    (one chunk of 70 rows; ragged chunks of 32, 32, 6), give the tokens of the one-by-one prefill, and logits within
+    the path's tolerance (other summation order, fp16 operands in the tensor-core products)."""
     spec = SMALL_SPECS[spec_i]
     prompt = H.prompt_tokens(spec, 3, 71)
     outs = []
-    for chunk in (1, 16, 5):
+    for gemm, chunk in ((0, 1), (0, 16), (0, 5), (1, 512), (1, 32)):
         eng = H.build_engine(spec, 3, 96)
-        eng.set_option("prefill_chunk", chunk)
+        eng.set_option("prefill_gemm", gemm)
+        eng.set_option("prefill_rows" if gemm else "prefill_chunk", chunk)
         outs.append((eng.generate_greedy(prompt, 10), eng.logits()))
         eng.close()
     for toks, lg in outs[1:]:
         assert np.array_equal(toks, outs[0][0])
         assert float(np.max(np.abs(lg - outs[0][1]))) <= LOGIT_TOL
+
+
+@pytest.mark.parametrize("spec_i", [0, 1, 2, 4, 5, 6, 7])
+def test_tensor_core_prefill_matches_checker(spec_i):
+    """A 150-token prompt prefilled in tensor-core chunks (128 + 21 rows, every weight format, QKV bias), then 32
+    greedy tokens: logits within 2e-2 of the CPU checker, tokens identical."""
+    spec = SMALL_SPECS[spec_i]
+    n_prompt, n_new = 150, 32
+    ora, _ = H.build_oracle(spec, 21, n_prompt + n_new + 1)
+    eng = H.build_engine(spec, 21, n_prompt + n_new + 1)
+    eng.set_option("prefill_rows", 128)
+    prompt = H.prompt_tokens(spec, 21, n_prompt)
+    want = ora.generate_greedy(prompt, n_new)
+    got = eng.generate_greedy(prompt, n_new)
+    err = float(np.max(np.abs(eng.logits() - ora.logits)))
+    assert err <= LOGIT_TOL, "logits max-abs %g" % err
+    assert np.array_equal(got, want)
+    eng.close()
 
 
 def test_engine_argument_errors():

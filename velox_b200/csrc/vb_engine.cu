@@ -7,6 +7,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <new>
 #include <vector>
 
@@ -84,6 +85,12 @@ struct vb_ctx {
     int32_t* pfc_table = nullptr;         // [chunk][max_blocks], every row = the sequence's block-table row
     float *pfc_hidden = nullptr, *pfc_qkv = nullptr, *pfc_q = nullptr, *pfc_attn = nullptr, *pfc_act = nullptr;
     uint32_t pfc_rows = 0;                // rows the buffers above hold
+    // prompts of at least `prefill_gemm_min` tokens: chunks of up to `prefill_rows` tokens whose four products per layer
+    // run on the tcgen05 tensor cores (vb_gemm_tc.cu); the workspace holds their fp16 operands
+    bool prefill_gemm = true;
+    uint32_t prefill_rows = 512, prefill_gemm_min = 48;
+    void* tc_ws = nullptr;
+    uint64_t tc_ws_bytes = 0;
 
     // activations
     float *hidden = nullptr, *qkv = nullptr, *q = nullptr, *attn_out = nullptr, *act = nullptr, *logits = nullptr;
@@ -303,13 +310,31 @@ __global__ void k_set_state(SeqState* state, uint32_t slot, const uint32_t* toke
 
 // rows j < n of a prefill chunk: prompt token first + j at position first + j; rows beyond n inactive
 __global__ void k_set_chunk_state(SeqState* state, const uint32_t* tokens, uint32_t first, uint32_t n, uint32_t rows) {
-    const uint32_t j = threadIdx.x;
+    const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j < rows) {
         state[j].token = j < n ? tokens[first + j] : 0u;
         state[j].pos = first + j;
         state[j].active = j < n ? 1u : 0u;
         state[j].pad = 0;
     }
+}
+
+// every row of the chunk's block table = the prefilled sequence's row
+__global__ void k_fill_chunk_table(int32_t* dst, const int32_t* src_row, uint32_t max_blocks) {
+    for (uint32_t i = threadIdx.x; i < max_blocks; i += blockDim.x) dst[(size_t)blockIdx.x * max_blocks + i] = src_row[i];
+}
+
+// The four products of a layer can run as tensor-core GEMMs when their canonical copies are resident (not with
+// VB_FLAG_LEAN_WEIGHTS) in a format the conversion kernel reads.
+bool tc_products_ok(vb_ctx* c) {
+    const int roles[] = {VB_ROLE_WQ, VB_ROLE_WO, VB_ROLE_WGATE, VB_ROLE_WUP, VB_ROLE_WDOWN};
+    for (int role : roles) {
+        GemvArgs a;
+        a.w = c->tensor(role, 0).m;
+        if (role == VB_ROLE_WQ) a.w.rows = c->qkv_rows;
+        if (!gemm_tc_supported(a)) return false;
+    }
+    return true;
 }
 
 bool all_loaded(vb_ctx* c, const char** missing) {
@@ -332,6 +357,8 @@ struct StepIO {
     const int32_t* block_table;
     uint32_t B;
     bool fused_append;  // false: K/V of all rows are appended by a kernel of their own before attention
+    void* tc_ws = nullptr;  // != null: the layer products run as tensor-core GEMMs with this workspace
+    uint64_t tc_ws_bytes = 0;
 };
 StepIO decode_io(vb_ctx* c) {
     return StepIO{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
@@ -365,6 +392,10 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         if (p2p) return tp_reduce(lcfg(c, true), c->links, io.hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed);
         return nccl_allreduce_sum_f32(c->nccl, io.hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
+    auto product = [&](const GemvArgs& ga) -> cudaError_t {
+        if (io.tc_ws) return gemm_tc(lcfg(c, true), ga, io.tc_ws, io.tc_ws_bytes);
+        return gemv(lcfg(c, true), ga, c->gemv_path);
+    };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
         const int L = (int)l;
         // RMSNorm + fused QKV projection
@@ -374,7 +405,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         g.norm_w = c->tensor(VB_ROLE_ATTN_NORM, L).m.data; g.norm_fmt = c->tensor(VB_ROLE_ATTN_NORM, L).m.fmt; g.eps = d.rms_eps;
         g.w = c->tensor(VB_ROLE_WQ, L).m; g.w.rows = c->qkv_rows;
         g.trace = next_trace(); g.max_ring = c->ring_role[0] ? c->ring_role[0] : c->gemv_ring;
-        VB_TRY(gemv(lcfg(c, true), g, c->gemv_path));
+        VB_TRY(product(g));
         // bias + RoPE + KV append
         __half* kv_layer = c->kv_pool + (size_t)l * c->kv_layer_elems;
         const void *bq = nullptr, *bk = nullptr, *bv = nullptr; int bf = VB_FMT_F32;
@@ -402,7 +433,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         o.trace = next_trace(); o.max_ring = c->ring_role[1] ? c->ring_role[1] : c->gemv_ring;
         pushed = false;
         if (p2p && c->tp_fused_push) { o.push.links = &c->links; o.push.site = 2 * l; o.push.n_sites = n_sites; o.pushed = &pushed; }
-        VB_TRY(gemv(lcfg(c, true), o, c->gemv_path));
+        VB_TRY(product(o));
         VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
         GemvArgs gu;
@@ -410,7 +441,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         gu.norm_w = c->tensor(VB_ROLE_MLP_NORM, L).m.data; gu.norm_fmt = c->tensor(VB_ROLE_MLP_NORM, L).m.fmt; gu.eps = d.rms_eps;
         gu.w = c->tensor(VB_ROLE_WGATE, L).m; gu.w2 = c->tensor(VB_ROLE_WUP, L).m;
         gu.trace = next_trace(); gu.max_ring = c->ring_role[2] ? c->ring_role[2] : c->gemv_ring;
-        VB_TRY(gemv(lcfg(c, true), gu, c->gemv_path));
+        VB_TRY(product(gu));
         // down projection + residual
         GemvArgs dn;
         dn.state = state; dn.batch = B; dn.x = io.act; dn.dst = row_dst; dn.epilogue = row_epi;
@@ -418,7 +449,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         dn.trace = next_trace(); dn.max_ring = c->ring_role[3] ? c->ring_role[3] : c->gemv_ring;
         pushed = false;
         if (p2p && c->tp_fused_push) { dn.push.links = &c->links; dn.push.site = 2 * l + 1; dn.push.n_sites = n_sites; dn.pushed = &pushed; }
-        VB_TRY(gemv(lcfg(c, true), dn, c->gemv_path));
+        VB_TRY(product(dn));
         VB_TRY(exchange(2 * l + 1));
     }
     if (with_head) {
@@ -589,7 +620,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
-                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
+                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -852,28 +883,51 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
     // j attends positions 0..first+j, so the result is the causal one.  (The reference's batched prefill driver:
     // velox_cuda_runner_k2.cu:1614-1704.)  Sharded contexts and the last token take the per-token path below.
     uint32_t done = 0;
-    const uint32_t P = c->prefill_chunk;
-    if (P >= 2 && P <= 32 && c->d.tp_size <= 1 && n_tokens > P) {
-        if (c->pfc_rows != P) {
+    const bool use_tc = c->prefill_gemm && c->d.tp_size <= 1 && n_tokens > c->prefill_gemm_min && c->prefill_rows >= 1 && tc_products_ok(c);
+    const uint32_t P = use_tc ? std::min(c->prefill_rows, n_tokens - 1) : c->prefill_chunk;
+    if (use_tc || (P >= 2 && P <= 32 && c->d.tp_size <= 1 && n_tokens > P)) {
+        const uint32_t cap = use_tc ? c->prefill_rows : P;  // rows the chunk buffers hold
+        if (c->pfc_rows != cap) {
             void* old[] = {c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
             for (void* p : old) if (p) cudaFree(p);
             c->pfc_state = nullptr; c->pfc_table = nullptr; c->pfc_hidden = c->pfc_qkv = c->pfc_q = c->pfc_attn = c->pfc_act = nullptr;
             c->pfc_rows = 0;
-            if ((rc = dev_alloc(&c->pfc_state, P)) != VB_OK || (rc = dev_alloc(&c->pfc_table, (uint64_t)P * c->max_blocks)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_hidden, (uint64_t)P * c->d.d_model)) != VB_OK || (rc = dev_alloc(&c->pfc_qkv, (uint64_t)P * c->qkv_rows)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_q, (uint64_t)P * c->qdim)) != VB_OK || (rc = dev_alloc(&c->pfc_attn, (uint64_t)P * c->qdim)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_act, (uint64_t)P * c->ffn)) != VB_OK)
+            if ((rc = dev_alloc(&c->pfc_state, cap)) != VB_OK || (rc = dev_alloc(&c->pfc_table, (uint64_t)cap * c->max_blocks)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_hidden, (uint64_t)cap * c->d.d_model)) != VB_OK || (rc = dev_alloc(&c->pfc_qkv, (uint64_t)cap * c->qkv_rows)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_q, (uint64_t)cap * c->qdim)) != VB_OK || (rc = dev_alloc(&c->pfc_attn, (uint64_t)cap * c->qdim)) != VB_OK ||
+                (rc = dev_alloc(&c->pfc_act, (uint64_t)cap * c->ffn)) != VB_OK)
                 return rc;
-            c->pfc_rows = P;
+            c->pfc_rows = cap;
         }
-        for (uint32_t j = 0; j < P; ++j)
-            VB_CUDA(cudaMemcpyAsync(c->pfc_table + (size_t)j * c->max_blocks, c->block_table_dev + (size_t)slot * c->max_blocks,
-                                    (size_t)c->max_blocks * 4, cudaMemcpyDeviceToDevice, c->stream));
-        const StepIO io{c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, nullptr, c->pfc_table, P, false};
-        while (done + P < n_tokens) {  // leaves at least one token for the per-token path (it produces the logits)
-            VB_CUDA(launch(lcfg(c, false), k_set_chunk_state, dim3(1), dim3(32), 0, c->pfc_state, (const uint32_t*)c->pf_tokens, done, P, P));
+        if (use_tc) {
+            const uint32_t dm = c->d.d_model;
+            uint64_t need = gemm_tc_workspace_bytes(c->qkv_rows, dm, cap, false);
+            need = std::max(need, gemm_tc_workspace_bytes(dm, c->qdim, cap, false));
+            need = std::max(need, gemm_tc_workspace_bytes(c->ffn, dm, cap, true));
+            need = std::max(need, gemm_tc_workspace_bytes(dm, c->ffn, cap, false));
+            if (c->tc_ws_bytes < need) {
+                if (c->tc_ws) cudaFree(c->tc_ws);
+                c->tc_ws = nullptr; c->tc_ws_bytes = 0;
+                if (cudaMalloc(&c->tc_ws, need + 1024) != cudaSuccess) {  // + 1024: the swizzled operands start on a 1024-byte boundary
+                    cudaGetLastError();
+                    set_error("vb_prefill: cannot allocate %llu bytes for the tensor-core workspace", (unsigned long long)need);
+                    return VB_ERR_OOM;
+                }
+                c->tc_ws_bytes = need;
+            }
+        }
+        VB_CUDA(launch(lcfg(c, false), k_fill_chunk_table, dim3(P), dim3(128), 0, c->pfc_table,
+                       (const int32_t*)(c->block_table_dev + (size_t)slot * c->max_blocks), c->max_blocks));
+        StepIO io{c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, nullptr, c->pfc_table, P, false};
+        if (use_tc) { io.tc_ws = (void*)(((uintptr_t)c->tc_ws + 1023) & ~(uintptr_t)1023); io.tc_ws_bytes = c->tc_ws_bytes; }
+        // the last token always takes the per-token path below (it produces the logits); the tensor-core chunks may be
+        // ragged (every row of a chunk is live), the batched-kernel chunks are whole
+        while (use_tc ? done + 1 < n_tokens : done + P < n_tokens) {
+            const uint32_t n = use_tc ? std::min(P, n_tokens - 1 - done) : P;
+            io.B = n;
+            VB_CUDA(launch(lcfg(c, false), k_set_chunk_state, dim3((n + 127) / 128), dim3(128), 0, c->pfc_state, (const uint32_t*)c->pf_tokens, done, n, n));
             VB_CUDA(enqueue_step(c, c->pfc_state, false, io));
-            done += P;
+            done += n;
         }
     }
     // the reference prefills one token per forward pass (velox_cuda_runner.cu:504-506)
@@ -1053,6 +1107,13 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "pdl")) { c->use_pdl = value != 0; return VB_OK; }
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_chunk")) { c->prefill_chunk = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "prefill_gemm")) { c->prefill_gemm = value != 0; return VB_OK; }
+    if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "prefill_rows")) {
+        VB_REQUIRE(value >= 1 && value <= 4096, "vb_set_option: prefill_rows must be in [1, 4096]");
+        c->prefill_rows = (uint32_t)value;
+        return VB_OK;
+    }
     if (!strcmp(name, "trace")) {
         if (value && !c->trace) {
             VB_CUDA(cudaMalloc((void**)&c->trace, 1024 * 4 * sizeof(unsigned long long)));

@@ -108,6 +108,13 @@ extern bool imma_multirow;
 extern int imma_pair_ring;
 extern bool imma_spread;
 
+// vb_gemm_tc.cu: multi-row products on the tcgen05 tensor cores (prefill chunks); the arguments are those of gemv(),
+// `batch` = rows of x; the workspace holds the fp16 operands
+cudaError_t gemm_tc_init();
+bool gemm_tc_supported(const GemvArgs& a);
+uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
+cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes);
+
 // vb_attn.cu
 struct AttnArgs {
     float* out = nullptr;          // [batch][Hq*D]

@@ -77,6 +77,8 @@ SIGNATURES = {
     "vb_op_embed": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp]),
     "vb_op_rmsnorm": (_i32, [_vp, _vp, _vp, _i32, _u32, _u32, _f32, _vp]),
     "vb_op_matmul": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp]),
+    "vb_op_matmul_rows_workspace_bytes": (_u64, [_u32, _u32, _u32]),
+    "vb_op_matmul_rows": (_i32, [_vp, _vp, _vp, _vp, _i32, _u32, _u32, _u32, _vp, _u64, _vp]),
     "vb_op_rope": (_i32, [_vp, _u32, _u32, _u32, _f32, _vp]),
     "vb_op_gqa_attention": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
     "vb_op_sample_argmax": (_i32, [_vp, _vp, _u32, _vp, _u64, _vp]),
