@@ -172,6 +172,7 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "prefill_chunk"  prompt tokens that go through the layers together in vb_prefill (16; 1 = token by token)
  *   "prefill_gemm"   1: prompts longer than "prefill_gemm_min" (48) tokens go through the layers in chunks of up to
  *                    "prefill_rows" (512) tokens whose products run on the tcgen05 tensor cores; 0: batched kernels
+ *   "prefill_flash"  1: those chunks use the causal tile attention kernel (head_dim 64 or 128); 0: one row per token
  *   "pdl"            1: programmatic dependent launch between the kernels of a step
  *   "trace"          1: device time stamps per kernel (vb_trace_read)
  *   "tp_p2p"         1: NVLink push exchange when peer regions are open, 0: NCCL

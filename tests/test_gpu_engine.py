@@ -210,10 +210,11 @@ def test_chunked_prefill_agrees_with_token_by_token(spec_i):
     spec = SMALL_SPECS[spec_i]
     prompt = H.prompt_tokens(spec, 3, 71)
     outs = []
-    for gemm, chunk in ((0, 1), (0, 16), (0, 5), (1, 512), (1, 32)):
+    for opts in ({"prefill_gemm": 0, "prefill_chunk": 1}, {"prefill_gemm": 0, "prefill_chunk": 16}, {"prefill_gemm": 0, "prefill_chunk": 5},
+                 {"prefill_rows": 512}, {"prefill_rows": 32}, {"prefill_rows": 32, "prefill_flash": 0}):
         eng = H.build_engine(spec, 3, 96)
-        eng.set_option("prefill_gemm", gemm)
-        eng.set_option("prefill_rows" if gemm else "prefill_chunk", chunk)
+        for name, value in opts.items():
+            eng.set_option(name, value)
         outs.append((eng.generate_greedy(prompt, 10), eng.logits()))
         eng.close()
     for toks, lg in outs[1:]:
@@ -221,10 +222,11 @@ def test_chunked_prefill_agrees_with_token_by_token(spec_i):
         assert float(np.max(np.abs(lg - outs[0][1]))) <= LOGIT_TOL
 
 
-@pytest.mark.parametrize("spec_i", [0, 1, 2, 4, 5, 6, 7])
+@pytest.mark.parametrize("spec_i", [0, 1, 2, 3, 4, 5, 6, 7])
 def test_tensor_core_prefill_matches_checker(spec_i):
-    """A 150-token prompt prefilled in tensor-core chunks (128 + 21 rows, every weight format, QKV bias), then 32
-    greedy tokens: logits within 2e-2 of the CPU checker, tokens identical."""
+    """A 150-token prompt prefilled in tensor-core chunks (128 + 21 rows; every weight format, QKV bias, head_dim 32 /
+    64 / 128, i.e. with and without the causal tile attention kernel), then 32 greedy tokens: logits within 2e-2 of
+    the CPU checker, tokens identical."""
     spec = SMALL_SPECS[spec_i]
     n_prompt, n_new = 150, 32
     ora, _ = H.build_oracle(spec, 21, n_prompt + n_new + 1)

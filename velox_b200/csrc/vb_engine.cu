@@ -88,6 +88,7 @@ struct vb_ctx {
     // prompts of at least `prefill_gemm_min` tokens: chunks of up to `prefill_rows` tokens whose four products per layer
     // run on the tcgen05 tensor cores (vb_gemm_tc.cu); the workspace holds their fp16 operands
     bool prefill_gemm = true;
+    bool prefill_flash = true;  // causal tile attention for those chunks (vb_attn_prefill.cu) instead of one launch row per token
     uint32_t prefill_rows = 512, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
     uint64_t tc_ws_bytes = 0;
@@ -359,6 +360,7 @@ struct StepIO {
     bool fused_append;  // false: K/V of all rows are appended by a kernel of their own before attention
     void* tc_ws = nullptr;  // != null: the layer products run as tensor-core GEMMs with this workspace
     uint64_t tc_ws_bytes = 0;
+    uint32_t first = 0;     // tensor-core chunks: position of row 0 (row j is position first + j of one sequence)
 };
 StepIO decode_io(vb_ctx* c) {
     return StepIO{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
@@ -425,7 +427,10 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         a.trace = next_trace(); a.err = c->err_word;
-        VB_TRY(attention(lcfg(c, true), a));
+        if (io.tc_ws && c->prefill_flash && attention_prefill_supported(c->hq, c->hkv, d.head_dim))
+            VB_TRY(attention_prefill(lcfg(c, true), io.attn_out, io.q, kv_layer, io.block_table, io.first, B, c->hq, c->hkv, d.head_dim, d.kv_block_tokens));
+        else
+            VB_TRY(attention(lcfg(c, true), a));
         // O-projection + residual
         GemvArgs o;
         o.state = state; o.batch = B; o.x = io.attn_out; o.dst = row_dst; o.epilogue = row_epi;
@@ -924,7 +929,7 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
         // ragged (every row of a chunk is live), the batched-kernel chunks are whole
         while (use_tc ? done + 1 < n_tokens : done + P < n_tokens) {
             const uint32_t n = use_tc ? std::min(P, n_tokens - 1 - done) : P;
-            io.B = n;
+            io.B = n; io.first = done;
             VB_CUDA(launch(lcfg(c, false), k_set_chunk_state, dim3((n + 127) / 128), dim3(128), 0, c->pfc_state, (const uint32_t*)c->pf_tokens, done, n, n));
             VB_CUDA(enqueue_step(c, c->pfc_state, false, io));
             done += n;
@@ -1108,6 +1113,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_chunk")) { c->prefill_chunk = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_gemm")) { c->prefill_gemm = value != 0; return VB_OK; }
+    if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_rows")) {
         VB_REQUIRE(value >= 1 && value <= 4096, "vb_set_option: prefill_rows must be in [1, 4096]");

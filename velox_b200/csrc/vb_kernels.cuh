@@ -146,6 +146,11 @@ uint32_t attn_tokens_per_split(uint32_t max_seq);
 cudaError_t attention(const LaunchCfg& lc, const AttnArgs& a);
 cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, size_t kv_batch_stride);
 
+// vb_attn_prefill.cu: causal attention of a prefill chunk (rows = consecutive positions of one sequence)
+bool attention_prefill_supported(uint32_t Hq, uint32_t Hkv, uint32_t D);
+cudaError_t attention_prefill(const LaunchCfg& lc, float* out, const float* q, const __half* kv_layer, const int32_t* table_row,
+                              uint32_t first, uint32_t n, uint32_t Hq, uint32_t Hkv, uint32_t D, uint32_t block_tokens);
+
 // vb_mla.cu
 cudaError_t mla_absorbed(const LaunchCfg& lc, float* dst, const float* x, const float* w_norm, const float* w_dkv,
                          const float* w_absq, const float* w_abso, float* pool, uint32_t step, uint32_t hidden,
