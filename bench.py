@@ -253,6 +253,27 @@ def main():
         eng.prefill_lockstep([H.prompt_tokens(spec, SEED, prompt_lens[slot], stream=PROMPT_STREAM + slot) for slot in range(batch)])
     eng.sync()
     ttft_s = time.perf_counter() - t0
+    prefill = None
+    if batch == 1 and not tp:
+        # the same prompt once more with every buffer in place: prefill throughput.  All but the last prompt token go
+        # through the layers as rows of tensor-core GEMMs (vb_gemm_tc.cu); their flops against the measured dense peak.
+        t1 = time.perf_counter()
+        eng.prefill(prompt, 0)
+        eng.sync()
+        pf_s = time.perf_counter() - t1
+        qdim, kvdim = spec.n_q_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+        layer_params = spec.d_model * (qdim + 2 * kvdim) + qdim * spec.d_model + 3 * spec.ffn_dim * spec.d_model
+        flops = 2.0 * layer_params * spec.n_layers * (args.prompt_len - 1)
+        tpeak = None
+        try:
+            tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        except Exception:
+            pass
+        prefill = {"tokens": args.prompt_len, "ms": 1e3 * pf_s, "tok_per_s": args.prompt_len / pf_s,
+                   "roofline": {"bound": "tensor", "achieved": flops / pf_s / 1e12, "peak": tpeak if tpeak else 1590.0, "unit": "TFLOP/s",
+                                "frac": flops / pf_s / 1e12 / (tpeak if tpeak else 1590.0), "peak_kind": "measured" if tpeak else "fallback",
+                                "what": "projection flops of prompt_len-1 rows / whole warm prefill time (host clock, includes attention, "
+                                        "operand conversion and the last token's decode-path step)"}}
     eng.build_graph()
 
     def barrier():
@@ -333,6 +354,8 @@ def main():
         "gpu_launches": int(launches), "clocks": clocks,
         "ttft_ms": 1e3 * ttft_s, "load_s": load_s,
     }
+    if prefill is not None:
+        line["prefill"] = prefill
     if rank == 0 and not args.no_cpu_baseline and world == 1:
         full, per_step, cores = cpu_sample(spec, 2, 2, 1)
         line["cpu_baseline"] = {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",

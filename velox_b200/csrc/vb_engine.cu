@@ -1113,6 +1113,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_chunk")) { c->prefill_chunk = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_gemm")) { c->prefill_gemm = value != 0; return VB_OK; }
+    if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_rows")) {

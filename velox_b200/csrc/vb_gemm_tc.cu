@@ -25,16 +25,16 @@ namespace vb {
 namespace {
 
 constexpr int BM = 128;      // weight rows per tile (UMMA M)
-constexpr int BN = 128;      // rows of x per tile (UMMA N)
+                             // rows of x per tile (UMMA N): 128 or 256, a template parameter of the kernel
 constexpr int BK = 64;       // K extent of a stage: 64 fp16 = one 128-byte swizzle row
-constexpr int TILE_BYTES = BM * BK * 2;  // 16 KB, also BN * BK * 2
-constexpr int STAGES_SINGLE = 6;         // 6 x 32 KB
-constexpr int STAGES_DUAL = 4;           // 4 x 48 KB
+constexpr int TILE_BYTES = BM * BK * 2;  // 16 KB: one box of 128 rows
+// ring depth so that the stages fill 192 KB: (weight tiles + x tiles) x 16 KB per stage
+__host__ __device__ constexpr int stages_for(bool dual, int bn) { return 192 / (16 * ((dual ? 2 : 1) + bn / 128)); }
 constexpr int SMEM_BYTES = 192 * 1024 + 1024 /* alignment slack */ + 256 /* barriers */;
 
 // instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate (bits 4-5 = 1), A and B fp16 (formats 0),
 // both K-major (bits 15, 16 = 0), N >> 3 at bit 17, M >> 4 at bit 24
-constexpr uint32_t IDESC = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+__host__ __device__ constexpr uint32_t idesc_for(int bn) { return (1u << 4) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); }
 
 // shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: start address >> 4 in bits 0-13,
 // leading byte offset (unused with a swizzle; 1) in bits 16-29, stride between groups of 8 rows = 1024 bytes
@@ -47,9 +47,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(IDESC), "r"(accumulate) : "memory");
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -90,12 +90,14 @@ struct GemmParams {
     uint32_t* err;
 };
 
-template <bool DUAL>
+template <bool DUAL, int BN>
 __global__ void __launch_bounds__(128, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
           const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
-    constexpr int STAGES = DUAL ? STAGES_DUAL : STAGES_SINGLE;
-    constexpr int STAGE_BYTES = (DUAL ? 3 : 2) * TILE_BYTES;
+    constexpr int STAGES = stages_for(DUAL, BN);
+    constexpr int W_TILES = DUAL ? 2 : 1, X_TILES = BN / 128;
+    constexpr int STAGE_BYTES = (W_TILES + X_TILES) * TILE_BYTES;
+    constexpr uint32_t IDESC = idesc_for(BN);
     constexpr uint32_t TMEM_COLS = DUAL ? 2 * BN : BN;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
@@ -138,7 +140,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             mbar_expect_tx(full, STAGE_BYTES);
             tma_load_2d(st, &map_w, kb * BK, row0, full);
             if (DUAL) tma_load_2d(st + TILE_BYTES, &map_w2, kb * BK, row0, full);
-            tma_load_2d(st + (DUAL ? 2 : 1) * TILE_BYTES, &map_x, kb * BK, tok0, full);
+            tma_load_2d(st + W_TILES * TILE_BYTES, &map_x, kb * BK, tok0, full);
+            if (X_TILES == 2) tma_load_2d(st + (W_TILES + 1) * TILE_BYTES, &map_x, kb * BK, tok0 + 128, full);  // rows 128..255: the next 16 groups of 8
         }
     } else if (warp == 1 && lane == 0) {
         // ---- tensor-core issue ----
@@ -148,12 +151,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (!wait_or_abort(bars + s * 8, ph, abort_flag)) break;
             tc_fence_after();
             const uint32_t st = base + s * STAGE_BYTES;
-            const uint64_t da = smem_desc(st), da2 = smem_desc(st + TILE_BYTES), db = smem_desc(st + (DUAL ? 2 : 1) * TILE_BYTES);
+            const uint64_t da = smem_desc(st), da2 = smem_desc(st + TILE_BYTES), db = smem_desc(st + W_TILES * TILE_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {  // 16 fp16 = 32 bytes further along the swizzled row: +2 in the address field
                 const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
-                mma_f16(tmem, da + 2u * k, db + 2u * k, acc);
-                if (DUAL) mma_f16(tmem + BN, da2 + 2u * k, db + 2u * k, acc);
+                mma_f16(tmem, da + 2u * k, db + 2u * k, IDESC, acc);
+                if (DUAL) mma_f16(tmem + BN, da2 + 2u * k, db + 2u * k, IDESC, acc);
             }
             mma_commit(bars + (STAGES + s) * 8);  // the stage is free again once these products have read it
         }
@@ -174,23 +177,34 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             if ((uint32_t)(tok0 + c0) >= p.n_rows) break;  // uniform over the block
+            // which of the 32 rows of x are written: one flag per lane, gathered once (no load between the stores below)
+            const uint32_t tl = (uint32_t)(tok0 + c0) + lane;
+            const bool live = tl < p.n_rows && (!p.state || p.state[tl].active);
+            const uint32_t live_mask = __ballot_sync(0xFFFFFFFFu, live);
             uint32_t v[32], u[32];
             tmem_ld32(lane_addr + c0, v);
             if (DUAL) tmem_ld32(lane_addr + BN + c0, u);
+            if (!o_ok) continue;
+            float* d0 = p.dst + (size_t)(tok0 + c0) * p.dst_stride + o;
+            if (!DUAL && p.epilogue == EPI_RESIDUAL) {
+                // all 32 residual values first (independent loads), then the sums: one memory round trip, not 32
+                float res[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const uint32_t t = (uint32_t)(tok0 + c0 + j);
-                if (t >= p.n_rows || !o_ok) continue;
-                if (p.state && !p.state[t].active) continue;
-                float a = __uint_as_float(v[j]) * sc;
-                float* d = p.dst + (size_t)t * p.dst_stride + o;
-                if (DUAL) {
-                    const float up = __uint_as_float(u[j]) * sc2;
-                    *d = (a / (1.0f + expf(-a))) * up;
-                } else if (p.epilogue == EPI_RESIDUAL) {
-                    *d += a;
-                } else {
-                    *d = a;
+                for (int j = 0; j < 32; ++j) res[j] = ((live_mask >> j) & 1u) ? __ldcg(d0 + (size_t)j * p.dst_stride) : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if ((live_mask >> j) & 1u) d0[(size_t)j * p.dst_stride] = res[j] + __uint_as_float(v[j]) * sc;
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (!((live_mask >> j) & 1u)) continue;
+                    const float a = __uint_as_float(v[j]) * sc;
+                    if (DUAL) {
+                        const float up = __uint_as_float(u[j]) * sc2;
+                        d0[(size_t)j * p.dst_stride] = (a / (1.0f + expf(-a))) * up;
+                    } else {
+                        d0[(size_t)j * p.dst_stride] = a;
+                    }
                 }
             }
         }
@@ -324,11 +338,17 @@ bool g_tc_init = false;
 
 }  // namespace
 
+bool gemm_tc_wide = false;  // vb_set_option("prefill_wide", 1): 256 rows of x per tile when a chunk has more than 128 (measured slower at 512 rows: fewer blocks than SMs)
+
 cudaError_t gemm_tc_init() {
     if (g_tc_init) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k_gemm_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    e = cudaFuncSetAttribute(k_gemm_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     g_tc_init = true;
     return cudaSuccess;
@@ -340,7 +360,7 @@ bool gemm_tc_supported(const GemvArgs& a) {
     return a.push.links == nullptr;
 }
 
-uint64_t gemm_tc_rows_padded(uint32_t n_rows) { return ((uint64_t)n_rows + BN - 1) / BN * BN; }
+uint64_t gemm_tc_rows_padded(uint32_t n_rows) { return ((uint64_t)n_rows + 127) / 128 * 128; }
 
 // workspace: x as fp16 [rows padded to 128][K], then the weight matrix (two for gate/up) as fp16 [out][K]
 uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual) {
@@ -389,9 +409,15 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     p.epilogue = a.epilogue;
     p.err = nullptr;
     fast_error_word(&p.err);
-    const dim3 grid((out_dim + BM - 1) / BM, (unsigned)(rows_pad / BN));
-    if (dual) return launch(lc, k_gemm_tc<true>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
-    return launch(lc, k_gemm_tc<false>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+    // 256 rows of x per tile (half the weight traffic per flop) once there are more than 128 rows
+    if (n_rows > 128 && gemm_tc_wide) {
+        const dim3 grid((out_dim + BM - 1) / BM, (unsigned)((rows_pad + 255) / 256));
+        if (dual) return launch(lc, k_gemm_tc<true, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+        return launch(lc, k_gemm_tc<false, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+    }
+    const dim3 grid((out_dim + BM - 1) / BM, (unsigned)(rows_pad / 128));
+    if (dual) return launch(lc, k_gemm_tc<true, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+    return launch(lc, k_gemm_tc<false, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
 }
 
 }  // namespace vb
