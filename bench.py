@@ -246,11 +246,17 @@ def main():
         eng.reserve(0, max_seq)
         eng.prefill(prompt, 0)
     else:
-        # every slot its own prompt of the same length, prefilled in lockstep (one step per position)
+        # every slot its own prompt, prefilled slot by slot in tensor-core chunks; a sharded engine (no chunked
+        # prefill) runs them in lockstep, one step per position
         from velox_b200.modelspec import PROMPT_STREAM
         for slot in range(batch):
             eng.reserve(slot, max_seq)
-        eng.prefill_lockstep([H.prompt_tokens(spec, SEED, prompt_lens[slot], stream=PROMPT_STREAM + slot) for slot in range(batch)])
+        prompts = [H.prompt_tokens(spec, SEED, prompt_lens[slot], stream=PROMPT_STREAM + slot) for slot in range(batch)]
+        if tp:
+            eng.prefill_lockstep(prompts)
+        else:
+            for slot in range(batch):
+                eng.prefill(prompts[slot], slot)
     eng.sync()
     ttft_s = time.perf_counter() - t0
     prefill = None

@@ -182,6 +182,30 @@ def test_batched_variable_length_sequences(spec_i):
     eng.close()
 
 
+@pytest.mark.parametrize("spec_i", [2, 4, 6, 7])
+def test_batched_decode_on_the_tensor_core_products(spec_i):
+    """Option decode_gemm: the decode steps of a batch (one row per slot, one slot inactive, lm_head included) run
+    their products as tcgen05 GEMMs; every sequence still matches its own CPU run (int4, int8, bf16, QKV bias)."""
+    spec = SMALL_SPECS[spec_i]
+    seed, n_new = 33, 10
+    lens = [5, 23, 16, 1, 9]
+    max_seq = max(lens) + n_new + 1
+    ora, _ = H.build_oracle(spec, seed, max_seq, n_seqs=len(lens))
+    eng = H.build_engine(spec, seed, max_seq, max_batch=len(lens) + 1)
+    eng.set_option("decode_gemm", 1)
+    prompts = [H.prompt_tokens(spec, seed, n, stream=(1 << 20) + i) for i, n in enumerate(lens)]
+    for i, p in enumerate(prompts):
+        eng.reserve(i, len(p) + n_new)
+        eng.prefill(p, i)
+    eng.build_graph()
+    eng.decode(n_new - 1)
+    for i, p in enumerate(prompts):
+        want = ora.generate_greedy(p, n_new, seq=i)
+        assert np.array_equal(eng.read_tokens(i, len(p) - 1, n_new), want), i
+        assert float(np.max(np.abs(eng.logits(i) - ora.logits))) <= LOGIT_TOL
+    eng.close()
+
+
 def test_lockstep_prefill_matches_the_checker():
     """All slots prefilled together, one step per prompt position (right-aligned), then decoded together."""
     spec = SMALL_SPECS[2]

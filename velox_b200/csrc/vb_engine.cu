@@ -88,6 +88,8 @@ struct vb_ctx {
     // prompts of at least `prefill_gemm_min` tokens: chunks of up to `prefill_rows` tokens whose four products per layer
     // run on the tcgen05 tensor cores (vb_gemm_tc.cu); the workspace holds their fp16 operands
     bool prefill_gemm = true;
+    bool decode_gemm = false;   // decode steps of wide batches through the same tensor-core GEMMs (one row per slot)
+    bool decode_gemm_auto = false;  // switched on by vb_create, not by the caller: falls back silently when unsupported
     bool prefill_flash = true;  // causal tile attention for those chunks (vb_attn_prefill.cu) instead of one launch row per token
     uint32_t prefill_rows = 512, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
@@ -338,6 +340,39 @@ bool tc_products_ok(vb_ctx* c) {
     return true;
 }
 
+// Workspace of the tensor-core products for `rows` rows of x (fp16 operands): the largest of a layer's four
+// products, and of the lm_head when `with_head`.
+int32_t ensure_tc_ws(vb_ctx* c, uint32_t rows, bool with_head) {
+    const uint32_t dm = c->d.d_model;
+    uint64_t need = gemm_tc_workspace_bytes(c->qkv_rows, dm, rows, false);
+    need = std::max(need, gemm_tc_workspace_bytes(dm, c->qdim, rows, false));
+    need = std::max(need, gemm_tc_workspace_bytes(c->ffn, dm, rows, true));
+    need = std::max(need, gemm_tc_workspace_bytes(dm, c->ffn, rows, false));
+    if (with_head) need = std::max(need, gemm_tc_workspace_bytes(c->vocab, dm, rows, false));
+    if (c->tc_ws_bytes >= need) return VB_OK;
+    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }  // a captured step holds the old address
+    if (c->tc_ws) cudaFree(c->tc_ws);
+    c->tc_ws = nullptr; c->tc_ws_bytes = 0;
+    if (cudaMalloc(&c->tc_ws, need + 1024) != cudaSuccess) {  // + 1024: the swizzled operands start on a 1024-byte boundary
+        cudaGetLastError();
+        set_error("cannot allocate %llu bytes for the tensor-core workspace", (unsigned long long)need);
+        return VB_ERR_OOM;
+    }
+    c->tc_ws_bytes = need;
+    return VB_OK;
+}
+
+// decode_gemm: make sure, outside any capture, that the products can take that path and that the workspace is there
+int32_t prepare_decode_gemm(vb_ctx* c) {
+    if (!c->decode_gemm) return VB_OK;
+    if (!tc_products_ok(c)) {
+        if (c->decode_gemm_auto) { c->decode_gemm = false; return VB_OK; }
+        set_error("decode_gemm needs the canonical weight copies (not VB_FLAG_LEAN_WEIGHTS) in a format the tensor-core path reads");
+        return VB_ERR_UNSUPPORTED;
+    }
+    return ensure_tc_ws(c, std::max(c->d.max_batch, c->prefill_rows), true);
+}
+
 bool all_loaded(vb_ctx* c, const char** missing) {
     static const char* names[] = {"embed", "attn_norm", "wq", "wk", "wv", "wo", "mlp_norm", "wgate", "wup", "wdown",
                                   "final_norm", "lm_head", "bq", "bk", "bv"};
@@ -361,9 +396,14 @@ struct StepIO {
     void* tc_ws = nullptr;  // != null: the layer products run as tensor-core GEMMs with this workspace
     uint64_t tc_ws_bytes = 0;
     uint32_t first = 0;     // tensor-core chunks: position of row 0 (row j is position first + j of one sequence)
+    bool causal_chunk = false;  // rows are consecutive positions of one sequence (prefill chunk), not one row per slot
 };
+void* tc_ws_aligned(vb_ctx* c) { return (void*)(((uintptr_t)c->tc_ws + 1023) & ~(uintptr_t)1023); }
 StepIO decode_io(vb_ctx* c) {
-    return StepIO{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
+    StepIO io{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
+    // wide batches: the products (lm_head included) as tensor-core GEMMs, one row of x per slot
+    if (c->decode_gemm && c->tc_ws && c->d.tp_size <= 1) { io.tc_ws = tc_ws_aligned(c); io.tc_ws_bytes = c->tc_ws_bytes; }
+    return io;
 }
 
 // The launch sequence of one token for every active row of `state`.
@@ -427,7 +467,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         a.trace = next_trace(); a.err = c->err_word;
-        if (io.tc_ws && c->prefill_flash && attention_prefill_supported(c->hq, c->hkv, d.head_dim))
+        if (io.causal_chunk && c->prefill_flash && attention_prefill_supported(c->hq, c->hkv, d.head_dim))
             VB_TRY(attention_prefill(lcfg(c, true), io.attn_out, io.q, kv_layer, io.block_table, io.first, B, c->hq, c->hkv, d.head_dim, d.kv_block_tokens));
         else
             VB_TRY(attention(lcfg(c, true), a));
@@ -463,7 +503,8 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         h.norm_w = c->tensor(VB_ROLE_FINAL_NORM, 0).m.data; h.norm_fmt = c->tensor(VB_ROLE_FINAL_NORM, 0).m.fmt; h.eps = d.rms_eps;
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
         h.trace = next_trace(); h.max_ring = c->head_ring;
-        VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
+        if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes));
+        else VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
         if (!tp) {
             VB_TRY(argmax(lcfg(c, true), nullptr, io.logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
         } else {
@@ -550,6 +591,8 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
         c->vocab = d.vocab / tp;
         c->vocab_off = c->vocab * d.tp_rank;
     }
+    // wide batches of weights that fp16 holds exactly (int8 per channel, fp16): decode products as tensor-core GEMMs
+    c->decode_gemm = c->decode_gemm_auto = d.max_batch >= 16 && tp <= 1 && (d.weight_fmt == VB_FMT_I8PC || d.weight_fmt == VB_FMT_F16);
     c->max_blocks = (d.max_seq_len + d.kv_block_tokens - 1) / d.kv_block_tokens;
     c->n_blocks = d.kv_blocks_total ? d.kv_blocks_total : d.max_batch * c->max_blocks;
     c->n_splits = attn_pick_splits(d.max_seq_len);
@@ -874,6 +917,7 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
                "vb_prefill: prompt of %u tokens exceeds the slot's KV reservation (%u tokens)", n_tokens, c->slot_blocks[slot] * c->d.kv_block_tokens);
     for (uint32_t i = 0; i < n_tokens; ++i) VB_REQUIRE(tokens[i] < c->d.vocab, "vb_prefill: token %u at %u >= vocab", tokens[i], i);
     VB_CUDA(cudaSetDevice(c->device));
+    if ((rc = prepare_decode_gemm(c)) != VB_OK) return rc;  // the last prompt token is a decode-path step
     if (c->pf_tokens_cap < n_tokens) {
         if (c->pf_tokens) cudaFree(c->pf_tokens);
         c->pf_tokens = nullptr; c->pf_tokens_cap = 0;
@@ -904,27 +948,11 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
                 return rc;
             c->pfc_rows = cap;
         }
-        if (use_tc) {
-            const uint32_t dm = c->d.d_model;
-            uint64_t need = gemm_tc_workspace_bytes(c->qkv_rows, dm, cap, false);
-            need = std::max(need, gemm_tc_workspace_bytes(dm, c->qdim, cap, false));
-            need = std::max(need, gemm_tc_workspace_bytes(c->ffn, dm, cap, true));
-            need = std::max(need, gemm_tc_workspace_bytes(dm, c->ffn, cap, false));
-            if (c->tc_ws_bytes < need) {
-                if (c->tc_ws) cudaFree(c->tc_ws);
-                c->tc_ws = nullptr; c->tc_ws_bytes = 0;
-                if (cudaMalloc(&c->tc_ws, need + 1024) != cudaSuccess) {  // + 1024: the swizzled operands start on a 1024-byte boundary
-                    cudaGetLastError();
-                    set_error("vb_prefill: cannot allocate %llu bytes for the tensor-core workspace", (unsigned long long)need);
-                    return VB_ERR_OOM;
-                }
-                c->tc_ws_bytes = need;
-            }
-        }
+        if (use_tc && (rc = ensure_tc_ws(c, cap, false)) != VB_OK) return rc;
         VB_CUDA(launch(lcfg(c, false), k_fill_chunk_table, dim3(P), dim3(128), 0, c->pfc_table,
                        (const int32_t*)(c->block_table_dev + (size_t)slot * c->max_blocks), c->max_blocks));
         StepIO io{c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, nullptr, c->pfc_table, P, false};
-        if (use_tc) { io.tc_ws = (void*)(((uintptr_t)c->tc_ws + 1023) & ~(uintptr_t)1023); io.tc_ws_bytes = c->tc_ws_bytes; }
+        if (use_tc) { io.tc_ws = tc_ws_aligned(c); io.tc_ws_bytes = c->tc_ws_bytes; io.causal_chunk = true; }
         // the last token always takes the per-token path below (it produces the logits); the tensor-core chunks may be
         // ragged (every row of a chunk is live), the batched-kernel chunks are whole
         while (use_tc ? done + 1 < n_tokens : done + P < n_tokens) {
@@ -950,6 +978,7 @@ int32_t vb_decode_step(vb_ctx* c) {
     int32_t rc = check_ready(c, "vb_decode_step");
     if (rc != VB_OK) return rc;
     VB_CUDA(cudaSetDevice(c->device));
+    if ((rc = prepare_decode_gemm(c)) != VB_OK) return rc;
     VB_CUDA(enqueue_step(c, c->state, true, decode_io(c)));
     return VB_OK;
 }
@@ -958,6 +987,7 @@ int32_t vb_decode_graph_build(vb_ctx* c) {
     int32_t rc = check_ready(c, "vb_decode_graph_build");
     if (rc != VB_OK) return rc;
     VB_CUDA(cudaSetDevice(c->device));
+    if ((rc = prepare_decode_gemm(c)) != VB_OK) return rc;
     if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }
     if (c->graph) { cudaGraphDestroy(c->graph); c->graph = nullptr; }
     for (int attempt = 0; attempt < 2; ++attempt) {
@@ -1113,6 +1143,12 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "fuse_append")) { c->fuse_append = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_chunk")) { c->prefill_chunk = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_gemm")) { c->prefill_gemm = value != 0; return VB_OK; }
+    if (!strcmp(name, "decode_gemm")) {  // the workspace is allocated by the next vb_decode_step / vb_decode_graph_build
+        VB_REQUIRE(!value || c->d.tp_size <= 1, "vb_set_option: decode_gemm is not available on a sharded context");
+        c->decode_gemm = value != 0;
+        c->decode_gemm_auto = false;
+        return VB_OK;
+    }
     if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }
