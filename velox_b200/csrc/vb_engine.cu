@@ -94,6 +94,11 @@ struct vb_ctx {
     uint32_t prefill_rows = 512, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
     uint64_t tc_ws_bytes = 0;
+    // resident fp16 copies of the layer matrices for those products, made once when they fit `tc_resident_gb`
+    // (HBM is plentiful: 14 GB for an 8B model); otherwise every call converts into the workspace
+    void* f16_pool = nullptr;
+    uint32_t tc_resident_gb = 40;
+    bool f16_tried = false;
 
     // activations
     float *hidden = nullptr, *qkv = nullptr, *q = nullptr, *attn_out = nullptr, *act = nullptr, *logits = nullptr;
@@ -362,6 +367,31 @@ int32_t ensure_tc_ws(vb_ctx* c, uint32_t rows, bool with_head) {
     return VB_OK;
 }
 
+// One fp16 copy of every layer matrix (QKV as one block), when they fit the budget.  Tried once per context.
+int32_t ensure_f16_copies(vb_ctx* c) {
+    if (c->f16_tried) return VB_OK;
+    c->f16_tried = true;
+    if (c->d.weight_fmt == VB_FMT_F16 || c->tc_resident_gb == 0) return VB_OK;
+    const uint64_t dm = c->d.d_model;
+    const uint64_t per_layer = ((uint64_t)c->qkv_rows * dm + dm * c->qdim + 3ull * c->ffn * dm) * 2 + 5 * 1024;
+    const uint64_t total = per_layer * c->d.n_layers;
+    if (total > (uint64_t)c->tc_resident_gb << 30) return VB_OK;
+    if (cudaMalloc(&c->f16_pool, total + 1024) != cudaSuccess) { cudaGetLastError(); c->f16_pool = nullptr; return VB_OK; }
+    unsigned char* p = (unsigned char*)(((uintptr_t)c->f16_pool + 1023) & ~(uintptr_t)1023);
+    const int roles[] = {VB_ROLE_WQ, VB_ROLE_WO, VB_ROLE_WGATE, VB_ROLE_WUP, VB_ROLE_WDOWN};
+    for (uint32_t l = 0; l < c->d.n_layers; ++l)
+        for (int role : roles) {
+            Tensor& t = c->tensor(role, (int)l);
+            WMat m = t.m;
+            if (role == VB_ROLE_WQ) m.rows = c->qkv_rows;
+            VB_CUDA(weights_to_f16(lcfg(c, false), p, m));
+            t.m.f16 = p;
+            p += ((uint64_t)m.rows * m.cols * 2 + 1023) / 1024 * 1024;
+        }
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    return VB_OK;
+}
+
 // decode_gemm: make sure, outside any capture, that the products can take that path and that the workspace is there
 int32_t prepare_decode_gemm(vb_ctx* c) {
     if (!c->decode_gemm) return VB_OK;
@@ -370,6 +400,8 @@ int32_t prepare_decode_gemm(vb_ctx* c) {
         set_error("decode_gemm needs the canonical weight copies (not VB_FLAG_LEAN_WEIGHTS) in a format the tensor-core path reads");
         return VB_ERR_UNSUPPORTED;
     }
+    int32_t rc = ensure_f16_copies(c);
+    if (rc != VB_OK) return rc;
     return ensure_tc_ws(c, std::max(c->d.max_batch, c->prefill_rows), true);
 }
 
@@ -668,7 +700,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
-                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws};
+                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -948,7 +980,7 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
                 return rc;
             c->pfc_rows = cap;
         }
-        if (use_tc && (rc = ensure_tc_ws(c, cap, false)) != VB_OK) return rc;
+        if (use_tc && ((rc = ensure_f16_copies(c)) != VB_OK || (rc = ensure_tc_ws(c, cap, false)) != VB_OK)) return rc;
         VB_CUDA(launch(lcfg(c, false), k_fill_chunk_table, dim3(P), dim3(128), 0, c->pfc_table,
                        (const int32_t*)(c->block_table_dev + (size_t)slot * c->max_blocks), c->max_blocks));
         StepIO io{c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, nullptr, c->pfc_table, P, false};
@@ -1149,6 +1181,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         c->decode_gemm_auto = false;
         return VB_OK;
     }
+    if (!strcmp(name, "tc_resident_gb")) { c->tc_resident_gb = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }

@@ -29,7 +29,8 @@ constexpr int BM = 128;      // weight rows per tile (UMMA M)
 constexpr int BK = 64;       // K extent of a stage: 64 fp16 = one 128-byte swizzle row
 constexpr int TILE_BYTES = BM * BK * 2;  // 16 KB: one box of 128 rows
 // ring depth so that the stages fill 192 KB: (weight tiles + x tiles) x 16 KB per stage
-__host__ __device__ constexpr int stages_for(bool dual, int bn) { return 192 / (16 * ((dual ? 2 : 1) + bn / 128)); }
+__host__ __device__ constexpr int stage_bytes_for(bool dual, int bn) { return (dual ? 2 : 1) * TILE_BYTES + bn * BK * 2; }
+__host__ __device__ constexpr int stages_for(bool dual, int bn) { return 192 * 1024 / stage_bytes_for(dual, bn); }
 constexpr int SMEM_BYTES = 192 * 1024 + 1024 /* alignment slack */ + 256 /* barriers */;
 
 // instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate (bits 4-5 = 1), A and B fp16 (formats 0),
@@ -95,8 +96,8 @@ __global__ void __launch_bounds__(128, 1)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
           const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     constexpr int STAGES = stages_for(DUAL, BN);
-    constexpr int W_TILES = DUAL ? 2 : 1, X_TILES = BN / 128;
-    constexpr int STAGE_BYTES = (W_TILES + X_TILES) * TILE_BYTES;
+    constexpr int W_TILES = DUAL ? 2 : 1, X_TILES = BN / 128;  // BN = 32: one box of 32 rows
+    constexpr int STAGE_BYTES = stage_bytes_for(DUAL, BN);
     constexpr uint32_t IDESC = idesc_for(BN);
     constexpr uint32_t TMEM_COLS = DUAL ? 2 * BN : BN;
     extern __shared__ unsigned char smem_raw[];
@@ -108,7 +109,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * BM, tok0 = blockIdx.y * BN;
+    // the tiles of x are the fastest block index: the blocks that share a weight tile run together and it comes
+    // from DRAM once
+    const int row0 = blockIdx.y * BM, tok0 = blockIdx.x * BN;
     const int nk = (int)((p.K + BK - 1) / BK);
 
     if (threadIdx.x == 0) {
@@ -234,12 +237,16 @@ k_rows_to_f16(__half* __restrict__ dst, const float* __restrict__ x, const void*
         for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) out[k] = __float2half_rn(0.0f);
         return;
     }
-    const float* in = x + (size_t)r * K;
+    const float4* in4 = reinterpret_cast<const float4*>(x + (size_t)r * K);  // K is a multiple of 8
+    const uint32_t K4 = K / 4;
     float inv = 1.0f;
     if (norm_w) {
         __shared__ float part[8];
         float ss = 0.0f;
-        for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) { const float v = in[k]; ss = fmaf(v, v, ss); }
+        for (uint32_t k = threadIdx.x; k < K4; k += blockDim.x) {
+            const float4 v = in4[k];
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
         ss = warp_sum(ss);
         if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
         __syncthreads();
@@ -248,13 +255,22 @@ k_rows_to_f16(__half* __restrict__ dst, const float* __restrict__ x, const void*
         for (int i = 0; i < 8; ++i) tot += part[i];
         inv = 1.0f / sqrtf(tot / (float)K + eps);
     }
-    for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) {
-        float v = in[k];
+    uint2* out2 = reinterpret_cast<uint2*>(out);
+    for (uint32_t k = threadIdx.x; k < K4; k += blockDim.x) {
+        float4 v = in4[k];
         if (norm_w) {
-            const float w = norm_fmt == VB_FMT_F16 ? __half2float(((const __half*)norm_w)[k]) : ((const float*)norm_w)[k];
-            v = (v * inv) * w;
+            float4 w;
+            if (norm_fmt == VB_FMT_F16) {
+                const uint2 raw = reinterpret_cast<const uint2*>(norm_w)[k];
+                const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), w23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                w = make_float4(w01.x, w01.y, w23.x, w23.y);
+            } else {
+                w = reinterpret_cast<const float4*>(norm_w)[k];
+            }
+            v.x = (v.x * inv) * w.x; v.y = (v.y * inv) * w.y; v.z = (v.z * inv) * w.z; v.w = (v.w * inv) * w.w;
         }
-        out[k] = __float2half_rn(v);
+        const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+        out2[k] = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
     }
 }
 
@@ -323,12 +339,12 @@ EncodeTiledFn encode_fn() {
 }
 
 // fp16 [rows][K] row-major, boxes of [128 rows][64 columns], 128-byte swizzle, zeros outside the matrix
-bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t K) {
+bool make_map(CUtensorMap* m, const void* ptr, uint64_t rows, uint64_t K, uint32_t box_rows = BM) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {K, rows};
     const cuuint64_t strides[1] = {K * 2};
-    const cuuint32_t box[2] = {BK, BM};
+    const cuuint32_t box[2] = {BK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -346,12 +362,24 @@ cudaError_t gemm_tc_init() {
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(k_gemm_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<true, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(k_gemm_tc<false, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(k_gemm_tc<true, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     g_tc_init = true;
     return cudaSuccess;
+}
+
+// fp16 [rows][cols] copy of a weight matrix (int8 per channel: the integers; the row scale stays with the caller)
+cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m) {
+    const uint64_t n8 = (uint64_t)m.rows * m.cols / 8;
+    uint64_t blocks = (n8 + 255) / 256;
+    if (blocks > 148ull * 64) blocks = 148ull * 64;
+    return launch(lc, k_weights_to_f16, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<uint4*>(dst), m.data, m.scales, (int)m.fmt, n8, m.cols);
 }
 
 bool gemm_tc_supported(const GemvArgs& a) {
@@ -388,6 +416,7 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     const WMat* mats[2] = {&a.w, &a.w2};
     for (int i = 0; i < (dual ? 2 : 1); ++i) {
         if (mats[i]->fmt == VB_FMT_F16) continue;  // used where it lies
+        if (mats[i]->f16) { wh[i] = mats[i]->f16; continue; }  // resident fp16 copy
         const uint64_t n8 = (uint64_t)out_dim * K / 8;
         uint64_t blocks = (n8 + 255) / 256;
         if (blocks > 148ull * 64) blocks = 148ull * 64;
@@ -397,7 +426,8 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
         wh[i] = wbase + i * wb;
     }
     CUtensorMap mw, mw2, mx;
-    if (!make_map(&mw, wh[0], out_dim, K) || !make_map(&mx, xh, rows_pad, K)) return cudaErrorNotSupported;
+    const bool narrow = n_rows <= 32;  // decode batches: 32 rows of x per tile, no tensor-core work on padding
+    if (!make_map(&mw, wh[0], out_dim, K) || !make_map(&mx, xh, rows_pad, K, narrow ? 32 : BM)) return cudaErrorNotSupported;
     if (dual) { if (!make_map(&mw2, wh[1], out_dim, K)) return cudaErrorNotSupported; } else mw2 = mw;
     GemmParams p;
     p.dst = a.dst + a.dst_offset;
@@ -409,13 +439,18 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     p.epilogue = a.epilogue;
     p.err = nullptr;
     fast_error_word(&p.err);
+    if (narrow) {
+        const dim3 grid(1, (out_dim + BM - 1) / BM);
+        if (dual) return launch(lc, k_gemm_tc<true, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+        return launch(lc, k_gemm_tc<false, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+    }
     // 256 rows of x per tile (half the weight traffic per flop) once there are more than 128 rows
     if (n_rows > 128 && gemm_tc_wide) {
-        const dim3 grid((out_dim + BM - 1) / BM, (unsigned)((rows_pad + 255) / 256));
+        const dim3 grid((unsigned)((rows_pad + 255) / 256), (out_dim + BM - 1) / BM);
         if (dual) return launch(lc, k_gemm_tc<true, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
         return launch(lc, k_gemm_tc<false, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
     }
-    const dim3 grid((out_dim + BM - 1) / BM, (unsigned)(rows_pad / 128));
+    const dim3 grid((unsigned)(rows_pad / 128), (out_dim + BM - 1) / BM);
     if (dual) return launch(lc, k_gemm_tc<true, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
     return launch(lc, k_gemm_tc<false, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
 }

@@ -52,6 +52,8 @@ struct WMat {
     const void* v3 = nullptr;
     const void* v3_scales = nullptr;
     const void* v3_swiglu = nullptr;
+    // resident fp16 [rows][cols] copy for the tensor-core GEMMs (vb_gemm_tc.cu); null: converted per call
+    const void* f16 = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {
