@@ -281,6 +281,9 @@ def main():
                                 "what": "projection flops of prompt_len-1 rows / whole warm prefill time (host clock, includes attention, "
                                         "operand conversion and the last token's decode-path step)"}}
     eng.build_graph()
+    qd_, kd_ = spec.n_q_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+    tc_extra_bytes = (spec.d_model * (qd_ + 2 * kd_) + qd_ * spec.d_model + 3 * spec.ffn_dim * spec.d_model) * spec.n_layers \
+        if "int8" in spec.name else 0
 
     def barrier():
         if dist is not None:
@@ -353,7 +356,9 @@ def main():
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram read+write of one step: ncu on the 4-layer case of this workload measured 1.006x the
                      # algorithmic bytes per layer (profiles/k_gemv_q4_imma_llama3-8b_ncu_full.md); scaled by depth
-                     "traffic": int(step_bytes * 1.006), "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     # (batch >= 16 with int8 weights: the decode products read resident fp16 copies of the layer
+                     # matrices, 2 bytes per weight where the algorithm counts 1 -- added to the traffic figure)
+                     "traffic": int(step_bytes * 1.006) + (tc_extra_bytes if batch >= 16 and not tp else 0), "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
                      "bytes_per_launch": step_bytes},
         "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 if batch == 1 else 0, "d2h_bytes_per_step": 4 * batch},

@@ -5,11 +5,12 @@
 // Operands are fp16 in shared memory, accumulation is fp32 in tensor memory:
 //   * x rows are converted fp32 -> fp16 (with the RMS normalisation of the reference, runtime.rs:588-601,
 //     folded in) by k_rows_to_f16 into a workspace [rows][K];
-//   * the weight matrix is brought to fp16 [out][K] in the workspace by k_weights_to_f16 (int4 g32: the
-//     exact fp32 value (q-8)*s rounded once; int8 per channel: the integer, exact, the row scale is applied
-//     to the fp32 accumulator in the epilogue; fp16 matrices are used where they lie);
-//   * k_gemm_tc: one block per tile of 128 weight rows (the M of the instruction, = tensor-memory lanes) by 128
-//     rows of x (N, = tensor-memory columns).  Warp 0 / lane 0 issues the TMA copies of 128-byte-swizzled
+//   * the weight matrix is brought to fp16 [out][K] by k_weights_to_f16 (int4 g32: the exact fp32 value
+//     (q-8)*s rounded once; int8 per channel: the integer, exact, the row scale is applied to the fp32
+//     accumulator in the epilogue), either once into a resident copy the engine keeps or per call into the
+//     workspace; fp16 matrices are used where they lie;
+//   * k_gemm_tc: one block per tile of 128 weight rows (the M of the instruction, = tensor-memory lanes) by 32,
+//     128 or 256 rows of x (N, = tensor-memory columns).  Warp 0 / lane 0 issues the TMA copies of 128-byte-swizzled
 //     [128][64] fp16 boxes into a ring of stages, warp 1 / lane 0 issues tcgen05.mma (four K=16 steps per
 //     stage) and hands each stage back with tcgen05.commit, all four warps read the accumulator with
 //     tcgen05.ld and write the epilogue (store / residual add / SiLU(gate)*up with the two accumulators of the
