@@ -235,8 +235,11 @@ def test_chunked_prefill_agrees_with_token_by_token(spec_i):
     prompt = H.prompt_tokens(spec, 3, 71)
     outs = []
     for opts in ({"prefill_gemm": 0, "prefill_chunk": 1}, {"prefill_gemm": 0, "prefill_chunk": 16}, {"prefill_gemm": 0, "prefill_chunk": 5},
-                 {"prefill_rows": 512}, {"prefill_rows": 32}, {"prefill_rows": 32, "prefill_flash": 0}):
+                 {"prefill_rows": 512}, {"prefill_rows": 32}, {"prefill_rows": 32, "prefill_flash": 0},
+                 {"prefill_rows": 512, "prefill_two_per_sm": 1}, {"prefill_rows": 512, "prefill_wide": 1}):
         eng = H.build_engine(spec, 3, 96)
+        for name in ("prefill_two_per_sm", "prefill_wide"):  # process-wide switches: set in every configuration
+            eng.set_option(name, opts.get(name, 0))
         for name, value in opts.items():
             eng.set_option(name, value)
         outs.append((eng.generate_greedy(prompt, 10), eng.logits()))

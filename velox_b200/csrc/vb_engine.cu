@@ -1182,6 +1182,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         return VB_OK;
     }
     if (!strcmp(name, "tc_resident_gb")) { c->tc_resident_gb = (uint32_t)value; return VB_OK; }
+    if (!strcmp(name, "prefill_two_per_sm")) { gemm_tc_two_per_sm = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }

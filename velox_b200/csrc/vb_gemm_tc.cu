@@ -31,7 +31,10 @@ constexpr int BK = 64;       // K extent of a stage: 64 fp16 = one 128-byte swiz
 constexpr int TILE_BYTES = BM * BK * 2;  // 16 KB: one box of 128 rows
 // ring depth so that the stages fill 192 KB: (weight tiles + x tiles) x 16 KB per stage
 __host__ __device__ constexpr int stage_bytes_for(bool dual, int bn) { return (dual ? 2 : 1) * TILE_BYTES + bn * BK * 2; }
-__host__ __device__ constexpr int stages_for(bool dual, int bn) { return 192 * 1024 / stage_bytes_for(dual, bn); }
+// PER_SM = 1: the ring fills 192 KB; PER_SM = 2: 96 KB, so that two blocks share an SM and one block's prologue
+// and epilogue overlap the other's main loop
+__host__ __device__ constexpr int stages_for(bool dual, int bn, int per_sm = 1) { return (192 / per_sm) * 1024 / stage_bytes_for(dual, bn); }
+constexpr int SMEM_BYTES_HALF = 96 * 1024 + 1024 + 256;
 constexpr int SMEM_BYTES = 192 * 1024 + 1024 /* alignment slack */ + 256 /* barriers */;
 
 // instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate (bits 4-5 = 1), A and B fp16 (formats 0),
@@ -92,11 +95,11 @@ struct GemmParams {
     uint32_t* err;
 };
 
-template <bool DUAL, int BN>
-__global__ void __launch_bounds__(128, 1)
+template <bool DUAL, int BN, int PER_SM = 1>
+__global__ void __launch_bounds__(128, PER_SM)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
           const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
-    constexpr int STAGES = stages_for(DUAL, BN);
+    constexpr int STAGES = stages_for(DUAL, BN, PER_SM);
     constexpr int W_TILES = DUAL ? 2 : 1, X_TILES = BN / 128;  // BN = 32: one box of 32 rows
     constexpr int STAGE_BYTES = stage_bytes_for(DUAL, BN);
     constexpr uint32_t IDESC = idesc_for(BN);
@@ -355,6 +358,7 @@ bool g_tc_init = false;
 
 }  // namespace
 
+bool gemm_tc_two_per_sm = true;  // vb_set_option("prefill_two_per_sm", 0): one block of twice the ring depth per SM (measured 4 % slower)
 bool gemm_tc_wide = false;  // vb_set_option("prefill_wide", 1): 256 rows of x per tile when a chunk has more than 128 (measured slower at 512 rows: fewer blocks than SMs)
 
 cudaError_t gemm_tc_init() {
@@ -362,6 +366,10 @@ cudaError_t gemm_tc_init() {
     cudaError_t e = cudaFuncSetAttribute(k_gemm_tc<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(k_gemm_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<false, 128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_HALF);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_gemm_tc<true, 128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_HALF);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(k_gemm_tc<false, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return e;
@@ -452,6 +460,10 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
         return launch(lc, k_gemm_tc<false, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
     }
     const dim3 grid((unsigned)(rows_pad / 128), (out_dim + BM - 1) / BM);
+    if (gemm_tc_two_per_sm) {  // 3 (2 for gate/up) stages per block, two blocks per SM
+        if (dual) return launch(lc, k_gemm_tc<true, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, p);
+        return launch(lc, k_gemm_tc<false, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, p);
+    }
     if (dual) return launch(lc, k_gemm_tc<true, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
     return launch(lc, k_gemm_tc<false, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
 }

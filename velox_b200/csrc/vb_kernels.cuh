@@ -112,6 +112,7 @@ extern bool imma_spread;
 // `batch` = rows of x; the workspace holds the fp16 operands
 cudaError_t gemm_tc_init();
 extern bool gemm_tc_wide;
+extern bool gemm_tc_two_per_sm;
 cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m);
 bool gemm_tc_supported(const GemvArgs& a);
 uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
