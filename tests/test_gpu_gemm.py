@@ -84,12 +84,12 @@ def test_matmul_rows_linearity_at_full_size(vb, oracle, dev):
 
 def test_matmul_rows_bad_arguments(vb, dev):
     lib = vb.load()
-    b = dev(1 << 20)
+    b = dev(8 << 20)
     base = (b.ptr.value + 1023) // 1024 * 1024
     p, p16 = C.c_void_p(base), C.c_void_p(base + 16)
-    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 8, 0, 1, p, 1 << 19, None) == vb.OK
-    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 8, 4, 0, p, 1 << 19, None) == vb.OK
-    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 12, 4, 1, p, 1 << 19, None) == vb.ERR_INVALID  # in_dim % 8
-    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_Q4G32, 64, 4, 1, p, 1 << 19, None) == vb.ERR_INVALID  # no scales
-    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 64, 4, 1, p16, 1 << 19, None) == vb.ERR_INVALID  # alignment
+    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 8, 0, 1, p, 6 << 20, None) == vb.OK
+    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 8, 4, 0, p, 6 << 20, None) == vb.OK
+    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 12, 4, 1, p, 6 << 20, None) == vb.ERR_INVALID  # in_dim % 8
+    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_Q4G32, 64, 4, 1, p, 6 << 20, None) == vb.ERR_INVALID  # no scales
+    assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 64, 4, 1, p16, 6 << 20, None) == vb.ERR_INVALID  # alignment
     assert lib.vb_op_matmul_rows(p, p, p, None, vb.FMT_F32, 64, 4, 1, p, 64, None) == vb.ERR_INVALID  # workspace too small

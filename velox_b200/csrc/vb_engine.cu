@@ -364,6 +364,7 @@ int32_t ensure_tc_ws(vb_ctx* c, uint32_t rows, bool with_head) {
         return VB_ERR_OOM;
     }
     c->tc_ws_bytes = need;
+    VB_CUDA(cudaMemsetAsync((void*)(((uintptr_t)c->tc_ws + 1023) & ~(uintptr_t)1023), 0, gemm_tc_workspace_zero_bytes(), c->stream));  // split-K tile counters
     return VB_OK;
 }
 
@@ -467,7 +468,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         return nccl_allreduce_sum_f32(c->nccl, io.hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     auto product = [&](const GemvArgs& ga) -> cudaError_t {
-        if (io.tc_ws) return gemm_tc(lcfg(c, true), ga, io.tc_ws, io.tc_ws_bytes);
+        if (io.tc_ws) return gemm_tc(lcfg(c, true), ga, io.tc_ws, io.tc_ws_bytes, true);
         return gemv(lcfg(c, true), ga, c->gemv_path);
     };
     for (uint32_t l = 0; l < d.n_layers; ++l) {
@@ -535,7 +536,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         h.norm_w = c->tensor(VB_ROLE_FINAL_NORM, 0).m.data; h.norm_fmt = c->tensor(VB_ROLE_FINAL_NORM, 0).m.fmt; h.eps = d.rms_eps;
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
         h.trace = next_trace(); h.max_ring = c->head_ring;
-        if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes));
+        if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes, true));
         else VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
         if (!tp) {
             VB_TRY(argmax(lcfg(c, true), nullptr, io.logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
@@ -1183,6 +1184,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     }
     if (!strcmp(name, "tc_resident_gb")) { c->tc_resident_gb = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_two_per_sm")) { gemm_tc_two_per_sm = value != 0; return VB_OK; }
+    if (!strcmp(name, "decode_split_k")) { gemm_tc_split_k = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }

@@ -19,6 +19,8 @@
 // block still frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "vb_kernels.cuh"
 #include "vb_tma.cuh"
 
@@ -93,6 +95,10 @@ struct GemmParams {
     uint32_t out_dim, n_rows, K, dst_stride;
     int epilogue;
     uint32_t* err;
+    // split K (gridDim.z > 1): every block stores its fp32 partial tile, the last block to arrive at the tile's
+    // counter sums the partials in split order (the same bits whoever is last) and runs the epilogue
+    float* part;          // [split][tile][BN / 32][32][128]
+    uint32_t* counters;   // [tile], zero between launches (the last block puts the zero back)
 };
 
 template <bool DUAL, int BN, int PER_SM = 1>
@@ -116,7 +122,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // the tiles of x are the fastest block index: the blocks that share a weight tile run together and it comes
     // from DRAM once
     const int row0 = blockIdx.y * BM, tok0 = blockIdx.x * BN;
-    const int nk = (int)((p.K + BK - 1) / BK);
+    const int nk_all = (int)((p.K + BK - 1) / BK);
+    const int kb_first = (int)(((long long)nk_all * blockIdx.z) / gridDim.z), kb_last = (int)(((long long)nk_all * (blockIdx.z + 1)) / gridDim.z);
+    const int nk = kb_last - kb_first;  // this block's share of the K blocks
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(bars + s * 8, 1); mbar_init(bars + (STAGES + s) * 8, 1); }
@@ -145,10 +153,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (!wait_or_abort(bars + (STAGES + s) * 8, ph ^ 1u, abort_flag)) break;
             const uint32_t full = bars + s * 8, st = base + s * STAGE_BYTES;
             mbar_expect_tx(full, STAGE_BYTES);
-            tma_load_2d(st, &map_w, kb * BK, row0, full);
-            if (DUAL) tma_load_2d(st + TILE_BYTES, &map_w2, kb * BK, row0, full);
-            tma_load_2d(st + W_TILES * TILE_BYTES, &map_x, kb * BK, tok0, full);
-            if (X_TILES == 2) tma_load_2d(st + (W_TILES + 1) * TILE_BYTES, &map_x, kb * BK, tok0 + 128, full);  // rows 128..255: the next 16 groups of 8
+            const int kx = (kb_first + kb) * BK;
+            tma_load_2d(st, &map_w, kx, row0, full);
+            if (DUAL) tma_load_2d(st + TILE_BYTES, &map_w2, kx, row0, full);
+            tma_load_2d(st + W_TILES * TILE_BYTES, &map_x, kx, tok0, full);
+            if (X_TILES == 2) tma_load_2d(st + (W_TILES + 1) * TILE_BYTES, &map_x, kx, tok0 + 128, full);  // rows 128..255: the next 16 groups of 8
         }
     } else if (warp == 1 && lane == 0) {
         // ---- tensor-core issue ----
@@ -181,6 +190,30 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const float sc = (p.row_scale && o_ok) ? __half2float(p.row_scale[o]) : 1.0f;
         const float sc2 = (DUAL && p.row_scale2 && o_ok) ? __half2float(p.row_scale2[o]) : 1.0f;
         const uint32_t lane_addr = tmem + ((warp * 32u) << 16);
+        const uint32_t n_split = gridDim.z, tile = blockIdx.y * gridDim.x + blockIdx.x, n_tiles = gridDim.x * gridDim.y;
+        bool reduce = false;  // this block sums the partials of all splits instead of reading its accumulator
+        if (!DUAL && n_split > 1) {
+            __shared__ uint32_t s_last;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if ((uint32_t)(tok0 + c0) >= p.n_rows) break;
+                uint32_t v[32];
+                tmem_ld32(lane_addr + c0, v);
+                float* pt = p.part + ((((size_t)blockIdx.z * n_tiles + tile) * (BN / 32) + c0 / 32) * 32) * 128 + threadIdx.x;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) __stcg(pt + j * 128, __uint_as_float(v[j]));
+            }
+            __threadfence();
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const uint32_t old = atomicAdd(p.counters + tile, 1u);
+                s_last = old == n_split - 1 ? 1u : 0u;
+                if (s_last) { p.counters[tile] = 0u; __threadfence(); }
+            }
+            __syncthreads();
+            reduce = s_last != 0u;
+        }
+        if (DUAL || n_split == 1 || reduce) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             if ((uint32_t)(tok0 + c0) >= p.n_rows) break;  // uniform over the block
@@ -189,8 +222,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const bool live = tl < p.n_rows && (!p.state || p.state[tl].active);
             const uint32_t live_mask = __ballot_sync(0xFFFFFFFFu, live);
             uint32_t v[32], u[32];
-            tmem_ld32(lane_addr + c0, v);
-            if (DUAL) tmem_ld32(lane_addr + BN + c0, u);
+            if (reduce) {
+                float acc[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) acc[j] = 0.0f;
+                for (uint32_t z = 0; z < n_split; ++z) {
+                    const float* pt = p.part + ((((size_t)z * n_tiles + tile) * (BN / 32) + c0 / 32) * 32) * 128 + threadIdx.x;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] += __ldcg(pt + j * 128);
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
+            } else {
+                tmem_ld32(lane_addr + c0, v);
+                if (DUAL) tmem_ld32(lane_addr + BN + c0, u);
+            }
             if (!o_ok) continue;
             float* d0 = p.dst + (size_t)(tok0 + c0) * p.dst_stride + o;
             if (!DUAL && p.epilogue == EPI_RESIDUAL) {
@@ -214,6 +260,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     }
                 }
             }
+        }
         }
     } else {
         if (threadIdx.x == 0 && p.err) atomicOr(p.err, 0x40u);
@@ -359,6 +406,7 @@ bool g_tc_init = false;
 }  // namespace
 
 bool gemm_tc_two_per_sm = true;  // vb_set_option("prefill_two_per_sm", 0): one block of twice the ring depth per SM (measured 4 % slower)
+bool gemm_tc_split_k = true;  // vb_set_option("decode_split_k", 0): one block per tile of 128 weight rows
 bool gemm_tc_wide = false;  // vb_set_option("prefill_wide", 1): 256 rows of x per tile when a chunk has more than 128 (measured slower at 512 rows: fewer blocks than SMs)
 
 cudaError_t gemm_tc_init() {
@@ -400,13 +448,21 @@ bool gemm_tc_supported(const GemvArgs& a) {
 uint64_t gemm_tc_rows_padded(uint32_t n_rows) { return ((uint64_t)n_rows + 127) / 128 * 128; }
 
 // workspace: x as fp16 [rows padded to 128][K], then the weight matrix (two for gate/up) as fp16 [out][K]
+// head of the workspace: the split-K tile counters (zeroed by whoever allocates the workspace) and partial tiles
+constexpr uint64_t WS_COUNTER_BYTES = 64 * 1024, WS_PART_BYTES = 4 * 1024 * 1024, WS_HEAD_BYTES = WS_COUNTER_BYTES + WS_PART_BYTES;
+uint64_t gemm_tc_workspace_zero_bytes() { return WS_COUNTER_BYTES; }
+
 uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual) {
+    return WS_HEAD_BYTES + gemm_tc_operand_bytes(out_dim, in_dim, n_rows, dual);
+}
+
+uint64_t gemm_tc_operand_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual) {
     const uint64_t xb = (gemm_tc_rows_padded(n_rows) * in_dim * 2 + 1023) / 1024 * 1024;
     const uint64_t wb = ((uint64_t)out_dim * in_dim * 2 + 1023) / 1024 * 1024;
     return xb + (dual ? 2 : 1) * wb;
 }
 
-cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes) {
+cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed) {
     if (!gemm_tc_supported(a)) return cudaErrorInvalidValue;
     const bool dual = a.epilogue == EPI_SWIGLU;
     const uint32_t K = a.w.cols, out_dim = a.w.rows, n_rows = a.batch;
@@ -416,8 +472,8 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     if (e != cudaSuccess) return e;
     const uint64_t rows_pad = gemm_tc_rows_padded(n_rows);
     const uint64_t xb = (rows_pad * K * 2 + 1023) / 1024 * 1024, wb = ((uint64_t)out_dim * K * 2 + 1023) / 1024 * 1024;
-    __half* xh = reinterpret_cast<__half*>(workspace);
-    unsigned char* wbase = reinterpret_cast<unsigned char*>(workspace) + xb;
+    __half* xh = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES);
+    unsigned char* wbase = reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES + xb;
 
     e = launch(lc, k_rows_to_f16, dim3((unsigned)rows_pad), dim3(256), 0, xh, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
     if (e != cudaSuccess) return e;
@@ -448,8 +504,17 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     p.epilogue = a.epilogue;
     p.err = nullptr;
     fast_error_word(&p.err);
+    p.counters = reinterpret_cast<uint32_t*>(workspace);
+    p.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + WS_COUNTER_BYTES);
     if (narrow) {
-        const dim3 grid(1, (out_dim + BM - 1) / BM);
+        // few row tiles (QKV, O, down of a decode batch: 28-36 blocks on 148 SMs): split K so that every SM streams
+        const uint32_t tiles = (out_dim + BM - 1) / BM, nk = (K + BK - 1) / BK;
+        uint32_t splits = 1;
+        if (!dual && counters_zeroed && gemm_tc_split_k && tiles * 2 <= 148) {
+            splits = std::min(std::min(148u / tiles, 8u), std::max(nk / 8u, 1u));
+            if ((uint64_t)splits * tiles * 128 * 32 * 4 > WS_PART_BYTES || tiles * 4 > WS_COUNTER_BYTES) splits = 1;
+        }
+        const dim3 grid(1, tiles, splits);
         if (dual) return launch(lc, k_gemm_tc<true, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
         return launch(lc, k_gemm_tc<false, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
     }

@@ -112,11 +112,15 @@ extern bool imma_spread;
 // `batch` = rows of x; the workspace holds the fp16 operands
 cudaError_t gemm_tc_init();
 extern bool gemm_tc_wide;
+extern bool gemm_tc_split_k;
+uint64_t gemm_tc_operand_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
+uint64_t gemm_tc_workspace_zero_bytes();  // leading bytes of the workspace that must be zero before the first call
 extern bool gemm_tc_two_per_sm;
 cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m);
 bool gemm_tc_supported(const GemvArgs& a);
 uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
-cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes);
+// counters_zeroed: the caller zeroed the head of the workspace once (allows the split-K path)
+cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed = false);
 
 // vb_attn.cu
 struct AttnArgs {
