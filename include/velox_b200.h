@@ -177,6 +177,8 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "prefill_wide"   1: 256 rows of x per tensor-core tile when a chunk has more than 128 rows (default 0)
  *   "decode_gemm"    1: the products of a decode step (lm_head included) run as tensor-core GEMMs, one row of x per
  *                    slot; default 1 when max_batch >= 16 and the weights are int8 per channel or fp16, else 0
+ *   "decode_split_k" 1 (default): decode-batch products with few 128-row tiles split K over several blocks per tile
+ *                    (partials summed in a fixed order: results do not depend on scheduling)
  *   "tc_resident_gb" budget in GB for resident fp16 copies of the layer matrices used by those GEMMs (40; 0: convert
  *                    per call into the workspace)
  *   "pdl"            1: programmatic dependent launch between the kernels of a step

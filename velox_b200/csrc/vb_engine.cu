@@ -375,7 +375,9 @@ int32_t ensure_f16_copies(vb_ctx* c) {
     if (c->d.weight_fmt == VB_FMT_F16 || c->tc_resident_gb == 0) return VB_OK;
     const uint64_t dm = c->d.d_model;
     const uint64_t per_layer = ((uint64_t)c->qkv_rows * dm + dm * c->qdim + 3ull * c->ffn * dm) * 2 + 5 * 1024;
-    const uint64_t total = per_layer * c->d.n_layers;
+    Tensor& head = c->tensor(VB_ROLE_LM_HEAD, 0);
+    const bool with_head = c->decode_gemm && head.m.fmt != VB_FMT_F16 && head.m.data != nullptr;  // decode batches run the lm_head here too
+    const uint64_t total = per_layer * c->d.n_layers + (with_head ? (uint64_t)head.m.rows * head.m.cols * 2 + 1024 : 0);
     if (total > (uint64_t)c->tc_resident_gb << 30) return VB_OK;
     if (cudaMalloc(&c->f16_pool, total + 1024) != cudaSuccess) { cudaGetLastError(); c->f16_pool = nullptr; return VB_OK; }
     unsigned char* p = (unsigned char*)(((uintptr_t)c->f16_pool + 1023) & ~(uintptr_t)1023);
@@ -389,6 +391,10 @@ int32_t ensure_f16_copies(vb_ctx* c) {
             t.m.f16 = p;
             p += ((uint64_t)m.rows * m.cols * 2 + 1023) / 1024 * 1024;
         }
+    if (with_head) {
+        VB_CUDA(weights_to_f16(lcfg(c, false), p, head.m));
+        head.m.f16 = p;
+    }
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;
 }
