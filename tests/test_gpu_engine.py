@@ -182,10 +182,11 @@ def test_batched_variable_length_sequences(spec_i):
     eng.close()
 
 
-@pytest.mark.parametrize("spec_i", [2, 4, 6, 7])
+@pytest.mark.parametrize("spec_i", [2, 4, 6, 7, 10, 11])
 def test_batched_decode_on_the_tensor_core_products(spec_i):
     """Option decode_gemm: the decode steps of a batch (one row per slot, one slot inactive, lm_head included) run
-    their products as tcgen05 GEMMs; every sequence still matches its own CPU run (int4, int8, bf16, QKV bias)."""
+    their products as tcgen05 GEMMs; every sequence still matches its own CPU run (int4, int8, bf16, QKV bias; the
+    long-FFN shapes split the K of the down projection over 8 blocks per tile, the others over 1 or 2)."""
     spec = SMALL_SPECS[spec_i]
     seed, n_new = 33, 10
     lens = [5, 23, 16, 1, 9]
