@@ -171,7 +171,7 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "fuse_append"    1: bias + RoPE + KV append inside the attention kernel
  *   "prefill_chunk"  prompt tokens that go through the layers together in vb_prefill (16; 1 = token by token)
  *   "prefill_gemm"   1: prompts longer than "prefill_gemm_min" (48) tokens go through the layers in chunks of up to
- *                    "prefill_rows" (512) tokens whose products run on the tcgen05 tensor cores; 0: batched kernels
+ *                    "prefill_rows" (2048) tokens whose products run on the tcgen05 tensor cores; 0: batched kernels
  *   "prefill_flash"  1: those chunks use the causal tile attention kernel (head_dim 64 or 128); 0: one row per token
  *   "prefill_two_per_sm" 1 (default): 128-row tiles run two blocks per SM with half the ring depth each
  *   "prefill_wide"   1: 256 rows of x per tensor-core tile when a chunk has more than 128 rows (default 0)

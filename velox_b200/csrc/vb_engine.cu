@@ -91,7 +91,7 @@ struct vb_ctx {
     bool decode_gemm = false;   // decode steps of wide batches through the same tensor-core GEMMs (one row per slot)
     bool decode_gemm_auto = false;  // switched on by vb_create, not by the caller: falls back silently when unsupported
     bool prefill_flash = true;  // causal tile attention for those chunks (vb_attn_prefill.cu) instead of one launch row per token
-    uint32_t prefill_rows = 512, prefill_gemm_min = 48;
+    uint32_t prefill_rows = 2048, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
     uint64_t tc_ws_bytes = 0;
     // resident fp16 copies of the layer matrices for those products, made once when they fit `tc_resident_gb`
