@@ -475,7 +475,8 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     __half* xh = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES);
     unsigned char* wbase = reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES + xb;
 
-    e = launch(lc, k_rows_to_f16, dim3((unsigned)rows_pad), dim3(256), 0, xh, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    // decode batches (<= 32 rows, one 32-row box of x): only those 32 rows are ever read
+    e = launch(lc, k_rows_to_f16, dim3(n_rows <= 32 ? 32u : (unsigned)rows_pad), dim3(256), 0, xh, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
     if (e != cudaSuccess) return e;
     const void* wh[2] = {a.w.data, a.w2.data};
     const WMat* mats[2] = {&a.w, &a.w2};
