@@ -3,18 +3,25 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
-Workload at N=1: Llama-3-8B-shape decoder, int4 group-32 weights + fp16 scales, fp16 embeddings, batch 1,
+Headline workload: Llama-3-8B-shape decoder, int4 group-32 weights + fp16 scales, fp16 embeddings, batch 1,
 512-token prompt, greedy decode (seed-generated synthetic weights and token ids; no checkpoint offline).
-A "step" is one decode step (one token).  `value` is decode tok/s with everything resident in HBM, timed by
-CUDA events on the library's stream around K CUDA-graph replays; `e2e` is the same metric when every step
-is driven from the host through the C ABI (token and position sent in, sampled token read back).
-N>1 runs N independent replicas (the 8B model fits one GPU): weak scaling, no data-path collective.
-The workloads named qwen2-72b-int4-tp* instead shard ONE Qwen2-72B-shape model over the N ranks (tensor
-parallel: one NCCL all-reduce after the O and the down projection, captured in the decode graph): strong
-scaling, `value` is the tok/s of the group and the roofline is per GPU.
+A "step" is one decode step (one token per sequence).  `value` is decode tok/s with everything resident in
+HBM, timed by CUDA events on the library's stream around K CUDA-graph replays; `e2e` is the same metric when
+every step is driven from the host through the C ABI (token and position sent in, sampled token read back).
+N>1 runs N independent replicas of that model (it fits one GPU): weak scaling, no data-path collective.
+
+The same line carries two more objects:
+  "tp"    at every N: ONE Qwen2-72B-shape int4-g32 model, batch 1, 1024-token prompt, sharded over the N ranks
+          (tensor parallel: column-parallel QKV / gate / up, row-parallel O / down, one exchange after each; N = 1
+          is the unsharded model on one GPU): per-token latency, per-GPU roofline, and at N > 1 the speed-up over
+          the unsharded model measured on rank 0's GPU in the same run, plus a parity flag (a 2-layer model of the
+          same width gives the same 32 greedy tokens sharded and unsharded);
+  "bs32"  at N = 1: Qwen2.5-7B-shape int8 per-channel model, 32 sequences with prompt lengths uniform in
+          [256, 2048], paged fp16 KV.
+--workload NAME makes NAME the headline instead (the two extra objects are then left out).
 
 --impl reference times the CPU restatement of the reference runtime (oracle/, OpenMP on all host cores) on
-a bounded sample of the same workload; rank 0 only.
+a bounded sample of the headline workload; rank 0 only.
 """
 from __future__ import annotations
 
@@ -35,6 +42,9 @@ METRIC = "decode_tok_per_s"
 UNIT = "tok/s"
 SEED = 20250101
 PROMPT_LEN = 512
+TP_WORKLOAD = "qwen2-72b-int4-tp-bs1"
+TP_PROMPT_LEN = 1024
+BS32_WORKLOAD = "qwen2.5-7b-int8-bs32"
 
 
 def load_peaks():
@@ -116,12 +126,27 @@ def workload_spec(name: str):
     raise SystemExit("unknown workload %r" % name)
 
 
+def synthetic_prompt(vocab: int, n: int, stream: int = 0) -> np.ndarray:
+    """Token ids uniform in [0, vocab), fixed by (SEED, stream)."""
+    return np.random.default_rng([SEED, stream]).integers(0, vocab, size=n, dtype=np.int64).astype(np.uint32)
+
+
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(spec, n_layers_sample: int, n_steps: int, warm: int):
     """Times the CPU checker on `n_layers_sample` layers + head of the workload; returns per-token seconds
-    extrapolated to the full depth (weight streaming is linear in the layer count)."""
+    extrapolated to the full depth (weight streaming is linear in the layer count).  The thread count is set
+    here, to every core this process may run on: launchers export OMP_NUM_THREADS=1."""
+    os.environ["OMP_NUM_THREADS"] = str(host_cores())
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import helpers as H
     from oracle import oracle as O
+    O.lib().vo_set_num_threads(host_cores())
     sub = spec.scaled(n_layers=n_layers_sample)
     eng, _ = H.build_oracle(sub, SEED, max_seq_len=warm + n_steps + 1)
     toks = H.prompt_tokens(spec, SEED, warm + n_steps)
@@ -174,58 +199,69 @@ def run_reference(args, spec, batch, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=128)
-    ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="llama3-8b-int4-bs1")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--gemv-path", type=int, default=1)
-    ap.add_argument("--no-pdl", action="store_true")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
-    ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (quick checks)")
-    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
-    ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
-                    help="tensor-parallel workloads: NVLink peer pushes inside the library's own kernels, or NCCL")
-    args = ap.parse_args()
-    if args.warmup < 3:
-        args.warmup = 3
+class Ranks:
+    """The process group of this run (torch.distributed over NCCL; plumbing only: barriers, max over ranks)."""
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    spec, batch = workload_spec(args.workload)
-    if args.layers > 0:
-        spec = spec.scaled(name="%s-%dlayers" % (spec.name, args.layers), n_layers=args.layers)
+    def __init__(self):
+        import torch
+        self.torch = torch
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            torch.cuda.set_device(self.local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
 
-    if args.impl == "reference":
-        run_reference(args, spec, batch, rank, world)
-        return
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        if self.torch.cuda.is_available():
+            self.torch.cuda.synchronize()
 
-    import torch  # plumbing only: process group, barrier, max over ranks
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    def max(self, v: float) -> float:
+        if self.dist is None:
+            return v
+        t = self.torch.tensor([v], device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
 
+    def close(self):
+        if self.dist is not None:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: int, sharded: bool, solo: bool = False,
+            with_e2e: bool = True, with_prefill: bool = False, layers: int = 0):
+    """Builds the workload's engine(s), prefills, captures the decode graph, times `steps` replays and the same
+    steps driven from the host.  sharded: one model over all ranks (else one engine per rank); solo: this rank
+    alone (no barriers, no max over ranks).  Returns the figures of a bench line."""
     from velox_b200.engine import Engine
-    # prompt length per slot: all equal, except the variable-length batch workload
-    prompt_lens = [args.prompt_len] * batch
-    if args.workload == "qwen2.5-7b-int8-bs32":
+    spec, batch = workload_spec(workload)
+    if layers > 0:
+        spec = spec.scaled(name="%s-%dlayers" % (spec.name, layers), n_layers=layers)
+    world = 1 if solo else R.world
+    tp = is_tp(workload)
+    prompt_lens = [prompt_len] * batch
+    if workload == BS32_WORKLOAD:
         prompt_lens = [int(x) for x in np.random.default_rng(SEED).integers(256, 2049, size=batch)]
-    max_seq = max(prompt_lens) + args.warmup + 2 * args.steps + 16
-    tp = is_tp(args.workload)
-    if tp and world > 1:
+    max_seq = max(prompt_lens) + warmup + 2 * steps + 16
+
+    def barrier():
+        if not solo:
+            R.barrier()
+
+    if sharded and world > 1:
         # one model over all ranks; the 72B shape only fits one GPU with the single-layout arena
         from velox_b200.tp import connect
-        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, tp_rank=rank, tp_size=world,
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=R.local_rank, tp_rank=R.rank, tp_size=world,
                      lean_weights=batch == 1)
         connect(eng, args.tp_exchange)
     else:
-        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=local_rank, lean_weights=tp and batch == 1)
+        eng = Engine(spec, max_seq_len=max_seq, max_batch=batch, device=R.local_rank, lean_weights=tp and batch == 1)
     eng.set_option("gemv_path", args.gemv_path)
     for kv in args.set:
         name, _, val = kv.partition("=")
@@ -235,24 +271,20 @@ def main():
     t0 = time.perf_counter()
     eng.load_synthetic(SEED)
     load_s = time.perf_counter() - t0
-    if dist is not None:
-        dist.barrier()  # ranks of one model step together
+    barrier()  # ranks of one model step together
 
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import helpers as H
     t0 = time.perf_counter()
     if batch == 1:
-        prompt = H.prompt_tokens(spec, SEED, args.prompt_len)
+        prompt = synthetic_prompt(spec.vocab, prompt_len)
         eng.reserve(0, max_seq)
         eng.prefill(prompt, 0)
     else:
         # every slot its own prompt, prefilled slot by slot in tensor-core chunks; a sharded engine (no chunked
         # prefill) runs them in lockstep, one step per position
-        from velox_b200.modelspec import PROMPT_STREAM
         for slot in range(batch):
             eng.reserve(slot, max_seq)
-        prompts = [H.prompt_tokens(spec, SEED, prompt_lens[slot], stream=PROMPT_STREAM + slot) for slot in range(batch)]
-        if tp:
+        prompts = [synthetic_prompt(spec.vocab, prompt_lens[slot], stream=1 + slot) for slot in range(batch)]
+        if sharded and world > 1:
             eng.prefill_lockstep(prompts)
         else:
             for slot in range(batch):
@@ -260,7 +292,7 @@ def main():
     eng.sync()
     ttft_s = time.perf_counter() - t0
     prefill = None
-    if batch == 1 and not tp:
+    if with_prefill and batch == 1 and not tp:
         # the same prompt once more with every buffer in place: prefill throughput.  All but the last prompt token go
         # through the layers as rows of tensor-core GEMMs (vb_gemm_tc.cu); their flops against the measured dense peak.
         t1 = time.perf_counter()
@@ -269,13 +301,13 @@ def main():
         pf_s = time.perf_counter() - t1
         qdim, kvdim = spec.n_q_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
         layer_params = spec.d_model * (qdim + 2 * kvdim) + qdim * spec.d_model + 3 * spec.ffn_dim * spec.d_model
-        flops = 2.0 * layer_params * spec.n_layers * (args.prompt_len - 1)
+        flops = 2.0 * layer_params * spec.n_layers * (prompt_len - 1)
         tpeak = None
         try:
             tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
         except Exception:
             pass
-        prefill = {"tokens": args.prompt_len, "ms": 1e3 * pf_s, "tok_per_s": args.prompt_len / pf_s,
+        prefill = {"tokens": prompt_len, "ms": 1e3 * pf_s, "tok_per_s": prompt_len / pf_s,
                    "roofline": {"bound": "tensor", "achieved": flops / pf_s / 1e12, "peak": tpeak if tpeak else 1590.0, "unit": "TFLOP/s",
                                 "frac": flops / pf_s / 1e12 / (tpeak if tpeak else 1590.0), "peak_kind": "measured" if tpeak else "fallback",
                                 "what": "projection flops of prompt_len-1 rows / whole warm prefill time (host clock, includes attention, "
@@ -285,101 +317,193 @@ def main():
     tc_extra_bytes = (spec.d_model * (qd_ + 2 * kd_) + qd_ * spec.d_model + 3 * spec.ffn_dim * spec.d_model) * spec.n_layers \
         if "int8" in spec.name else 0
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize() if torch.cuda.is_available() else None
-        eng.sync()
-
     # ---- device-resident timing: K graph replays between CUDA events on the library's stream ----------
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(R.local_rank)
     sampler.start()          # nvidia-smi needs a moment to start: sample from the warm-up on, all under load
-    eng.decode(args.warmup)
+    eng.decode(warmup)
     eng.sync()
     wbytes, kv0 = eng.step_bytes()
     barrier()
     l0 = eng.launch_count()
-    ms = eng.decode(args.steps, timed=True)
+    ms = eng.decode(steps, timed=True)
     launches = eng.launch_count() - l0
+    eng.sync()
     barrier()
     _, kv1 = eng.step_bytes()
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_per_step = ms / args.steps
-    groups = 1 if tp else world  # independent model instances
+    if not solo:
+        ms = R.max(ms)
+    ms_per_step = ms / steps
+    groups = 1 if (sharded or solo) else world  # independent model instances
     value = groups * batch * 1e3 / ms_per_step
 
     # ---- end to end: every step driven from the host through the C ABI ----------------------------------
-    tok, pos = eng.state(0)
-    eng_pos = [eng.state(slot)[1] for slot in range(batch)]  # position of every slot's next token
-    barrier()
-    t0 = time.perf_counter()
-    if batch == 1:
-        for _ in range(args.steps):
-            tok = eng.forward_step(tok, pos, 0)   # sends (token,pos), replays one step, reads the token back
-            pos += 1
-    else:
-        for _ in range(args.steps):               # tokens feed back on the device; the host reads every slot's token
-            eng.decode(1)
-            for slot in range(batch):
-                eng.read_tokens(slot, eng_pos[slot], 1)
-                eng_pos[slot] += 1
-    e2e_s = time.perf_counter() - t0
+    e2e = None
+    if with_e2e:
+        tok, pos = eng.state(0)
+        eng_pos = [eng.state(slot)[1] for slot in range(batch)]  # position of every slot's next token
+        barrier()
+        t0 = time.perf_counter()
+        if batch == 1:
+            for _ in range(steps):
+                tok = eng.forward_step(tok, pos, 0)   # sends (token,pos), replays one step, reads the token back
+                pos += 1
+        else:
+            for _ in range(steps):               # tokens feed back on the device; the host reads every slot's token
+                eng.decode(1)
+                for slot in range(batch):
+                    eng.read_tokens(slot, eng_pos[slot], 1)
+                    eng_pos[slot] += 1
+        e2e_s = time.perf_counter() - t0
+        if not solo:
+            e2e_s = R.max(e2e_s)
+        e2e = {"value": groups * batch * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 if batch == 1 else 0,
+               "d2h_bytes_per_step": 4 * batch}
     if sampler.rows == []:
         # very short runs: keep the GPU busy until the sampler has something to report
         t_end = time.perf_counter() + 1.0
-        while not sampler.rows and time.perf_counter() < t_end:
+        spare = max_seq - max(eng.state(slot)[1] for slot in range(batch)) - 1
+        while not sampler.rows and time.perf_counter() < t_end and spare >= 8:
             eng.decode(8)
             eng.sync()
+            spare -= 8
     clocks = sampler.stop()
-    if dist is not None:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e = groups * batch * args.steps / e2e_s
 
     peak, peak_kind = load_peaks()
     step_bytes = wbytes + (kv0 + kv1) // 2  # mean context over the timed region
     achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
-        "config": {"workload": args.workload, "model": spec.name, "batch": batch, "prompt_len": args.prompt_len if len(set(prompt_lens)) == 1 else "uniform in [256, 2048]",
+    out = {
+        "spec": spec, "batch": batch, "ms_per_step": ms_per_step, "value": value, "e2e": e2e, "launches": int(launches),
+        "clocks": clocks, "ttft_ms": 1e3 * ttft_s, "load_s": load_s, "prefill": prefill, "groups": groups,
+        "config": {"workload": workload, "model": spec.name, "batch": batch,
+                   "prompt_len": prompt_len if len(set(prompt_lens)) == 1 else "uniform in [256, 2048]",
                    "weights": ("int8 per output channel + fp16 scales" if "int8" in spec.name else "int4 g32 + fp16 scales") +
                               ", fp16 embeddings/norms", "kv": "paged fp16, 16-token blocks",
                    "l2_policy": "inputs larger than L2: %.2f GB of weights streamed per step" % (wbytes / 1e9),
-                   "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if tp else 1,
-                   "tp_exchange": (args.tp_exchange if tp and world > 1 else None)},
+                   "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if sharded else 1,
+                   "tp_exchange": (args.tp_exchange if sharded and world > 1 else None)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      # dram read+write of one step: ncu on the 4-layer case of this workload measured 1.006x the
-                     # algorithmic bytes per layer (profiles/k_gemv_q4_imma_llama3-8b_ncu_full.md); scaled by depth
+                     # algorithmic bytes per layer, and every layer is the same five kernels; scaled by depth
                      # (batch >= 16 with int8 weights: the decode products read resident fp16 copies of the layer
                      # matrices, 2 bytes per weight where the algorithm counts 1 -- added to the traffic figure)
-                     "traffic": int(step_bytes * 1.006) + (tc_extra_bytes if batch >= 16 and not tp else 0), "peak_kind": peak_kind, "frac_of_8TBs": achieved / 8000.0,
+                     "traffic": int(step_bytes * 1.006) + (tc_extra_bytes if batch >= 16 and not tp else 0), "peak_kind": peak_kind,
+                     "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
                      "bytes_per_launch": step_bytes},
-        "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": 8 if batch == 1 else 0, "d2h_bytes_per_step": 4 * batch},
-        "gpu_launches": int(launches), "clocks": clocks,
-        "ttft_ms": 1e3 * ttft_s, "load_s": load_s,
     }
-    if prefill is not None:
-        line["prefill"] = prefill
-    if rank == 0 and not args.no_cpu_baseline and world == 1:
-        full, per_step, cores = cpu_sample(spec, 2, 2, 1)
-        line["cpu_baseline"] = {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
-                                "sample": "2 decode tokens through 2 of %d layers + lm_head on the CPU restatement, "
-                                          "extrapolated linearly to full depth" % spec.n_layers}
-    if tp and world > 1:
+    if sharded and world > 1:
         from velox_b200.tp import shutdown
         shutdown(eng)
     else:
         eng.close()
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    return out
+
+
+def tp_parity(args, R: Ranks) -> bool:
+    """A 2-layer model of the 72B width, sharded over all ranks and unsharded on rank 0: same 32 greedy tokens."""
+    from velox_b200.engine import Engine
+    from velox_b200.tp import connect, shutdown
+    spec, _ = workload_spec(TP_WORKLOAD)
+    spec = spec.scaled(name=spec.name + "-2layers", n_layers=2)
+    prompt = synthetic_prompt(spec.vocab, 24, stream=99)
+    eng = Engine(spec, max_seq_len=64, max_batch=1, device=R.local_rank, tp_rank=R.rank, tp_size=R.world, lean_weights=True)
+    connect(eng, args.tp_exchange)
+    eng.load_synthetic(SEED)
+    R.barrier()
+    got = eng.generate_greedy(prompt, 32)
+    shutdown(eng)
+    ok = 1.0
+    if R.rank == 0:
+        one = Engine(spec, max_seq_len=64, max_batch=1, device=R.local_rank, lean_weights=True)
+        one.load_synthetic(SEED)
+        want = one.generate_greedy(prompt, 32)
+        one.close()
+        ok = 1.0 if np.array_equal(got, want) else 0.0
+    return R.max(1.0 - ok) == 0.0
+
+
+def tp_object(args, R: Ranks):
+    """The north-star split: Qwen2-72B shape over the N ranks of this run (see the module docstring)."""
+    m = measure(args, R, TP_WORKLOAD, args.steps, args.warmup, TP_PROMPT_LEN, sharded=True, with_e2e=True)
+    obj = {"workload": TP_WORKLOAD, "model": m["spec"].name, "tensor_parallel": R.world, "batch": 1, "prompt_len": TP_PROMPT_LEN,
+           "ms_per_token": m["ms_per_step"], "tok_s": m["value"], "e2e_tok_s": m["e2e"]["value"], "scaling": "strong",
+           "exchange": (("NVLink peer stores inside the library's kernels" if args.tp_exchange == "p2p" else "NCCL all-reduce")
+                        if R.world > 1 else None),
+           "roofline": dict(m["roofline"], kernel="decode step (one CUDA-graph launch = one token), per GPU"),
+           "gpu_launches": m["launches"], "ttft_ms": m["ttft_ms"], "clocks": m["clocks"]}
+    if R.world > 1:
+        obj["parity_32_tokens_vs_unsharded"] = tp_parity(args, R)
+        # the unsharded model on rank 0's GPU, same box, same run: the TP-1 latency the speed-up is quoted against
+        tp1 = None
+        if R.rank == 0:
+            tp1 = measure(args, R, TP_WORKLOAD, args.steps, args.warmup, TP_PROMPT_LEN, sharded=False, solo=True, with_e2e=False)
+        R.barrier()
+        if tp1 is not None:
+            obj["tp1_ms_per_token"] = tp1["ms_per_step"]
+            obj["speedup_vs_tp1"] = tp1["ms_per_step"] / m["ms_per_step"]
+    return obj
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, help="headline workload (default llama3-8b-int4-bs1 plus the tp / bs32 objects)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="leave out the tp and bs32 objects")
+    ap.add_argument("--gemv-path", type=int, default=1)
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--prompt-len", type=int, default=0)
+    ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (quick checks)")
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
+    ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="tensor-parallel workloads: NVLink peer pushes inside the library's own kernels, or NCCL")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    extras = args.workload is None and not args.no_extras and args.layers == 0
+    if args.workload is None:
+        args.workload = "llama3-8b-int4-bs1"
+    if args.prompt_len <= 0:
+        args.prompt_len = TP_PROMPT_LEN if is_tp(args.workload) else PROMPT_LEN
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    spec, batch = workload_spec(args.workload)
+    if args.layers > 0:
+        spec = spec.scaled(name="%s-%dlayers" % (spec.name, args.layers), n_layers=args.layers)
+
+    if args.impl == "reference":
+        run_reference(args, spec, batch, rank, world)
+        return
+
+    R = Ranks()
+    tp = is_tp(args.workload)
+    m = measure(args, R, args.workload, args.steps, args.warmup, args.prompt_len, sharded=tp, with_e2e=True, with_prefill=True,
+                layers=args.layers)
+    line = {
+        "metric": METRIC, "value": m["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "strong" if tp else "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic", "config": m["config"], "roofline": m["roofline"], "e2e": m["e2e"],
+        "gpu_launches": m["launches"], "clocks": m["clocks"], "ttft_ms": m["ttft_ms"], "load_s": m["load_s"],
+    }
+    if m["prefill"] is not None:
+        line["prefill"] = m["prefill"]
+    if extras:
+        line["tp"] = tp_object(args, R)
+        if world == 1:
+            b = measure(args, R, BS32_WORKLOAD, args.steps, args.warmup, 0, sharded=False, with_e2e=True)
+            line["bs32"] = {"workload": BS32_WORKLOAD, "model": b["spec"].name, "batch": 32, "prompt_len": "uniform in [256, 2048]",
+                            "ms_per_step": b["ms_per_step"], "tok_s": b["value"], "e2e_tok_s": b["e2e"]["value"],
+                            "roofline": b["roofline"], "gpu_launches": b["launches"], "ttft_ms": b["ttft_ms"]}
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        full, per_step, cores = cpu_sample(spec, 6, 6, 1)
+        line["cpu_baseline"] = {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
+                                "sample": "6 decode tokens through 6 of %d layers + lm_head on the CPU restatement, "
+                                          "extrapolated linearly to full depth" % spec.n_layers}
+    R.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
 

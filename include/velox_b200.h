@@ -115,7 +115,10 @@ int32_t vb_destroy(vb_ctx* ctx);
  * caller passes the FULL tensor and the context keeps its own shard. */
 int32_t vb_load_tensor(vb_ctx* ctx, int32_t role, int32_t layer, const void* src, int32_t src_fmt,
                        int32_t src_loc, uint64_t rows, uint64_t cols);
-/* Load a tensor that already is in the context's storage format (canonical layout, see DESIGN). */
+/* Load a tensor that already is in the context's storage format, in the canonical layout: F32/F16/BF16
+ * [rows][cols] row-major; Q4G32 / Q4G64REF u32 [rows][cols/8], a word holding elements e0..e7 as
+ * e0|e2<<4|e4<<8|e6<<12|e1<<16|e3<<20|e5<<24|e7<<28 (src/codegen.rs:2363-2364), with f16 scales
+ * [rows][cols/32] resp. half2(scale,min) [rows][cols/64]; I8PC s8 [rows][cols] with f16 scales [rows]. */
 int32_t vb_load_tensor_packed(vb_ctx* ctx, int32_t role, int32_t layer, const void* data,
                               const void* scales, int32_t src_loc, uint64_t rows, uint64_t cols);
 /* Synthetic weights: value i = mean + std * N_i(seed, stream), generated on the GPU and converted. */
@@ -150,6 +153,12 @@ int32_t vb_read_tokens(vb_ctx* ctx, int32_t slot, uint32_t first_pos, uint32_t n
 int32_t vb_read_logits(vb_ctx* ctx, int32_t slot, float* out, uint64_t n_floats);
 int32_t vb_read_hidden(vb_ctx* ctx, int32_t slot, float* out, uint64_t n_floats);
 int32_t vb_read_state(vb_ctx* ctx, int32_t slot, uint32_t* token, uint32_t* pos);
+/* The whole device state of a slot (the reference's VeloxDecodeState + its active_mask bit,
+ * src/codegen.rs:1040-1050): `limit` = tokens of the slot's KV reservation.  The sampler clears `active`
+ * when the next position would leave the reservation, and vb_decode_run / vb_decode_step return
+ * VB_ERR_STATE instead of stepping a slot past it (the reference clamps the cache row with
+ * safe_step = min(step, S_max - 1), src/runners/tinystories_smollm.cu:213). Any out pointer may be NULL. */
+int32_t vb_read_state_ex(vb_ctx* ctx, int32_t slot, uint32_t* token, uint32_t* pos, uint32_t* active, uint32_t* limit);
 /* Kernels launched through this context since creation (graph replays count their nodes). */
 int32_t vb_launch_count(vb_ctx* ctx, uint64_t* out);
 /* Algorithmic HBM bytes of one decode step at the slots' current positions (weights once + KV). */

@@ -82,6 +82,7 @@ def lib() -> C.CDLL:
         L.vo_sample_argmax_f32.argtypes = [C.c_void_p, C.c_size_t]
         L.vo_mla_absorbed_step_f32.argtypes = [C.c_void_p] * 7 + [C.c_size_t] * 4 + [C.c_float]
         L.vo_num_threads.restype = C.c_int
+        L.vo_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 

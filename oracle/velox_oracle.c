@@ -617,6 +617,16 @@ size_t vo_engine_generate_greedy(vo_engine* e, uint32_t seq, const uint32_t* pro
     return n_new;
 }
 
+/* Host threads the checker's matrix-vector loops may use (launchers such as torch.distributed.run export
+ * OMP_NUM_THREADS=1; the timed CPU baseline states its core count and therefore sets it itself). */
+void vo_set_num_threads(int n) {
+#if defined(_OPENMP)
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int vo_num_threads(void) {
 #if defined(_OPENMP)
     return omp_get_max_threads();

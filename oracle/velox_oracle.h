@@ -113,6 +113,7 @@ const float* vo_engine_hidden(const vo_engine* e);
 size_t     vo_engine_generate_greedy(vo_engine* e, uint32_t seq, const uint32_t* prompt, size_t n_prompt,
                                      size_t n_new, uint32_t* out_tokens);
 int        vo_num_threads(void);
+void       vo_set_num_threads(int n);
 
 #ifdef __cplusplus
 }

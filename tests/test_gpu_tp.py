@@ -19,7 +19,7 @@ from velox_b200.modelspec import shard_plan
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-SEED, N_PROMPT, N_NEW = 11, 24, 40
+SEED, N_PROMPT, N_NEW = 11, 24, 32  # 32 steps: the logits compared below are those of step 32
 
 
 def _gpu_count() -> int:
@@ -54,17 +54,15 @@ def test_tp2_matches_unsharded_and_checker(tmp_path, graph, exchange):
     # every rank reports the same tokens; they are the unsharded engine's
     for r in ranks:
         assert np.array_equal(r["tokens"], ranks[0]["tokens"])
-    assert np.array_equal(ranks[0]["tokens"][:32], ref_tokens[:32])
+    assert np.array_equal(ranks[0]["tokens"], ref_tokens)
     tp_logits = np.concatenate([r["logits"] for r in ranks])
     assert tp_logits.shape == ref_logits.shape
-    if np.array_equal(ranks[0]["tokens"], ref_tokens):
-        assert np.max(np.abs(tp_logits - ref_logits)) < 2e-3  # only the summation order differs
+    assert np.max(np.abs(tp_logits - ref_logits)) < 2e-3  # only the summation order differs
     # CPU checker: logits within the path's tolerance, greedy tokens equal for the first 32 steps
     orc, stored = build_oracle(TP_SPEC, SEED, N_PROMPT + N_NEW + 8)
     o_tokens = orc.generate_greedy(prompt, N_NEW)
-    assert np.array_equal(ranks[0]["tokens"][:32], o_tokens[:32])
-    if np.array_equal(ranks[0]["tokens"], o_tokens):
-        assert np.max(np.abs(tp_logits - orc.logits)) <= 2e-2
+    assert np.array_equal(ranks[0]["tokens"], o_tokens)
+    assert np.max(np.abs(tp_logits - orc.logits)) <= 2e-2
     # stored shards are the unsharded tensors' rectangles, bit for bit
     hd, d = TP_SPEC.head_dim, TP_SPEC.d_model
     for k, r in enumerate(ranks):

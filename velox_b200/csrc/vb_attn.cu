@@ -368,8 +368,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
             for (uint32_t i = threadIdx.x; i < GM * D; i += blockDim.x) q_s[i / D][i % D] = (i < ng * D) ? qb[i] : 0.0f;
         }
         __syncthreads();
-        if (appender && gc == 0) {
+        if (appender && gc == 0 && !(a.state && a.state[b].limit && pos >= a.state[b].limit)) {
             // the new token's row goes to the cache (16-byte stores); this block reads it from new_kv below
+            // (never outside the slot's reservation: the sampler deactivates a slot before that can happen)
             const int32_t blk = spec_table ? blk_s[pos / a.block_tokens] : a.block_table[(size_t)b * a.max_blocks + pos / a.block_tokens];
             KVT* kd = reinterpret_cast<KVT*>(const_cast<void*>(a.k)) + (((size_t)blk * 2) * a.Hkv + kvh) * a.block_tokens * D +
                       (size_t)(pos % a.block_tokens) * D;

@@ -384,6 +384,7 @@ __global__ void k_bias_rope_kv_append(float* __restrict__ q_out, const float* __
     const uint32_t b = blockIdx.y;
     if (!state[b].active) return;
     const uint32_t pos = state[b].pos;
+    if (state[b].limit && pos >= state[b].limit) return;  // never write outside the slot's reservation
     const uint32_t half = D / 2;
     const uint32_t n_rot = (Hq + Hkv) * half;  // rotation pairs of q and k
     const uint32_t n_v = Hkv * half;           // v handled as pairs too
@@ -509,8 +510,7 @@ __global__ void k_argmax_stage2(uint32_t* __restrict__ out_token, const float* _
         if (state) {
             const uint32_t pos = state[b].pos;
             if (ring) ring[(size_t)b * ring_slots + (pos % ring_slots)] = tok;
-            state[b].token = tok;
-            state[b].pos = pos + 1;
+            seq_advance(state + b, tok);
         }
     }
 }
@@ -548,8 +548,7 @@ __global__ void k_argmax_pairs(const ArgPair* __restrict__ pairs, uint32_t n_ran
     const uint32_t tok = (best.i == 0xFFFFFFFFu) ? 0u : best.i;
     const uint32_t pos = state[b].pos;
     if (ring) ring[(size_t)b * ring_slots + (pos % ring_slots)] = tok;
-    state[b].token = tok;
-    state[b].pos = pos + 1;
+    seq_advance(state + b, tok);
 }
 cudaError_t argmax_pairs(const LaunchCfg& lc, const void* pairs, uint32_t n_ranks, uint32_t batch, SeqState* state, uint32_t* ring,
                          uint32_t ring_slots) {

@@ -11,110 +11,10 @@
 #include <new>
 #include <vector>
 
-#include "vb_internal.cuh"
-#include "vb_kernels.cuh"
+#include "vb_ctx.cuh"
 #include "vb_nccl.h"
 
 namespace vb {
-
-constexpr uint32_t RING_SLOTS = 1024;  // VELOX_HOST_RING_SLOTS (src/codegen.rs:1022)
-
-struct Tensor {
-    WMat m;
-    bool loaded = false;
-};
-
-}  // namespace vb
-
-using namespace vb;
-
-struct vb_ctx {
-    vb_model_desc d;
-    int device = 0;
-    cudaStream_t stream = nullptr;
-    uint64_t launches = 0;
-    int gemv_path = 1;
-    bool use_pdl = true;
-    bool fuse_append = true;
-    unsigned long long* trace = nullptr;  // [TRACE_MAX][4] device timestamps when the "trace" option is on
-    uint32_t trace_n = 0;
-    float* rope_inv_freq = nullptr;  // [head_dim/2]
-    std::vector<float> rope_inv_freq_host;
-
-    // derived
-    uint32_t qdim = 0, kvdim = 0, qkv_rows = 0, max_blocks = 0, n_blocks = 0, n_splits = 1, tokens_per_split = 32;
-    // this rank's shard (tensor parallel; equal to the whole model when tp_size == 1):
-    // query/KV heads, FFN columns [ffn_off, ffn_off + ffn) in whole 128-column blocks, vocabulary rows
-    uint32_t hq = 0, hkv = 0, ffn = 0, ffn_off = 0, vocab = 0, vocab_off = 0;
-    void* nccl = nullptr;                 // communicator of the TP group
-    TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
-    bool links_open = false, use_links = true, links_standin = false;
-    bool tp_fused_push = true;            // row-parallel products send their rows to the peers from their own epilogue
-    uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
-    uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
-    uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
-    float* partial = nullptr;             // [max_batch][d_model] row-parallel partial sums (all-reduced in place)
-    unsigned char* tp_pair = nullptr;     // [max_batch] (value, index) of this rank's best logit
-    unsigned char* tp_pairs = nullptr;    // [tp_size][max_batch] gathered
-
-    // weight arena (execution order, 256-byte aligned slabs)
-    uint8_t* arena = nullptr;
-    uint64_t arena_bytes = 0;
-    std::vector<Tensor> t;  // [role][layer]
-
-    // paged KV pool: per layer [block][K|V][kv_head][block_tokens][D] fp16
-    __half* kv_pool = nullptr;
-    uint64_t kv_layer_elems = 0;
-    int32_t* block_table_dev = nullptr;
-    std::vector<int32_t> block_table_host;
-    std::vector<int32_t> free_blocks;
-    std::vector<uint32_t> slot_blocks;  // blocks held per slot
-
-    // device state
-    SeqState* state = nullptr;     // decode state, one per slot
-    SeqState* pf_state = nullptr;  // prefill state (only the slot being prefilled is active)
-    std::vector<SeqState> state_host;
-    uint32_t* ring_host = nullptr;  // mapped pinned [max_batch][RING_SLOTS]
-    uint32_t* ring_dev = nullptr;
-    uint32_t* pf_tokens = nullptr;  // device copy of the prompt being prefilled
-    uint32_t pf_tokens_cap = 0;
-    // chunked prefill: `prefill_chunk` prompt tokens go through the layers together as rows of one step (weights are
-    // read once per chunk by the batched kernels); all rows live on the prefilled sequence's KV blocks
-    uint32_t prefill_chunk = 16;
-    SeqState* pfc_state = nullptr;        // [chunk]
-    int32_t* pfc_table = nullptr;         // [chunk][max_blocks], every row = the sequence's block-table row
-    float *pfc_hidden = nullptr, *pfc_qkv = nullptr, *pfc_q = nullptr, *pfc_attn = nullptr, *pfc_act = nullptr;
-    uint32_t pfc_rows = 0;                // rows the buffers above hold
-    // prompts of at least `prefill_gemm_min` tokens: chunks of up to `prefill_rows` tokens whose four products per layer
-    // run on the tcgen05 tensor cores (vb_gemm_tc.cu); the workspace holds their fp16 operands
-    bool prefill_gemm = true;
-    bool decode_gemm = false;   // decode steps of wide batches through the same tensor-core GEMMs (one row per slot)
-    bool decode_gemm_auto = false;  // switched on by vb_create, not by the caller: falls back silently when unsupported
-    bool prefill_flash = true;  // causal tile attention for those chunks (vb_attn_prefill.cu) instead of one launch row per token
-    uint32_t prefill_rows = 2048, prefill_gemm_min = 48;
-    void* tc_ws = nullptr;
-    uint64_t tc_ws_bytes = 0;
-    // resident fp16 copies of the layer matrices for those products, made once when they fit `tc_resident_gb`
-    // (HBM is plentiful: 14 GB for an 8B model); otherwise every call converts into the workspace
-    void* f16_pool = nullptr;
-    uint32_t tc_resident_gb = 40;
-    bool f16_tried = false;
-
-    // activations
-    float *hidden = nullptr, *qkv = nullptr, *q = nullptr, *attn_out = nullptr, *act = nullptr, *logits = nullptr;
-    float* attn_scratch = nullptr;
-    float* cand_v = nullptr;
-    uint32_t* cand_i = nullptr;
-
-    cudaGraph_t graph = nullptr;
-    cudaGraphExec_t graph_exec = nullptr;
-    uint64_t graph_nodes = 0;
-    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-
-    Tensor& tensor(int role, int layer) { return t[(size_t)role * (d.n_layers ? d.n_layers : 1) + (size_t)layer]; }
-};
-
-namespace {
 
 inline uint64_t align256(uint64_t v) { return (v + 255) & ~255ULL; }
 bool role_is_global(int role) { return role == VB_ROLE_EMBED || role == VB_ROLE_FINAL_NORM || role == VB_ROLE_LM_HEAD; }
@@ -307,13 +207,16 @@ LaunchCfg lcfg(vb_ctx* c, bool pdl) {
 }
 
 __global__ void k_set_state(SeqState* state, uint32_t slot, const uint32_t* tokens, uint32_t idx, uint32_t token,
-                            uint32_t pos, uint32_t active) {
+                            uint32_t pos, uint32_t active, uint32_t limit) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         state[slot].token = tokens ? tokens[idx] : token;
         state[slot].pos = pos;
-        state[slot].active = active;
-        state[slot].pad = 0;
+        state[slot].active = (limit && pos >= limit) ? 0u : active;
+        state[slot].limit = limit;
     }
+}
+__global__ void k_set_limit(SeqState* state, uint32_t slot, uint32_t limit) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) state[slot].limit = limit;
 }
 
 // rows j < n of a prefill chunk: prompt token first + j at position first + j; rows beyond n inactive
@@ -323,7 +226,7 @@ __global__ void k_set_chunk_state(SeqState* state, const uint32_t* tokens, uint3
         state[j].token = j < n ? tokens[first + j] : 0u;
         state[j].pos = first + j;
         state[j].active = j < n ? 1u : 0u;
-        state[j].pad = 0;
+        state[j].limit = 0;  // the host checked the chunk against the reservation
     }
 }
 
@@ -425,18 +328,6 @@ bool all_loaded(vb_ctx* c, const char** missing) {
     return true;
 }
 
-// Activation buffers and block table one launch sequence works on: the context's own (decode, one row per slot)
-// or the prefill chunk's (one row per prompt token of the chunk, all rows on the same sequence's KV blocks).
-struct StepIO {
-    float *hidden, *qkv, *q, *attn_out, *act, *logits;
-    const int32_t* block_table;
-    uint32_t B;
-    bool fused_append;  // false: K/V of all rows are appended by a kernel of their own before attention
-    void* tc_ws = nullptr;  // != null: the layer products run as tensor-core GEMMs with this workspace
-    uint64_t tc_ws_bytes = 0;
-    uint32_t first = 0;     // tensor-core chunks: position of row 0 (row j is position first + j of one sequence)
-    bool causal_chunk = false;  // rows are consecutive positions of one sequence (prefill chunk), not one row per slot
-};
 void* tc_ws_aligned(vb_ctx* c) { return (void*)(((uintptr_t)c->tc_ws + 1023) & ~(uintptr_t)1023); }
 StepIO decode_io(vb_ctx* c) {
     StepIO io{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
@@ -470,7 +361,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
     bool pushed = false;  // set by the row-parallel product when its own epilogue sent the rows to the peers
     auto exchange = [&](uint32_t site) -> cudaError_t {
         if (!tp) return cudaSuccess;
-        if (p2p) return tp_reduce(lcfg(c, true), c->links, io.hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed);
+        if (p2p) return tp_reduce(lcfg(c, true), c->links, io.hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed, state, d.d_model);
         return nccl_allreduce_sum_f32(c->nccl, io.hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     auto product = [&](const GemvArgs& ga) -> cudaError_t {
@@ -562,6 +453,22 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
     return cudaSuccess;
 }
 
+int32_t ensure_chunk_buffers(vb_ctx* c, uint32_t cap) {
+    if (c->pfc_rows >= cap) return VB_OK;
+    int32_t rc;
+    void* old[] = {c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
+    for (void* p : old) if (p) cudaFree(p);
+    c->pfc_state = nullptr; c->pfc_table = nullptr; c->pfc_hidden = c->pfc_qkv = c->pfc_q = c->pfc_attn = c->pfc_act = nullptr;
+    c->pfc_rows = 0;
+    if ((rc = dev_alloc(&c->pfc_state, cap)) != VB_OK || (rc = dev_alloc(&c->pfc_table, (uint64_t)cap * c->max_blocks)) != VB_OK ||
+        (rc = dev_alloc(&c->pfc_hidden, (uint64_t)cap * c->d.d_model)) != VB_OK || (rc = dev_alloc(&c->pfc_qkv, (uint64_t)cap * c->qkv_rows)) != VB_OK ||
+        (rc = dev_alloc(&c->pfc_q, (uint64_t)cap * c->qdim)) != VB_OK || (rc = dev_alloc(&c->pfc_attn, (uint64_t)cap * c->qdim)) != VB_OK ||
+        (rc = dev_alloc(&c->pfc_act, (uint64_t)cap * c->ffn)) != VB_OK)
+        return rc;
+    c->pfc_rows = cap;
+    return VB_OK;
+}
+
 int32_t check_ready(vb_ctx* c, const char* who) {
     if (!c) { set_error("%s: null context", who); return VB_ERR_INVALID; }
     const char* missing = nullptr;
@@ -573,7 +480,7 @@ int32_t check_ready(vb_ctx* c, const char* who) {
     return VB_OK;
 }
 
-}  // namespace
+}  // namespace vb
 
 extern "C" {
 
@@ -654,6 +561,8 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     c->free_blocks.reserve(c->n_blocks);
     for (int32_t b = (int32_t)c->n_blocks - 1; b >= 0; --b) c->free_blocks.push_back(b);
     c->slot_blocks.assign(d.max_batch, 0);
+    c->pos_hi.assign(d.max_batch, 0);
+    c->maybe_active.assign(d.max_batch, 0);
     VB_CREATE_TRY(dev_alloc(&c->state, d.max_batch));
     VB_CREATE_TRY(dev_alloc(&c->pf_state, d.max_batch));
     VB_CREATE_CUDA(cudaMemsetAsync(c->state, 0, d.max_batch * sizeof(SeqState), c->stream));
@@ -787,9 +696,28 @@ static int32_t finish_load(vb_ctx* c, Tensor* t, int32_t role, int32_t layer, co
     return VB_OK;
 }
 
-static void mark_loaded(vb_ctx* c, int32_t role, Tensor* t) {
+// Marks the tensor loaded and brings the resident fp16 copy the tensor-core products read (made once, on first use)
+// up to date with it: a tensor reloaded later must not leave those products on the old weights.  The fused QKV copy
+// belongs to Wq; a tied head's copy follows the embedding table.
+static int32_t mark_loaded(vb_ctx* c, int32_t role, int32_t layer, Tensor* t) {
     t->loaded = true;
-    if (role == VB_ROLE_EMBED && c->d.tied_lm_head) set_tied_head(c);  // tied: the head reads the table
+    int32_t owner_role = (role == VB_ROLE_WK || role == VB_ROLE_WV) ? VB_ROLE_WQ : role;
+    if (role == VB_ROLE_EMBED && c->d.tied_lm_head) {  // tied: the head reads the table
+        const void* keep = c->tensor(VB_ROLE_LM_HEAD, 0).m.f16;
+        set_tied_head(c);
+        c->tensor(VB_ROLE_LM_HEAD, 0).m.f16 = keep;
+        owner_role = VB_ROLE_LM_HEAD;
+    }
+    Tensor& o = c->tensor(owner_role, role_is_global(owner_role) ? 0 : layer);
+    if (o.m.f16 && o.m.data) {
+        WMat m = o.m;
+        if (owner_role == VB_ROLE_WQ) m.rows = c->qkv_rows;
+        LaunchCfg lc = lcfg(c, false);
+        lc.counter = nullptr;
+        VB_CUDA(weights_to_f16(lc, const_cast<void*>(o.m.f16), m));
+        VB_CUDA(cudaStreamSynchronize(c->stream));
+    }
+    return VB_OK;
 }
 
 int32_t vb_load_tensor(vb_ctx* c, int32_t role, int32_t layer, const void* src, int32_t src_fmt, int32_t src_loc,
@@ -833,8 +761,7 @@ int32_t vb_load_tensor(vb_ctx* c, int32_t role, int32_t layer, const void* src, 
     if (f32) cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor", __FILE__, __LINE__);
     if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
-    mark_loaded(c, role, t);
-    return VB_OK;
+    return mark_loaded(c, role, layer, t);
 }
 
 int32_t vb_load_tensor_packed(vb_ctx* c, int32_t role, int32_t layer, const void* data, const void* scales, int32_t src_loc,
@@ -853,8 +780,7 @@ int32_t vb_load_tensor_packed(vb_ctx* c, int32_t role, int32_t layer, const void
     if (sb) VB_CUDA(cudaMemcpyAsync(cn.scales, scales, sb, kind, c->stream));
     VB_CUDA(cudaStreamSynchronize(c->stream));
     if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
-    mark_loaded(c, role, t);
-    return VB_OK;
+    return mark_loaded(c, role, layer, t);
 }
 
 int32_t vb_load_tensor_synthetic(vb_ctx* c, int32_t role, int32_t layer, uint64_t seed, uint64_t stream_id, float mean,
@@ -880,8 +806,7 @@ int32_t vb_load_tensor_synthetic(vb_ctx* c, int32_t role, int32_t layer, uint64_
     cudaFree(f32);
     if (e != cudaSuccess) return cuda_fail(e, "vb_load_tensor_synthetic", __FILE__, __LINE__);
     if ((rc = finish_load(c, t, role, layer, cn)) != VB_OK) return rc;
-    mark_loaded(c, role, t);
-    return VB_OK;
+    return mark_loaded(c, role, layer, t);
 }
 
 int32_t vb_export_tensor(vb_ctx* c, int32_t role, int32_t layer, void* data, uint64_t data_bytes, void* scales, uint64_t scales_bytes) {
@@ -922,6 +847,9 @@ int32_t vb_seq_reserve(vb_ctx* c, int32_t slot, uint32_t n_tokens) {
     VB_CUDA(cudaSetDevice(c->device));
     VB_CUDA(cudaMemcpyAsync(c->block_table_dev + (size_t)slot * c->max_blocks + first, row + first, (size_t)(need - first) * 4,
                             cudaMemcpyHostToDevice, c->stream));
+    LaunchCfg lc = lcfg(c, false);
+    lc.counter = nullptr;
+    VB_CUDA(launch(lc, k_set_limit, dim3(1), dim3(32), 0, c->state, (uint32_t)slot, have * c->d.kv_block_tokens));
     VB_CUDA(cudaStreamSynchronize(c->stream));
     return VB_OK;
 }
@@ -932,7 +860,7 @@ int32_t vb_seq_release(vb_ctx* c, int32_t slot) {
     int32_t* row = c->block_table_host.data() + (size_t)slot * c->max_blocks;
     for (uint32_t i = c->slot_blocks[slot]; i > 0; --i) c->free_blocks.push_back(row[i - 1]);
     c->slot_blocks[slot] = 0;
-    return vb_seq_set(c, slot, 0, 0, 0);
+    return vb_seq_set(c, slot, 0, 0, 0);  // also clears the slot's limit and host-side bound
 }
 
 int32_t vb_seq_set(vb_ctx* c, int32_t slot, uint32_t token, uint32_t pos, uint32_t active) {
@@ -943,7 +871,10 @@ int32_t vb_seq_set(vb_ctx* c, int32_t slot, uint32_t token, uint32_t pos, uint32
                pos, c->slot_blocks[slot] * c->d.kv_block_tokens);
     VB_CUDA(cudaSetDevice(c->device));
     LaunchCfg lc = lcfg(c, false);
-    VB_CUDA(launch(lc, k_set_state, dim3(1), dim3(32), 0, c->state, (uint32_t)slot, (const uint32_t*)nullptr, 0u, token, pos, active));
+    VB_CUDA(launch(lc, k_set_state, dim3(1), dim3(32), 0, c->state, (uint32_t)slot, (const uint32_t*)nullptr, 0u, token, pos, active,
+                   c->slot_blocks[slot] * c->d.kv_block_tokens));
+    c->pos_hi[slot] = pos;
+    c->maybe_active[slot] = active ? 1 : 0;
     return VB_OK;
 }
 
@@ -975,18 +906,7 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
     const uint32_t P = use_tc ? std::min(c->prefill_rows, n_tokens - 1) : c->prefill_chunk;
     if (use_tc || (P >= 2 && P <= 32 && c->d.tp_size <= 1 && n_tokens > P)) {
         const uint32_t cap = use_tc ? c->prefill_rows : P;  // rows the chunk buffers hold
-        if (c->pfc_rows != cap) {
-            void* old[] = {c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act};
-            for (void* p : old) if (p) cudaFree(p);
-            c->pfc_state = nullptr; c->pfc_table = nullptr; c->pfc_hidden = c->pfc_qkv = c->pfc_q = c->pfc_attn = c->pfc_act = nullptr;
-            c->pfc_rows = 0;
-            if ((rc = dev_alloc(&c->pfc_state, cap)) != VB_OK || (rc = dev_alloc(&c->pfc_table, (uint64_t)cap * c->max_blocks)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_hidden, (uint64_t)cap * c->d.d_model)) != VB_OK || (rc = dev_alloc(&c->pfc_qkv, (uint64_t)cap * c->qkv_rows)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_q, (uint64_t)cap * c->qdim)) != VB_OK || (rc = dev_alloc(&c->pfc_attn, (uint64_t)cap * c->qdim)) != VB_OK ||
-                (rc = dev_alloc(&c->pfc_act, (uint64_t)cap * c->ffn)) != VB_OK)
-                return rc;
-            c->pfc_rows = cap;
-        }
+        if ((rc = ensure_chunk_buffers(c, cap)) != VB_OK) return rc;
         if (use_tc && ((rc = ensure_f16_copies(c)) != VB_OK || (rc = ensure_tc_ws(c, cap, false)) != VB_OK)) return rc;
         VB_CUDA(launch(lcfg(c, false), k_fill_chunk_table, dim3(P), dim3(128), 0, c->pfc_table,
                        (const int32_t*)(c->block_table_dev + (size_t)slot * c->max_blocks), c->max_blocks));
@@ -1004,21 +924,45 @@ int32_t vb_prefill(vb_ctx* c, int32_t slot, const uint32_t* tokens, uint32_t n_t
     }
     // the reference prefills one token per forward pass (velox_cuda_runner.cu:504-506)
     for (uint32_t i = done; i < n_tokens; ++i) {
-        VB_CUDA(launch(lcfg(c, false), k_set_state, dim3(1), dim3(32), 0, c->pf_state, (uint32_t)slot, (const uint32_t*)c->pf_tokens, i, 0u, i, 1u));
+        VB_CUDA(launch(lcfg(c, false), k_set_state, dim3(1), dim3(32), 0, c->pf_state, (uint32_t)slot, (const uint32_t*)c->pf_tokens, i, 0u, i, 1u,
+                       c->slot_blocks[slot] * c->d.kv_block_tokens));
         VB_CUDA(enqueue_step(c, c->pf_state, i + 1 == n_tokens, decode_io(c)));
     }
     // hand the slot over to the decode state: first generated token at position n_tokens
     VB_CUDA(cudaMemcpyAsync(c->state + slot, c->pf_state + slot, sizeof(SeqState), cudaMemcpyDeviceToDevice, c->stream));
     VB_CUDA(cudaStreamSynchronize(c->stream));
+    c->pos_hi[slot] = n_tokens;
+    c->maybe_active[slot] = 1;  // (a prompt that fills the reservation leaves the slot inactive on the device)
     return VB_OK;
+}
+
+// Steps that could carry a possibly-active slot past its KV reservation are refused on the host; on the device
+// the sampler deactivates a slot whose next position would leave it, so no kernel ever writes outside.
+static int32_t check_reservations(vb_ctx* c, uint32_t n_steps, const char* who) {
+    for (uint32_t s = 0; s < c->d.max_batch; ++s) {
+        if (!c->maybe_active[s]) continue;
+        const uint64_t limit = (uint64_t)c->slot_blocks[s] * c->d.kv_block_tokens;
+        if ((uint64_t)c->pos_hi[s] + n_steps > limit) {
+            set_error("%s: %u step(s) would take slot %u from position %u past its KV reservation of %llu tokens "
+                      "(reserve more with vb_seq_reserve, or release the slot)", who, n_steps, s, c->pos_hi[s], (unsigned long long)limit);
+            return VB_ERR_STATE;
+        }
+    }
+    return VB_OK;
+}
+static void advance_bounds(vb_ctx* c, uint32_t n_steps) {
+    for (uint32_t s = 0; s < c->d.max_batch; ++s)
+        if (c->maybe_active[s]) c->pos_hi[s] += n_steps;
 }
 
 int32_t vb_decode_step(vb_ctx* c) {
     int32_t rc = check_ready(c, "vb_decode_step");
     if (rc != VB_OK) return rc;
+    if ((rc = check_reservations(c, 1, "vb_decode_step")) != VB_OK) return rc;
     VB_CUDA(cudaSetDevice(c->device));
     if ((rc = prepare_decode_gemm(c)) != VB_OK) return rc;
     VB_CUDA(enqueue_step(c, c->state, true, decode_io(c)));
+    advance_bounds(c, 1);
     return VB_OK;
 }
 
@@ -1060,6 +1004,8 @@ int32_t vb_decode_graph_build(vb_ctx* c) {
 int32_t vb_decode_run(vb_ctx* c, uint32_t n_steps, float* elapsed_ms) {
     int32_t rc = check_ready(c, "vb_decode_run");
     if (rc != VB_OK) return rc;
+    if ((rc = check_reservations(c, n_steps, "vb_decode_run")) != VB_OK) return rc;
+    advance_bounds(c, n_steps);
     VB_CUDA(cudaSetDevice(c->device));
     if (elapsed_ms) VB_CUDA(cudaEventRecord(c->ev0, c->stream));
     for (uint32_t s = 0; s < n_steps; ++s) {
@@ -1086,10 +1032,11 @@ static int32_t check_device_error(vb_ctx* c) {
     const uint32_t v = *reinterpret_cast<volatile uint32_t*>(w);
     if (v != 0) {
         *reinterpret_cast<volatile uint32_t*>(w) = 0;
+        // a split-K product that gave up leaves its tile counters between 0 and the split count: start them over
+        if (c->tc_ws) cudaMemsetAsync(tc_ws_aligned(c), 0, gemm_tc_workspace_zero_bytes(), c->stream);
         set_error("a bounded device-side wait expired (code 0x%x): results of the last launches are invalid", v);
         return VB_ERR_TIMEOUT;
     }
-    (void)c;
     return VB_OK;
 }
 
@@ -1141,6 +1088,20 @@ int32_t vb_read_state(vb_ctx* c, int32_t slot, uint32_t* token, uint32_t* pos) {
     VB_CUDA(cudaMemcpy(&s, c->state + slot, sizeof(s), cudaMemcpyDeviceToHost));
     if (token) *token = s.token;
     if (pos) *pos = s.pos;
+    return VB_OK;
+}
+
+int32_t vb_read_state_ex(vb_ctx* c, int32_t slot, uint32_t* token, uint32_t* pos, uint32_t* active, uint32_t* limit) {
+    VB_REQUIRE(c != nullptr, "vb_read_state_ex: null context");
+    VB_REQUIRE(slot >= 0 && (uint32_t)slot < c->d.max_batch, "vb_read_state_ex: slot %d out of range", slot);
+    VB_CUDA(cudaSetDevice(c->device));
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    SeqState s;
+    VB_CUDA(cudaMemcpy(&s, c->state + slot, sizeof(s), cudaMemcpyDeviceToHost));
+    if (token) *token = s.token;
+    if (pos) *pos = s.pos;
+    if (active) *active = s.active;
+    if (limit) *limit = s.limit;
     return VB_OK;
 }
 

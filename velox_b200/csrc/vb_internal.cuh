@@ -89,8 +89,17 @@ struct SeqState {
     uint32_t token;   // token to feed at this step
     uint32_t pos;     // its position
     uint32_t active;  // 0: slot skipped by every kernel (the reference's active_mask bit)
-    uint32_t pad;
+    uint32_t limit;   // tokens the slot's KV reservation holds (0: unchecked); positions >= limit are never written
 };
+// The sampler's state advance: the slot goes inactive when its next position would leave the reservation
+// (the reference clamps with safe_step = min(step, S_max - 1), src/codegen.rs:1252; here the slot stops instead
+// of overwriting its last row).
+__host__ __device__ __forceinline__ void seq_advance(SeqState* s, uint32_t tok) {
+    const uint32_t np = s->pos + 1;
+    s->token = tok;
+    s->pos = np;
+    if (s->limit && np >= s->limit) s->active = 0;
+}
 
 // ---- launch helper: programmatic dependent launch aware -------------------------------------------
 struct LaunchCfg {

@@ -39,8 +39,9 @@ struct TpLinks {
 void tp_links_layout(TpLinks* l, uint32_t rank, uint32_t size, uint32_t max_elems, uint32_t max_batch);
 cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l);
 // `pushed`: the producing kernel already stored the partial into the peers' regions (TpPush); only poll and sum
+// `state` != null: rows (of `row_elems` elements) of inactive slots take no part in the exchange
 cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, const float* partial, uint32_t n, uint32_t site,
-                      uint32_t n_sites, uint32_t* err, bool pushed = false);
+                      uint32_t n_sites, uint32_t* err, bool pushed = false, const SeqState* state = nullptr, uint32_t row_elems = 0);
 // Exchange `site` of a step: where the epilogue of a row-parallel product sends its output rows (pairs of rows,
 // sequence-tagged 16-byte words, see vb_tp.cu) besides storing them locally.
 struct TpPush {

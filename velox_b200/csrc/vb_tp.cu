@@ -47,10 +47,12 @@ __global__ void k_tp_epoch(unsigned long long* epoch) {
 // One thread per pair of elements; grid = ceil(n/2/256).
 template <bool PUSHED>
 __global__ void __launch_bounds__(256) k_tp_reduce_ll(TpLinks links, float* __restrict__ hidden, const float* __restrict__ partial,
-                                                       uint32_t n, uint32_t site, uint32_t n_sites, uint32_t* __restrict__ err) {
+                                                       uint32_t n, uint32_t site, uint32_t n_sites, uint32_t* __restrict__ err,
+                                                       const SeqState* __restrict__ state, uint32_t row_elems) {
     pdl_wait();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;  // element pair
-    const bool valid = 2 * i < n;
+    // rows of inactive slots are neither sent nor awaited (activity is replicated: every rank skips the same rows)
+    const bool valid = 2 * i < n && !(state && !state[(2 * i) / row_elems].active);
     const unsigned long long epoch = *reinterpret_cast<const volatile unsigned long long*>(links.base[links.rank] + links.epoch_off);
     const uint32_t seq = (uint32_t)(epoch * n_sites + site) + 1u;
     const size_t slot_elems = links.max_pairs;  // uint4 slots per (buffer, source)
@@ -112,8 +114,7 @@ __global__ void k_tp_argmax_ll(TpLinks links, const uint2* __restrict__ pairs, u
     const uint32_t tok = best_i == 0xFFFFFFFFu ? 0u : best_i;
     const uint32_t pos = state[b].pos;
     if (ring) ring[(size_t)b * ring_slots + (pos % ring_slots)] = tok;
-    state[b].token = tok;
-    state[b].pos = pos + 1;
+    seq_advance(state + b, tok);
 }
 
 }  // namespace
@@ -133,12 +134,12 @@ cudaError_t tp_epoch_advance(const LaunchCfg& lc, const TpLinks& l) {
 }
 
 cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, const float* partial, uint32_t n, uint32_t site,
-                      uint32_t n_sites, uint32_t* err, bool pushed) {
+                      uint32_t n_sites, uint32_t* err, bool pushed, const SeqState* state, uint32_t row_elems) {
     if (n == 0) return cudaSuccess;
-    if (n % 2 != 0 || (n + 1) / 2 > l.max_pairs) return cudaErrorInvalidValue;
+    if (n % 2 != 0 || (n + 1) / 2 > l.max_pairs || (state && (row_elems == 0 || row_elems % 2 != 0))) return cudaErrorInvalidValue;
     const uint32_t pairs = n / 2;
-    if (pushed) return launch(lc, k_tp_reduce_ll<true>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err);
-    return launch(lc, k_tp_reduce_ll<false>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err);
+    if (pushed) return launch(lc, k_tp_reduce_ll<true>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err, state, row_elems);
+    return launch(lc, k_tp_reduce_ll<false>, dim3((pairs + 255) / 256), dim3(256), 0, l, hidden, partial, n, site, n_sites, err, state, row_elems);
 }
 
 cudaError_t tp_argmax(const LaunchCfg& lc, const TpLinks& l, const void* pairs, uint32_t batch, uint32_t site, uint32_t n_sites,

@@ -154,6 +154,12 @@ class Engine:
         L.check(self._lib.vb_read_state(self.h, slot, C.byref(t), C.byref(p)))
         return t.value, p.value
 
+    def state_ex(self, slot: int = 0):
+        """(token, pos, active, limit) of a slot; limit = tokens of its KV reservation."""
+        t, p, a, l = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint32()
+        L.check(self._lib.vb_read_state_ex(self.h, slot, C.byref(t), C.byref(p), C.byref(a), C.byref(l)))
+        return t.value, p.value, a.value, l.value
+
     # ---- the reference's engine calls --------------------------------------------------------------
     def forward_step(self, token: int, pos: int, slot: int = 0) -> int:
         """src/runtime.rs:1328: one token at `pos`; returns the greedy next token."""

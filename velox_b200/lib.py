@@ -65,6 +65,7 @@ SIGNATURES = {
     "vb_read_logits": (_i32, [_vp, _i32, _vp, _u64]),
     "vb_read_hidden": (_i32, [_vp, _i32, _vp, _u64]),
     "vb_read_state": (_i32, [_vp, _i32, C.POINTER(_u32), C.POINTER(_u32)]),
+    "vb_read_state_ex": (_i32, [_vp, _i32, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32), C.POINTER(_u32)]),
     "vb_launch_count": (_i32, [_vp, C.POINTER(_u64)]),
     "vb_step_bytes": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "vb_set_option": (_i32, [_vp, C.c_char_p, C.c_int64]),
