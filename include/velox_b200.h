@@ -128,6 +128,15 @@ int32_t vb_load_tensor_synthetic(vb_ctx* ctx, int32_t role, int32_t layer, uint6
 int32_t vb_export_tensor(vb_ctx* ctx, int32_t role, int32_t layer, void* data, uint64_t data_bytes,
                          void* scales, uint64_t scales_bytes);
 int32_t vb_weight_bytes(vb_ctx* ctx, uint64_t* total_bytes);
+/* GGUF tensor types this library reads (ggml type numbers), and the byte size of a tensor of n_elems elements
+ * (0 for an unsupported type or a K-quant tensor that is not whole super-blocks). */
+enum { VB_GGML_F32 = 0, VB_GGML_F16 = 1, VB_GGML_Q4_K = 12, VB_GGML_Q6_K = 14 };
+uint64_t vb_gguf_tensor_bytes(int32_t ggml_type, uint64_t n_elems);
+/* Load one tensor as it sits in a GGUF file (host memory, [rows][cols] with cols innermost): F32 / F16 as
+ * vb_load_tensor; Q4_K / Q6_K are unpacked on the GPU to the reference's q4 group-64 format exactly as its loader does
+ * (load_gguf_tensor_to_arena, src/runners/velox_cuda_runner_k2.cu:350-417) -- stored as is by a VB_FMT_Q4G64REF
+ * context, converted through fp32 by any other. */
+int32_t vb_load_tensor_gguf(vb_ctx* ctx, int32_t role, int32_t layer, const void* src, int32_t ggml_type, uint64_t rows, uint64_t cols);
 
 /* Sequences.  A slot is one of max_batch sequences; reserve() assigns KV blocks for `n_tokens`
  * positions up front so that no decode step ever allocates. */
@@ -147,6 +156,21 @@ int32_t vb_decode_graph_build(vb_ctx* ctx);
  * (velox_cuda_runner.cu:537-546).  If elapsed_ms != NULL the call brackets the replays with CUDA
  * events on the context's stream, waits for the end and returns the device time. */
 int32_t vb_decode_run(vb_ctx* ctx, uint32_t n_steps, float* elapsed_ms);
+/* Prompt-lookup speculative decoding of one sequence (src/runners/velox_cuda_runner_k2.cu:2127-2311; drafting
+ * :1572-1611): prefill `prompt`, then generate n_new greedy tokens (the first comes from the prefill) where each
+ * forward pass verifies up to max_draft_len (1..7) drafted tokens at once.  The tokens are those of plain greedy
+ * decoding; `stats` (may be NULL) reports the draft bookkeeping the reference prints.  ema_floor: acceptance EMA below
+ * which drafting pauses (reference default 0.20).  The slot needs n_prompt + n_new + max_draft_len reserved tokens;
+ * every other slot must be inactive.  On return the slot's device state holds the next token to feed. */
+typedef struct vb_spec_stats {
+    uint64_t steps;        /* forward passes after the prefill                                  */
+    uint64_t plain_steps;  /* of which single-token passes (no draft, or paused by the policy)   */
+    uint64_t drafted, accepted;
+    float    ema_final;
+    uint32_t ladder_final;
+} vb_spec_stats;
+int32_t vb_generate_speculative(vb_ctx* ctx, int32_t slot, const uint32_t* prompt, uint32_t n_prompt, uint32_t n_new,
+                                uint32_t max_draft_len, float ema_floor, uint32_t* out_tokens, vb_spec_stats* stats);
 int32_t vb_sync(vb_ctx* ctx);
 /* Tokens generated for `slot`: ring entries of positions [first_pos, first_pos+n). */
 int32_t vb_read_tokens(vb_ctx* ctx, int32_t slot, uint32_t first_pos, uint32_t n, uint32_t* out);
@@ -197,6 +221,12 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "tp_p2p_standin" diagnostic: private stand-in regions instead of peers (every exchange then runs into its
  *                    poll limit; used by the time-out test) */
 int32_t vb_set_option(vb_ctx* ctx, const char* name, int64_t value);
+/* Sampler of the decode steps that follow: temperature <= 1e-5 or top_p <= 0 is the greedy argmax (the reference's own
+ * fallback, src/runtime.rs:1100); otherwise temperature + nucleus sampling (vb_op_sample_top_p) with the coin of
+ * sequence `slot` at position `pos` drawn from (seed, slot, pos) by a counter hash, so that a run is reproducible and
+ * independent of batching.  mode 0: sample_top_p_f32 (src/runtime.rs:1092-1152); mode 1: the emitted C99 model's walk
+ * over the unsorted distribution (src/runners/tinystories_smollm.c:506-529).  Drops the captured graph. */
+int32_t vb_set_sampling(vb_ctx* ctx, float temperature, float top_p, uint64_t seed, int32_t mode);
 
 /* Tensor parallel set-up (tp_size>1): every rank calls vb_tp_unique_id on rank 0's buffer contents
  * (128 bytes, exchanged by the host through its own channel) and then vb_tp_init. */
@@ -244,6 +274,12 @@ int32_t vb_op_gqa_attention(float* out, const float* q, const float* k_cache, co
 /* SampleArgmax (src/runtime.rs:1078-1088): first index of the maximum; NaN never wins. */
 int32_t vb_op_sample_argmax(uint32_t* out_token, const float* logits, uint32_t n, void* scratch,
                             uint64_t scratch_bytes, void* stream);
+/* SampleTopP (src/runtime.rs:1092-1152; mode 1: src/runners/tinystories_smollm.c:506-529): temperature + nucleus
+ * sampling of one row of logits with the caller's coin in [0,1), as the reference takes it.  Equal probabilities
+ * rank by index (the reference's unstable sort leaves their order open); sums are block reductions, so a decision
+ * within rounding of a threshold may pick the neighbouring token of a sequential sum.  `scratch`: n floats. */
+int32_t vb_op_sample_top_p(uint32_t* out_token, const float* logits, uint32_t n, float temperature, float top_p,
+                           float random_coin, int32_t mode, void* scratch, uint64_t scratch_bytes, void* stream);
 /* The same argmax for callers that must not allocate device memory and have none to spare: a runner that has
  * handed all of its memory to the arenas up front (the reference's "0 dynamic allocations" serving rule), code
  * running while a stream is being captured, or a host behind an FFI that forbids cudaMalloc.  No counterpart in
@@ -264,6 +300,10 @@ int32_t vb_op_mla_absorbed(float* dst, const float* x, const float* w_norm, cons
  * symmetric formats).  `src` fp32 [rows][cols] on the device. */
 int32_t vb_op_quantize(void* data, void* scales, const float* src, int32_t fmt, uint64_t rows, uint64_t cols, void* stream);
 int32_t vb_op_dequantize(float* dst, const void* data, const void* scales, int32_t fmt, uint64_t rows, uint64_t cols, void* stream);
+/* GGUF Q4_K (144-byte) / Q6_K (210-byte) super-blocks of 256 weights -> q4 group-64: 32 packed words and 4
+ * half2(scale,min) per block (velox_cuda_unpack_q4_k_fused_kernel / _q6_k_, src/runners/velox_cuda_runner_k2.cu:211-347).
+ * All pointers are device pointers. */
+int32_t vb_op_unpack_gguf(void* words, void* scale_min, const void* src_blocks, int32_t ggml_type, uint64_t n_blocks, void* stream);
 int32_t vb_op_fill_normal(float* dst, uint64_t n, uint64_t seed, uint64_t stream_id, float mean, float std, void* stream);
 /* Bytes of scratch the ops above want for a given problem (upper bound). */
 uint64_t vb_op_scratch_bytes(uint32_t n_q_heads, uint32_t head_dim, uint32_t max_seq, uint32_t vocab);

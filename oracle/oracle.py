@@ -28,9 +28,21 @@ class VoConfig(C.Structure):
                 ("qkv_bias", C.c_uint32), ("n_seqs", C.c_uint32), ("mla_latent", C.c_uint32)]
 
 
+def _stale(target: str) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(os.path.join(_HERE, f)) > t for f in os.listdir(_HERE) if f.endswith((".c", ".h")))
+
+
+class SpecStats(C.Structure):
+    _fields_ = [("steps", C.c_uint64), ("plain_steps", C.c_uint64), ("drafted", C.c_uint64), ("accepted", C.c_uint64),
+                ("ema_final", C.c_float), ("ladder_final", C.c_uint32)]
+
+
 def build(force: bool = False) -> None:
     """Compile the checker with the Makefile beside this file (gcc, a few seconds)."""
-    if force or not os.path.exists(os.path.join(_HERE, "libvelox_oracle.so")):
+    if force or _stale(os.path.join(_HERE, "libvelox_oracle.so")):
         subprocess.check_call(["make", "-C", _HERE, "libvelox_oracle.so"], stdout=subprocess.DEVNULL)
     if force or not os.path.exists(os.path.join(_HERE, "_ref", "libvelox_ref_smollm.so")):
         subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
@@ -82,6 +94,18 @@ def lib() -> C.CDLL:
         L.vo_sample_argmax_f32.argtypes = [C.c_void_p, C.c_size_t]
         L.vo_mla_absorbed_step_f32.argtypes = [C.c_void_p] * 7 + [C.c_size_t] * 4 + [C.c_float]
         L.vo_num_threads.restype = C.c_int
+        for f in ("vo_sample_top_p_f32", "vo_sample_top_p_c99"):
+            getattr(L, f).restype = C.c_uint32
+            getattr(L, f).argtypes = [C.c_void_p, C.c_size_t, C.c_float, C.c_float, C.c_float, C.POINTER(C.c_float)]
+        L.vo_sample_coin.restype = C.c_float
+        L.vo_sample_coin.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32]
+        L.vo_prompt_lookup_draft.restype = C.c_int
+        L.vo_prompt_lookup_draft.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_int]
+        L.vo_engine_generate_speculative.restype = C.c_size_t
+        L.vo_engine_generate_speculative.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_float,
+                                                     C.c_void_p, C.POINTER(SpecStats)]
+        L.vo_unpack_q4_k.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+        L.vo_unpack_q6_k.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
         L.vo_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
@@ -225,6 +249,14 @@ class Engine:
         lib().vo_engine_generate_greedy(self.h, seq, _p(prompt), len(prompt), n_new, _p(out))
         return out
 
+    def generate_speculative(self, prompt, n_new: int, max_draft_len: int = 3, ema_floor: float = 0.20, seq: int = 0):
+        """(tokens, stats) of the prompt-lookup speculative loop (velox_cuda_runner_k2.cu:2166-2310)."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+        out = np.zeros(n_new, dtype=np.uint32)
+        st = SpecStats()
+        lib().vo_engine_generate_speculative(self.h, seq, _p(prompt), len(prompt), n_new, max_draft_len, ema_floor, _p(out), C.byref(st))
+        return out, st
+
     def close(self):
         if self.h:
             lib().vo_engine_destroy(self.h)
@@ -235,3 +267,34 @@ class Engine:
             self.close()
         except Exception:
             pass
+
+
+def sample_top_p(logits: np.ndarray, temperature: float, top_p: float, coin: float, mode: int = 0):
+    """(token, margin): mode 0 = src/runtime.rs:1092-1152, mode 1 = the emitted C99 twin."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    m = C.c_float()
+    fn = lib().vo_sample_top_p_f32 if mode == 0 else lib().vo_sample_top_p_c99
+    tok = fn(_p(logits), logits.size, temperature, top_p, coin, C.byref(m))
+    return int(tok), float(m.value)
+
+
+def sample_coin(seed: int, slot: int, pos: int) -> float:
+    return float(lib().vo_sample_coin(seed, slot, pos))
+
+
+def prompt_lookup_draft(history, max_draft: int) -> np.ndarray:
+    history = np.ascontiguousarray(history, dtype=np.uint32)
+    out = np.zeros(8, dtype=np.uint32)
+    n = lib().vo_prompt_lookup_draft(_p(history), len(history), _p(out), max_draft)
+    return out[:n]
+
+
+def unpack_gguf(blocks: np.ndarray, ggml_type: int):
+    """Q4_K (type 12) / Q6_K (type 14) super-blocks -> (words [n*32] u32, scale_min [n*4][2] u16) in q4 group-64."""
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    bs = {12: 144, 14: 210}[ggml_type]
+    n = blocks.size // bs
+    words = np.empty(n * 32, dtype=np.uint32)
+    sm = np.empty((n * 4, 2), dtype=np.uint16)
+    (lib().vo_unpack_q4_k if ggml_type == 12 else lib().vo_unpack_q6_k)(_p(words), _p(sm), _p(blocks), n)
+    return words, sm

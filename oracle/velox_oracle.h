@@ -115,6 +115,40 @@ size_t     vo_engine_generate_greedy(vo_engine* e, uint32_t seq, const uint32_t*
 int        vo_num_threads(void);
 void       vo_set_num_threads(int n);
 
+/* ---- rows next to the decode step (velox_oracle_next.c) ----------------------------------- */
+/* src/runtime.rs:1092-1152: temperature + nucleus sampling; equal probabilities sort lower index first.
+ * `margin` (may be NULL): how far the two threshold decisions were from flipping. */
+uint32_t vo_sample_top_p_f32(const float* logits, size_t n, float temperature, float top_p, float random_coin, float* margin);
+/* src/runners/tinystories_smollm.c:506-529: the emitted C99 twin (unsorted cumulative walk). */
+uint32_t vo_sample_top_p_c99(const float* logits, size_t n, float temperature, float top_p, float random_coin, float* margin);
+/* The coin both engines draw for (seed, slot, position): the reference leaves the coin to its caller. */
+float    vo_sample_coin(uint64_t seed, uint32_t slot, uint32_t pos);
+
+/* src/runners/velox_cuda_runner_k2.cu:1572-1611: prompt-lookup drafting; returns the draft length. */
+int      vo_prompt_lookup_draft(const uint32_t* history, size_t history_len, uint32_t* draft, int max_draft);
+/* src/runners/velox_cuda_runner_k2.cu:2160-2225, :2298-2303: adaptive draft-width policy. */
+typedef struct vo_spec_policy {
+    int   max_draft_len;
+    float ema_floor, ema;
+    int   plain_stride, plain_since_spec;
+} vo_spec_policy;
+void     vo_spec_policy_init(vo_spec_policy* p, int max_draft_len, float ema_floor);
+int      vo_spec_policy_width(vo_spec_policy* p, int K, size_t remaining);
+void     vo_spec_policy_update(vo_spec_policy* p, int accepted, int K);
+typedef struct vo_spec_stats {
+    uint64_t steps, plain_steps, drafted, accepted;
+    float    ema_final;
+    uint32_t ladder_final;
+} vo_spec_stats;
+/* src/runners/velox_cuda_runner_k2.cu:2166-2310: the speculative generation loop over the CPU engine. */
+size_t   vo_engine_generate_speculative(vo_engine* e, uint32_t seq, const uint32_t* prompt, size_t n_prompt, size_t n_new,
+                                        int max_draft_len, float ema_floor, uint32_t* out_tokens, vo_spec_stats* st);
+
+/* src/runners/velox_cuda_runner_k2.cu:200-347: GGUF Q4_K (144-byte) / Q6_K (210-byte) super-blocks of 256 weights ->
+ * the reference's q4 group-64 format: 32 packed words + 4 half2(scale,min) per block. */
+void     vo_unpack_q4_k(uint32_t* words, uint16_t* scale_min, const uint8_t* src, size_t n_blocks);
+void     vo_unpack_q6_k(uint32_t* words, uint16_t* scale_min, const uint8_t* src, size_t n_blocks);
+
 #ifdef __cplusplus
 }
 #endif

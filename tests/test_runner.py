@@ -89,3 +89,30 @@ def test_runner_generates_the_checkers_tokens_from_a_safetensors_file(tmp_path, 
     assert re.search(r"TTFT \(Prefill Latency\) : [0-9.]+ ms", r.stdout) and "Final Step Top-5 Logits:" in r.stdout
     top1 = re.search(r"#1: token_id=(\d+) logit=([-0-9.]+)", r.stdout)
     assert int(top1.group(1)) == int(np.argmax(ora.logits)) and abs(float(top1.group(2)) - float(np.max(ora.logits))) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_runner_takes_the_flags_the_compiler_driver_passes(tmp_path):
+    """`veloxc --run` always passes --verbose and, when asked, --speculative / --draft-len / --spec-ema, plus --context-len
+    for the K2 runner (src/cli.rs:653-683): the speculative run prints the same tokens as the plain one, the report keeps
+    the lines the reference's tooling parses."""
+    base = [runner_path(), "--synthetic", "3", "--dims", "4096,512,2,8,2,64,1408", "--quantize", "q4g32", "--steps", "40", "--verbose",
+            "--tokens", "5,9,5,9,5,9,5,9,11,5,9"]
+    plain = subprocess.run(base, capture_output=True, text=True, timeout=300)
+    assert plain.returncode == 0, plain.stderr[-2000:]
+    spec = subprocess.run(base + ["--speculative", "--draft-len", "4", "--spec-ema", "0.2", "--context-len", "16384"],
+                          capture_output=True, text=True, timeout=300)
+    assert spec.returncode == 0, spec.stderr[-2000:]
+    pat = r"Generated Tokens \(40\)\s*: \[([0-9, ]*)\]"
+    assert re.search(pat, plain.stdout).group(1) == re.search(pat, spec.stdout).group(1)
+    steps = re.findall(r"^\[Step (\d+)\] Token: (\d+)", spec.stdout, flags=re.M)
+    assert [int(s) for s, _ in steps] == list(range(40))
+    assert "Decoding Mode          : Speculative Decoding (Prompt-Lookup, max draft K=4)" in spec.stdout
+    assert re.search(r"Draft Acceptance Rate  : [0-9.]+% \(\d+ / \d+ draft tokens accepted\)", spec.stdout)
+    assert "Parity 4-token check   : SKIPPED" in spec.stdout and "Parity 32-token check  : SKIPPED" in spec.stdout
+    assert "Decoding Mode          : Autoregressive Standard (Single Token)" in plain.stdout
+    # "--speculative K" carries the width itself, as the reference runner parses it
+    spec2 = subprocess.run(base + ["--speculative", "2"], capture_output=True, text=True, timeout=300)
+    assert spec2.returncode == 0 and "max draft K=2" in spec2.stdout
+    sampled = subprocess.run(base + ["--temperature", "0.9", "--top-p", "0.9", "--seed", "4"], capture_output=True, text=True, timeout=300)
+    assert sampled.returncode == 0 and "Decoding Mode          : Nucleus Sampling" in sampled.stdout

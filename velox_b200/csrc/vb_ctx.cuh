@@ -102,6 +102,18 @@ struct vb_ctx {
     float* cand_v = nullptr;
     uint32_t* cand_i = nullptr;
 
+    // sampler: temperature <= 1e-5 or top_p <= 0 means greedy (the reference's rule, src/runtime.rs:1100)
+    float sample_temperature = 0.0f, sample_top_p = 0.0f;
+    int sample_mode = 0;
+    uint64_t sample_seed = 0;
+    float* sample_probs = nullptr;  // [max_batch][vocab] scratch of the sampling kernel
+
+    // speculative verify pass (vb_spec.cu): logits / argmax candidates of up to 8 rows, candidate and winner tokens
+    float* spec_logits = nullptr;
+    float* spec_cand_v = nullptr;
+    uint32_t* spec_cand_i = nullptr;
+    uint32_t* spec_tokens = nullptr;
+
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     uint64_t graph_nodes = 0;
@@ -126,11 +138,22 @@ struct StepIO {
     bool causal_chunk = false;  // rows are consecutive positions of one sequence (prefill chunk), not one row per slot
 };
 
+template <typename T>
+inline int32_t dev_alloc(T** p, uint64_t n_elems) {
+    cudaError_t e = cudaMalloc((void**)p, (n_elems ? n_elems : 1) * sizeof(T));
+    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc", __FILE__, __LINE__); return VB_ERR_OOM; }
+    return VB_OK;
+}
+
 LaunchCfg lcfg(vb_ctx* c, bool pdl);
 StepIO decode_io(vb_ctx* c);
 // The launch sequence of one token for every active row of `state` (with_head: final norm, lm_head and sampler too).
 cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepIO& io);
 int32_t check_ready(vb_ctx* c, const char* who);
+// [rows][cols] of this rank's shard of a role, and its storage format (false: the model has no such tensor)
+bool role_shape(const vb_ctx* c, int role, uint32_t* rows, uint32_t* cols, int32_t* fmt);
+// vb_gguf.cu
+cudaError_t unpack_gguf(const LaunchCfg& lc, void* words, void* scale_min, const void* src, int ggml_type, uint64_t n_blocks);
 // Makes the chunk buffers (pfc_*) hold at least `rows` rows.
 int32_t ensure_chunk_buffers(vb_ctx* c, uint32_t rows);
 

@@ -191,12 +191,6 @@ int32_t plan_arena(vb_ctx* c) {
     return VB_OK;
 }
 
-template <typename T>
-int32_t dev_alloc(T** p, uint64_t n_elems) {
-    cudaError_t e = cudaMalloc((void**)p, (n_elems ? n_elems : 1) * sizeof(T));
-    if (e != cudaSuccess) { cuda_fail(e, "cudaMalloc", __FILE__, __LINE__); return VB_ERR_OOM; }
-    return VB_OK;
-}
 
 LaunchCfg lcfg(vb_ctx* c, bool pdl) {
     LaunchCfg lc;
@@ -435,7 +429,10 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         h.trace = next_trace(); h.max_ring = c->head_ring;
         if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes, true));
         else VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
-        if (!tp) {
+        if (!tp && c->sample_probs && c->sample_temperature > 1e-5f && c->sample_top_p > 0.0f && io.logits == c->logits) {
+            VB_TRY(sample_top_p(lcfg(c, true), nullptr, io.logits, c->sample_probs, c->vocab, B, c->sample_temperature, c->sample_top_p,
+                                c->sample_mode, nullptr, 0.0f, 1, c->sample_seed, state, c->ring_dev, RING_SLOTS));
+        } else if (!tp) {
             VB_TRY(argmax(lcfg(c, true), nullptr, io.logits, c->vocab, B, c->cand_v, c->cand_i, state, c->ring_dev, RING_SLOTS));
         } else {
             // vocab-parallel head: best (value, global index) per rank, gathered, same tie rule over the ranks
@@ -616,7 +613,8 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
-                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool};
+                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool, c->sample_probs,
+                     c->spec_logits, c->spec_cand_v, c->spec_cand_i, c->spec_tokens};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -1132,6 +1130,22 @@ int32_t vb_step_bytes(vb_ctx* c, uint64_t* weight_bytes, uint64_t* kv_bytes) {
     wb += n_active * wmat_data_bytes((int32_t)c->d.embed_fmt, 1, c->d.d_model);
     if (weight_bytes) *weight_bytes = wb;
     if (kv_bytes) *kv_bytes = kb;
+    return VB_OK;
+}
+
+int32_t vb_set_sampling(vb_ctx* c, float temperature, float top_p, uint64_t seed, int32_t mode) {
+    VB_REQUIRE(c != nullptr, "vb_set_sampling: null context");
+    VB_REQUIRE(mode == 0 || mode == 1, "vb_set_sampling: mode %d (0: runtime rule, 1: emitted C99 rule)", mode);
+    VB_REQUIRE(temperature == temperature && top_p == top_p, "vb_set_sampling: NaN parameter");
+    const bool on = temperature > 1e-5f && top_p > 0.0f;
+    if (on && c->d.tp_size > 1) { set_error("vb_set_sampling: a sharded context holds a slice of the logits; sampling runs unsharded"); return VB_ERR_UNSUPPORTED; }
+    VB_CUDA(cudaSetDevice(c->device));
+    if (on && !c->sample_probs) {
+        int32_t rc = dev_alloc(&c->sample_probs, (uint64_t)c->d.max_batch * c->vocab);
+        if (rc != VB_OK) return rc;
+    }
+    if (c->graph_exec) { cudaGraphExecDestroy(c->graph_exec); c->graph_exec = nullptr; }  // the sampler is part of the captured step
+    c->sample_temperature = temperature; c->sample_top_p = top_p; c->sample_seed = seed; c->sample_mode = mode;
     return VB_OK;
 }
 

@@ -42,7 +42,10 @@
 namespace vb {
 
 constexpr int IM_WARPS = 8;                              // warps that share one 16-row tile (they split its K extent)
-constexpr int IM_GROUPS = 2;                             // tile groups per block: they share the staged x, nothing else
+// tile groups per block: they share the staged x, nothing else.  (Measured and dropped: 4 groups = 32 warps at 64
+// registers, +4 % step time; a 64-register block of 16 warps that takes half an SM so that the next kernel's block
+// moves in early: gaps between kernels shrink to ~0.6 us but the two-slot ring that fits streams at 3.9 TB/s, +28 %.)
+constexpr int IM_GROUPS = 2;
 constexpr int IM_CONSUMERS = IM_GROUPS * IM_WARPS * 32;  // threads per block
 constexpr int IM_BLK_BYTES = 1152;     // int4: 16 rows x 128 columns of nibbles + the block's 64 fp16 scales
 constexpr int IM_BLK_BYTES_I8 = 2048;  // int8 per-channel: 16 rows x 128 columns of bytes (row scales live apart)
@@ -140,9 +143,9 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 struct BlockCursor {
     uint32_t tile, kk;
     __device__ __forceinline__ bool valid(uint32_t n_tiles) const { return tile < n_tiles; }
-    __device__ __forceinline__ void advance(uint32_t KT, uint32_t warp) {
+    __device__ __forceinline__ void advance(uint32_t KT, uint32_t warp, uint32_t tile_stride) {
         kk += IM_WARPS;
-        if (kk >= KT) { kk = warp; tile += IM_GROUPS * gridDim.x; }
+        if (kk >= KT) { kk = warp; tile += tile_stride; }
     }
 };
 
@@ -206,18 +209,23 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     pdl_launch_dependents();
 
     // ---- prologue: weights do not depend on the previous kernel; fill the ring before waiting for x ----------
-    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(ring + (size_t)wid * NS * BLK);
+    const unsigned char* my_ring_ptr = ring + (size_t)wid * NS * BLK;
+    const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(my_ring_ptr);
     BlockCursor icur{vtile0, warp};  // next block to request
-    uint32_t issued = 0;
+    uint32_t islot = 0;              // byte offset of the ring slot the next request fills (wraps at NS slots)
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
 #pragma unroll
     for (int i = 0; i < NS - 1; ++i) {
-        if (icur.valid(n_tiles)) { issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
+        if (icur.valid(n_tiles)) {
+            issue_block<W>(a.w, KT, icur, my_ring + islot, lane);
+            icur.advance(KT, warp, vstride);
+            islot = islot + BLK == NS * BLK ? 0u : islot + BLK;
+        }
         cp_async_commit();
     }
 
     // Norm weights are parameters too: the 16-bit ones of a row that fits in registers are fetched now.
-    constexpr int XC = 4;  // chunks of 8 elements a thread holds at once
+    constexpr int XC = 4;  // chunks of 8 elements a thread holds at once (rows of up to 16384 elements in one trip)
     const uint32_t n_chunks = K / 8;
     const bool in_regs = n_chunks <= (uint32_t)XC * IM_CONSUMERS;  // rows of up to 16384 elements: one trip through registers
     const bool nw_pre = a.norm_w && in_regs && (a.norm_fmt == VB_FMT_F16 || a.norm_fmt == VB_FMT_BF16);
@@ -231,11 +239,14 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     // ---- x: only now wait for the producer kernel ----------------------------------------------------------------
     pdl_wait();
     trace_mark(a.trace, 1);
-    bool act[NB];  // an inactive row still drains the pipeline, skipping x
+    // An inactive row still drains the pipeline; its x is loaded all the same (the buffer always exists), so that the
+    // activity flags and x travel together instead of one memory trip after the other.
+    bool act[NB], row_live[NB];
     bool active = false;
 #pragma unroll
     for (int r = 0; r < NB; ++r) {
-        act[r] = (NB == 1 || (uint32_t)r < a.nb_rows) && (!a.state || a.state[r].active);
+        row_live[r] = NB == 1 || (uint32_t)r < a.nb_rows;
+        act[r] = row_live[r] && (!a.state || a.state[r].active);
         active = active || act[r];
     }
     // the step's exchange counter (advanced once at the start of the step), for the sequence tags of pushed rows
@@ -257,7 +268,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                 const int row = i / PRS;
                 const uint32_t c = threadIdx.x + (i % PRS) * IM_CONSUMERS;
                 float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-                if (act[row] && c < n_chunks) {
+                if (row_live[row] && c < n_chunks) {
                     const float* x = a.x + (size_t)row * K + c * 8;
                     v0 = *reinterpret_cast<const float4*>(x); v1 = *reinterpret_cast<const float4*>(x + 4);
                 }
@@ -327,16 +338,16 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         const float* x = a.x + (size_t)row * K;
         unsigned char* xq_r = xq + (size_t)row * xrow;
         int2* sxp_r = sxp + (size_t)row * srow;
-        bool active_r = act[0];
+        bool active_r = act[0], live_r = row_live[0];
 #pragma unroll
-        for (int r = 1; r < NB; ++r) if (r == row) active_r = act[r];
+        for (int r = 1; r < NB; ++r) if (r == row) { active_r = act[r]; live_r = row_live[r]; }
         float xr[XC][8];
         auto load_batch = [&](uint32_t it0) {
 #pragma unroll
             for (int i = 0; i < XC; ++i) {
                 const uint32_t c = threadIdx.x + (it0 + i) * IM_CONSUMERS;
                 float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
-                if (active_r && c < n_chunks) { v0 = *reinterpret_cast<const float4*>(x + c * 8); v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4); }
+                if (live_r && c < n_chunks) { v0 = *reinterpret_cast<const float4*>(x + c * 8); v1 = *reinterpret_cast<const float4*>(x + c * 8 + 4); }
                 xr[i][0] = v0.x; xr[i][1] = v0.y; xr[i][2] = v0.z; xr[i][3] = v0.w;
                 xr[i][4] = v1.x; xr[i][5] = v1.y; xr[i][6] = v1.z; xr[i][7] = v1.w;
             }
@@ -397,7 +408,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     }
 
     // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
-    uint32_t parity = 0, consumed = 0;
+    uint32_t parity = 0, cslot = 0;  // cslot: byte offset of the ring slot read next
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     // single row: column g of B is (group gj of a block, plane); multi-row: (row gj of x, plane) of one group at a time
     const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)(gj % NB) * xrow + plane * 32 + 8 * t;
@@ -424,14 +435,18 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
             }
         }
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
-        for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
+        for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, cslot = cslot + BLK == NS * BLK ? 0u : cslot + BLK) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
-            if (icur.valid(n_tiles)) { issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane); icur.advance(KT, warp); ++issued; }
+            if (icur.valid(n_tiles)) {
+                issue_block<W>(a.w, KT, icur, my_ring + islot, lane);
+                icur.advance(KT, warp, vstride);
+                islot = islot + BLK == NS * BLK ? 0u : islot + BLK;
+            }
             cp_async_commit();
             cp_async_wait<NS - 1>();
             __syncwarp();
             if (active) {
-                const unsigned char* blk = ring + ((size_t)wid * NS + consumed % NS) * BLK;
+                const unsigned char* blk = my_ring_ptr + cslot;
                 if constexpr (NB > 1) {
 #pragma unroll
                     for (int sub = 0; sub < SUB; ++sub) {
@@ -657,16 +672,12 @@ constexpr int IM_NB2 = 2;  // ... and for rows of x too long for four of them to
 template <int W>
 static cudaError_t imma_opt_in() {
     cudaError_t e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<8, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<2, W, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<4, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    if ((e = cudaFuncSetAttribute(k_gemv_q4_imma<3, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_gemv_q4_imma<2, W, IM_NB2>, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM);
+#define VB_OPT_IN(...) if ((e = cudaFuncSetAttribute(__VA_ARGS__, cudaFuncAttributeMaxDynamicSharedMemorySize, IM_MAX_SMEM)) != cudaSuccess) return e
+    VB_OPT_IN(k_gemv_q4_imma<8, W, 1>); VB_OPT_IN(k_gemv_q4_imma<4, W, 1>); VB_OPT_IN(k_gemv_q4_imma<3, W, 1>); VB_OPT_IN(k_gemv_q4_imma<2, W, 1>);
+    VB_OPT_IN(k_gemv_q4_imma<4, W, IM_NB>); VB_OPT_IN(k_gemv_q4_imma<3, W, IM_NB>); VB_OPT_IN(k_gemv_q4_imma<2, W, IM_NB>);
+    VB_OPT_IN(k_gemv_q4_imma<4, W, IM_NB2>); VB_OPT_IN(k_gemv_q4_imma<3, W, IM_NB2>); VB_OPT_IN(k_gemv_q4_imma<2, W, IM_NB2>);
+#undef VB_OPT_IN
+    return cudaSuccess;
 }
 cudaError_t gemv_imma_init() {
     cudaError_t e = imma_opt_in<IM_Q4>();

@@ -29,6 +29,12 @@ cudaError_t argmax(const LaunchCfg& lc, uint32_t* out_token, const float* logits
                    uint32_t* cand_i, SeqState* state, uint32_t* ring, uint32_t ring_slots);
 uint32_t argmax_chunks(uint32_t n);
 
+// vb_sample.cu: temperature + nucleus sampling, one block per sequence; `probs` = [batch][n] scratch.  The coin of a
+// sequence comes from `coins[b]`, else (use_seed) from (seed, b, state[b].pos), else it is `coin`.
+cudaError_t sample_top_p(const LaunchCfg& lc, uint32_t* out_token, const float* logits, float* probs, uint32_t n, uint32_t batch,
+                         float temperature, float top_p, int mode, const float* coins, float coin, int use_seed, uint64_t seed,
+                         SeqState* state, uint32_t* ring, uint32_t ring_slots);
+
 // Peer-mapped receive regions of a tensor-parallel group (vb_tp.cu): base[r] is rank r's region as mapped here.
 struct TpLinks {
     unsigned char* base[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};

@@ -207,6 +207,16 @@ class Engine:
             self.decode(n_new - 1)
         return self.read_tokens(slot, n - 1, n_new)
 
+    def generate_speculative(self, prompt, n_new: int, max_draft_len: int = 3, ema_floor: float = 0.20, slot: int = 0):
+        """Prompt-lookup speculative decoding (velox_cuda_runner_k2.cu:2127-2311): (tokens, stats)."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.uint32)
+        self.reserve(slot, len(prompt) + n_new + max_draft_len)
+        out = np.zeros(n_new, dtype=np.uint32)
+        st = L.SpecStats()
+        L.check(self._lib.vb_generate_speculative(self.h, slot, _ptr(prompt), len(prompt), n_new, max_draft_len, ema_floor,
+                                                  _ptr(out), C.byref(st)))
+        return out, st
+
     def read_tokens(self, slot: int, first_pos: int, n: int) -> np.ndarray:
         out = np.empty(n, dtype=np.uint32)
         L.check(self._lib.vb_read_tokens(self.h, slot, first_pos, n, _ptr(out)))
@@ -235,6 +245,10 @@ class Engine:
         w, k = C.c_uint64(), C.c_uint64()
         L.check(self._lib.vb_step_bytes(self.h, C.byref(w), C.byref(k)))
         return w.value, k.value
+
+    def set_sampling(self, temperature: float, top_p: float, seed: int = 0, mode: int = 0):
+        """Sampler of the following decode steps (0 / 0 = greedy); coins come from (seed, slot, position)."""
+        L.check(self._lib.vb_set_sampling(self.h, float(temperature), float(top_p), int(seed), int(mode)))
 
     def set_option(self, name: str, value: int):
         L.check(self._lib.vb_set_option(self.h, name.encode(), int(value)))

@@ -20,6 +20,7 @@ FMT_F32, FMT_F16, FMT_BF16, FMT_Q4G32, FMT_Q4G64REF, FMT_I8PC = range(6)
 LOC_HOST, LOC_DEVICE = 0, 1
 ATTN_GQA, ATTN_MLA_REF = 0, 1
 FLAG_LEAN_WEIGHTS = 1
+GGML_F32, GGML_F16, GGML_Q4_K, GGML_Q6_K = 0, 1, 12, 14
 
 
 class VeloxError(RuntimeError):
@@ -40,6 +41,11 @@ class ModelDesc(C.Structure):
     )
 
 
+class SpecStats(C.Structure):
+    _fields_ = [("steps", C.c_uint64), ("plain_steps", C.c_uint64), ("drafted", C.c_uint64), ("accepted", C.c_uint64),
+                ("ema_final", C.c_float), ("ladder_final", C.c_uint32)]
+
+
 # name -> (restype, argtypes); the list mirrors include/velox_b200.h one to one
 _vp, _u32, _i32, _u64, _f32 = C.c_void_p, C.c_uint32, C.c_int32, C.c_uint64, C.c_float
 SIGNATURES = {
@@ -53,6 +59,8 @@ SIGNATURES = {
     "vb_load_tensor_synthetic": (_i32, [_vp, _i32, _i32, _u64, _u64, _f32, _f32, _u64, _u64]),
     "vb_export_tensor": (_i32, [_vp, _i32, _i32, _vp, _u64, _vp, _u64]),
     "vb_weight_bytes": (_i32, [_vp, C.POINTER(_u64)]),
+    "vb_gguf_tensor_bytes": (_u64, [_i32, _u64]),
+    "vb_load_tensor_gguf": (_i32, [_vp, _i32, _i32, _vp, _i32, _u64, _u64]),
     "vb_seq_reserve": (_i32, [_vp, _i32, _u32]),
     "vb_seq_release": (_i32, [_vp, _i32]),
     "vb_seq_set": (_i32, [_vp, _i32, _u32, _u32, _u32]),
@@ -60,6 +68,7 @@ SIGNATURES = {
     "vb_decode_step": (_i32, [_vp]),
     "vb_decode_graph_build": (_i32, [_vp]),
     "vb_decode_run": (_i32, [_vp, _u32, C.POINTER(_f32)]),
+    "vb_generate_speculative": (_i32, [_vp, _i32, _vp, _u32, _u32, _u32, _f32, _vp, _vp]),
     "vb_sync": (_i32, [_vp]),
     "vb_read_tokens": (_i32, [_vp, _i32, _u32, _u32, _vp]),
     "vb_read_logits": (_i32, [_vp, _i32, _vp, _u64]),
@@ -69,6 +78,7 @@ SIGNATURES = {
     "vb_launch_count": (_i32, [_vp, C.POINTER(_u64)]),
     "vb_step_bytes": (_i32, [_vp, C.POINTER(_u64), C.POINTER(_u64)]),
     "vb_set_option": (_i32, [_vp, C.c_char_p, C.c_int64]),
+    "vb_set_sampling": (_i32, [_vp, _f32, _f32, _u64, _i32]),
     "vb_trace_read": (_i32, [_vp, _vp, _u32, C.POINTER(_u32)]),
     "vb_tp_unique_id": (_i32, [_vp]),
     "vb_tp_init": (_i32, [_vp, _vp]),
@@ -83,10 +93,12 @@ SIGNATURES = {
     "vb_op_rope": (_i32, [_vp, _u32, _u32, _u32, _f32, _vp]),
     "vb_op_gqa_attention": (_i32, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp, _u64, _vp]),
     "vb_op_sample_argmax": (_i32, [_vp, _vp, _u32, _vp, _u64, _vp]),
+    "vb_op_sample_top_p": (_i32, [_vp, _vp, _u32, _f32, _f32, _f32, _i32, _vp, _u64, _vp]),
     "vb_op_sample_argmax_static": (_i32, [_vp, _vp, _u32, _vp]),
     "vb_op_mla_absorbed": (_i32, [_vp] * 7 + [_u32] * 4 + [_f32, _vp, _u64, _vp]),
     "vb_op_quantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
     "vb_op_dequantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
+    "vb_op_unpack_gguf": (_i32, [_vp, _vp, _vp, _i32, _u64, _vp]),
     "vb_op_fill_normal": (_i32, [_vp, _u64, _u64, _u64, _f32, _f32, _vp]),
     "vb_op_scratch_bytes": (_u64, [_u32, _u32, _u32, _u32]),
     "vb_dev_alloc": (_i32, [C.POINTER(_vp), _u64]),

@@ -27,6 +27,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-72b"])
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     args = ap.parse_args()
     base = LLAMA3_8B_INT4 if args.model == "llama3-8b" else QWEN2_72B_INT4
     spec = base.scaled(name="trace", n_layers=args.layers)
@@ -43,6 +44,9 @@ def main():
     if dist is not None:
         dist.barrier()
     eng.set_option("trace", 1)
+    for kv in args.set:
+        name, _, val = kv.partition("=")
+        eng.set_option(name, int(val))
     rng = np.random.default_rng(PROMPT_STREAM)
     prompt = rng.integers(0, spec.vocab, args.prompt_len, dtype=np.uint32)
     eng.reserve(0, args.prompt_len + 64)
