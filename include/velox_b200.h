@@ -291,11 +291,62 @@ int32_t vb_op_sample_top_p(uint32_t* out_token, const float* logits, uint32_t n,
  * share the one array: calls that may overlap on the GPU (different streams) race and must be serialised by
  * the caller.  Nothing in the array has to start at zero -- every slot read was written by the same call. */
 int32_t vb_op_sample_argmax_static(uint32_t* out_token, const float* logits, uint32_t n, void* stream);
+/* A weight matrix in caller-owned device memory: canonical layout of `fmt` (see vb_load_tensor_packed), [out][in]. */
+typedef struct vb_weight {
+    const void* data;
+    const void* scales;  /* NULL for F32 / F16 / BF16 */
+    int32_t     fmt;     /* VB_FMT_* */
+} vb_weight;
+/* Scratch (device bytes, 16-byte aligned) the fused ops below want for a layer shape. */
+uint64_t vb_op_fused_scratch_bytes(uint32_t d_model, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, uint32_t ffn_dim, uint32_t max_seq);
+/* FusedNormQkvRopeAttn (src/ir.rs:232-248; emitted src/codegen.rs:1757, C99 twin src/runners/tinystories_smollm.c:277-311):
+ * dst_attn[n_q*D] = GQA attention of rope(rmsnorm(x).Wq^T + b_q) over the layer's fp32 cache after K = rope(x'.Wk^T + b_k)
+ * and V = x'.Wv^T + b_v were written to row `step` of k_layer / v_layer ([max_seq][n_kv*D] each, the reference's
+ * contiguous layout; rows >= max_seq clamp to the last, its safe_step).  Biases are fp32 or NULL, w_norm fp32.
+ * step_dev != NULL: the position is read from that device word instead of `step`, so a captured graph of this call
+ * serves every position (what the reference gets from VeloxDecodeState). */
+int32_t vb_op_fused_norm_qkv_rope_attn(float* dst_attn, const float* input_hidden, const float* w_norm, const vb_weight* w_q,
+                                       const vb_weight* w_k, const vb_weight* w_v, const float* b_q, const float* b_k, const float* b_v,
+                                       float* k_layer, float* v_layer, uint32_t max_seq, uint32_t step, const uint32_t* step_dev,
+                                       uint32_t d_model, uint32_t n_q, uint32_t n_kv, uint32_t head_dim, float eps, float theta,
+                                       void* scratch, uint64_t scratch_bytes, void* stream);
+/* FusedOutProjResSwiGluRes (src/ir.rs:249-272; emitted src/codegen.rs:1912, C99 twin tinystories_smollm.c:314-344):
+ * mid = attn_in.Wo^T + residual_in; dst_hidden = mid + (silu(n.Wg^T) * (n.Wu^T)).Wd^T with n = rmsnorm(mid, w_post_norm).
+ * dst_hidden may alias residual_in. */
+int32_t vb_op_fused_outproj_res_swiglu_res(float* dst_hidden, const float* attn_in, const float* residual_in, const vb_weight* w_out,
+                                           const float* w_post_norm, const vb_weight* w_gate, const vb_weight* w_up, const vb_weight* w_down,
+                                           uint32_t d_model, uint32_t attn_dim, uint32_t ffn_dim, float eps, void* scratch,
+                                           uint64_t scratch_bytes, void* stream);
+/* KVWrite (src/ir.rs:83): k / v [kv_dim] into row `step` (or *step_dev) of the layer's fp32 cache. */
+int32_t vb_op_kv_write(float* k_layer, float* v_layer, const float* k, const float* v, uint32_t step, const uint32_t* step_dev,
+                       uint32_t kv_dim, uint32_t max_seq, void* stream);
+/* SwiGlu (src/ir.rs:158; src/runtime.rs:1048-1073 without the residual): dst[d] = (silu(x.Wg^T) * (x.Wu^T)).Wd^T.
+ * scratch: ffn_dim floats. */
+int32_t vb_op_swiglu(float* dst, const float* input, const vb_weight* w_gate, const vb_weight* w_up, const vb_weight* w_down,
+                     uint32_t d_model, uint32_t ffn_dim, void* scratch, uint64_t scratch_bytes, void* stream);
 /* FusedMlaAbsorbedAttn (src/runtime.rs:944-1044): one layer's latent pool [max_seq][latent], fp32. */
 int32_t vb_op_mla_absorbed(float* dst, const float* x, const float* w_norm, const float* w_dkv,
                            const float* w_absq, const float* w_abso, float* latent_pool, uint32_t step,
                            uint32_t hidden, uint32_t latent, uint32_t max_seq, float eps,
                            void* scratch, uint64_t scratch_bytes, void* stream);
+/* Multi-head latent attention decode in the weight-absorbed form, the attention core of the DeepSeek-V3-style stack the
+ * reference's model file declares (examples/deepseek_v3_mla.vlx:18-45; decode scope :117-150 `mla_decode_absorbed`); the
+ * reference's runtime implements only the single-head block above.  For sequence b and head h:
+ *   out[b][h][:512] = sum_t softmax_t(scale * q[b][h][:576] . cache[b][t][:576]) * cache[b][t][:512],  t < ctx_len[b]
+ * q fp32 [batch][n_heads][576] = [q_nope . W_uk (512) | q_rope (64)]; latent_cache bf16 [batch][cache_stride_rows][576] =
+ * [c_kv | k_rope] per token; ctx_len on the device (a captured graph serves growing contexts).  Products run in bf16 on
+ * the tensor cores with fp32 accumulation; the context is cut into slices of split_tokens rows (0 = 1024) merged by a
+ * second kernel.  scratch: vb_op_mla_decode_scratch_bytes, 16-byte aligned. */
+uint64_t vb_op_mla_decode_scratch_bytes(uint32_t batch, uint32_t n_heads, uint32_t max_ctx, uint32_t split_tokens);
+int32_t vb_op_mla_decode(float* out, const float* q, const void* latent_cache, const uint32_t* ctx_len, uint32_t batch, uint32_t n_heads,
+                         uint32_t max_ctx, uint64_t cache_stride_rows, float scale, uint32_t split_tokens, void* scratch, uint64_t scratch_bytes,
+                         void* stream);
+/* LatentKVAppend (src/ir.rs:90, `kv_latent.append_latent`): cache[b][pos[b]][:] = bf16(rows[b][:576]). */
+int32_t vb_op_mla_latent_append(void* latent_cache, const float* rows, const uint32_t* pos, uint32_t batch, uint64_t cache_stride_rows, void* stream);
+/* The per-head products of the absorbed form: dst[b][h][:n_out] = src[b][h][:n_in] . W_h, W bf16 [n_heads][..][..] with
+ * W_h stored [n_out][n_in] (w_rows_are_out = 1: ctx . W_uv_h^T) or [n_in][n_out] (0: q_nope . W_uk_h). */
+int32_t vb_op_mla_head_product(float* dst, const float* src, const void* w_bf16, uint32_t n_heads, uint32_t n_in, uint32_t n_out, uint32_t batch,
+                               int32_t w_rows_are_out, void* stream);
 /* Load-time conversions (velox_cuda_quantize_q4_group64_kernel, src/codegen.rs:2337-2369, and the
  * symmetric formats).  `src` fp32 [rows][cols] on the device. */
 int32_t vb_op_quantize(void* data, void* scales, const float* src, int32_t fmt, uint64_t rows, uint64_t cols, void* stream);

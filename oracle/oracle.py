@@ -35,6 +35,12 @@ def _stale(target: str) -> bool:
     return any(os.path.getmtime(os.path.join(_HERE, f)) > t for f in os.listdir(_HERE) if f.endswith((".c", ".h")))
 
 
+class MlaBlock(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("d_model", "n_heads", "q_lora", "kv_lora", "nope_dim", "rope_dim", "v_dim")] + \
+               [("eps", C.c_float), ("theta", C.c_float)] + \
+               [(n, C.c_void_p) for n in ("w_norm", "w_dq", "w_uq", "w_qr", "w_dkv", "w_kr", "w_uk", "w_uv", "w_o")]
+
+
 class SpecStats(C.Structure):
     _fields_ = [("steps", C.c_uint64), ("plain_steps", C.c_uint64), ("drafted", C.c_uint64), ("accepted", C.c_uint64),
                 ("ema_final", C.c_float), ("ladder_final", C.c_uint32)]
@@ -104,6 +110,9 @@ def lib() -> C.CDLL:
         L.vo_engine_generate_speculative.restype = C.c_size_t
         L.vo_engine_generate_speculative.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_int, C.c_float,
                                                      C.c_void_p, C.POINTER(SpecStats)]
+        L.vo_mla_step_absorbed.argtypes = [C.POINTER(MlaBlock), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
+        L.vo_mla_step_explicit.argtypes = [C.POINTER(MlaBlock), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_int]
+        L.vo_mla_core.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t, C.c_float]
         L.vo_unpack_q4_k.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
         L.vo_unpack_q6_k.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
         L.vo_set_num_threads.argtypes = [C.c_int]
@@ -298,3 +307,54 @@ def unpack_gguf(blocks: np.ndarray, ggml_type: int):
     sm = np.empty((n * 4, 2), dtype=np.uint16)
     (lib().vo_unpack_q4_k if ggml_type == 12 else lib().vo_unpack_q6_k)(_p(words), _p(sm), _p(blocks), n)
     return words, sm
+
+
+def bf16_round(a: np.ndarray) -> np.ndarray:
+    """fp32 values rounded to bfloat16 (nearest even) and widened again."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32).reshape(np.shape(a))
+
+
+def to_bf16_bits(a: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16).reshape(np.shape(a))
+
+
+class MlaBlockWeights:
+    """One multi-head latent attention block (examples/deepseek_v3_mla.vlx:18-45) with weights rounded to bf16."""
+
+    NAMES = ("w_norm", "w_dq", "w_uq", "w_qr", "w_dkv", "w_kr", "w_uk", "w_uv", "w_o")
+
+    def __init__(self, rng, d_model, n_heads, q_lora, kv_lora=512, nope_dim=128, rope_dim=64, v_dim=128, eps=1e-6, theta=10000.0, std=0.02):
+        self.dims = dict(d_model=d_model, n_heads=n_heads, q_lora=q_lora, kv_lora=kv_lora, nope_dim=nope_dim, rope_dim=rope_dim, v_dim=v_dim)
+        H = n_heads
+        shapes = {"w_norm": (d_model,), "w_dq": (q_lora, d_model), "w_uq": (H * nope_dim, q_lora), "w_qr": (H * rope_dim, q_lora),
+                  "w_dkv": (kv_lora, d_model), "w_kr": (rope_dim, d_model), "w_uk": (H * nope_dim, kv_lora), "w_uv": (H * v_dim, kv_lora),
+                  "w_o": (d_model, H * v_dim)}
+        self.w = {}
+        for n in self.NAMES:
+            base = 1.0 if n == "w_norm" else 0.0
+            self.w[n] = bf16_round((base + std * rng.standard_normal(shapes[n])).astype(np.float32))
+        self.c = MlaBlock(eps=eps, theta=theta, **self.dims)
+        for n in self.NAMES:
+            setattr(self.c, n, self.w[n].ctypes.data)
+
+    def step(self, x, cache, pos, absorbed=True, cache_bf16=False):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        dst = np.empty_like(x)
+        H, W = self.dims["n_heads"], self.dims["kv_lora"] + self.dims["rope_dim"]
+        if absorbed:
+            q_cat, ctx = np.empty((H, W), np.float32), np.empty((H, self.dims["kv_lora"]), np.float32)
+            lib().vo_mla_step_absorbed(C.byref(self.c), _p(dst), _p(x), _p(cache), pos, int(cache_bf16), _p(q_cat), _p(ctx))
+            return dst, q_cat, ctx
+        lib().vo_mla_step_explicit(C.byref(self.c), _p(dst), _p(x), _p(cache), pos, int(cache_bf16))
+        return dst
+
+
+def mla_core(q_cat: np.ndarray, cache_rows: np.ndarray, dc: int, scale: float) -> np.ndarray:
+    q_cat = np.ascontiguousarray(q_cat, dtype=np.float32)
+    cache_rows = np.ascontiguousarray(cache_rows, dtype=np.float32)
+    H, W = q_cat.shape
+    out = np.empty((H, dc), np.float32)
+    lib().vo_mla_core(_p(out), _p(q_cat), _p(cache_rows), H, dc, W - dc, cache_rows.shape[0], scale)
+    return out

@@ -149,6 +149,18 @@ size_t   vo_engine_generate_speculative(vo_engine* e, uint32_t seq, const uint32
 void     vo_unpack_q4_k(uint32_t* words, uint16_t* scale_min, const uint8_t* src, size_t n_blocks);
 void     vo_unpack_q6_k(uint32_t* words, uint16_t* scale_min, const uint8_t* src, size_t n_blocks);
 
+/* ---- multi-head latent attention, absorbed and explicit (velox_oracle_mla.c; parity unpinned beyond the
+ * single-head block: see that file's header) --------------------------------------------------------------------- */
+typedef struct vo_mla_block {
+    uint32_t d_model, n_heads, q_lora, kv_lora, nope_dim, rope_dim, v_dim;
+    float    eps, theta;
+    const float *w_norm, *w_dq, *w_uq, *w_qr, *w_dkv, *w_kr, *w_uk, *w_uv, *w_o;
+} vo_mla_block;
+void vo_mla_step_absorbed(const vo_mla_block* m, float* dst, const float* x, float* cache, size_t pos, int cache_bf16,
+                          float* q_cat_out, float* ctx_out);
+void vo_mla_step_explicit(const vo_mla_block* m, float* dst, const float* x, float* cache, size_t pos, int cache_bf16);
+void vo_mla_core(float* out, const float* q_cat, const float* cache, size_t n_heads, size_t dc, size_t dr, size_t n_rows, float scale);
+
 #ifdef __cplusplus
 }
 #endif

@@ -74,9 +74,9 @@ def test_speculative_argument_checks():
     eng = H.build_engine(SPEC, 8, 64, max_batch=2)
     p = H.prompt_tokens(SPEC, 8, 8)
     eng.reserve(0, 20)
-    out = np.zeros(16, dtype=np.uint32)
-    with pytest.raises(L.VeloxError) as e:     # reservation too small for prompt + new + draft rows
-        L.check(eng._lib.vb_generate_speculative(eng.h, 0, p.ctypes.data_as(L.C.c_void_p), 8, 16, 3, 0.2, out.ctypes.data_as(L.C.c_void_p), None))
+    out = np.zeros(32, dtype=np.uint32)
+    with pytest.raises(L.VeloxError) as e:     # 32 reserved tokens (two blocks) do not hold prompt + new + draft rows
+        L.check(eng._lib.vb_generate_speculative(eng.h, 0, p.ctypes.data_as(L.C.c_void_p), 8, 32, 3, 0.2, out.ctypes.data_as(L.C.c_void_p), None))
     assert e.value.code == L.ERR_INVALID
     eng.reserve(1, 32)
     eng.prefill(p, 1)

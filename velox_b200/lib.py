@@ -41,6 +41,10 @@ class ModelDesc(C.Structure):
     )
 
 
+class Weight(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("scales", C.c_void_p), ("fmt", C.c_int32)]
+
+
 class SpecStats(C.Structure):
     _fields_ = [("steps", C.c_uint64), ("plain_steps", C.c_uint64), ("drafted", C.c_uint64), ("accepted", C.c_uint64),
                 ("ema_final", C.c_float), ("ladder_final", C.c_uint32)]
@@ -95,7 +99,16 @@ SIGNATURES = {
     "vb_op_sample_argmax": (_i32, [_vp, _vp, _u32, _vp, _u64, _vp]),
     "vb_op_sample_top_p": (_i32, [_vp, _vp, _u32, _f32, _f32, _f32, _i32, _vp, _u64, _vp]),
     "vb_op_sample_argmax_static": (_i32, [_vp, _vp, _u32, _vp]),
+    "vb_op_fused_scratch_bytes": (_u64, [_u32] * 6),
+    "vb_op_fused_norm_qkv_rope_attn": (_i32, [_vp] * 11 + [_u32, _u32, _vp] + [_u32] * 4 + [_f32, _f32, _vp, _u64, _vp]),
+    "vb_op_fused_outproj_res_swiglu_res": (_i32, [_vp] * 8 + [_u32] * 3 + [_f32, _vp, _u64, _vp]),
+    "vb_op_kv_write": (_i32, [_vp] * 4 + [_u32, _vp, _u32, _u32, _vp]),
+    "vb_op_swiglu": (_i32, [_vp] * 5 + [_u32, _u32, _vp, _u64, _vp]),
     "vb_op_mla_absorbed": (_i32, [_vp] * 7 + [_u32] * 4 + [_f32, _vp, _u64, _vp]),
+    "vb_op_mla_decode_scratch_bytes": (_u64, [_u32] * 4),
+    "vb_op_mla_decode": (_i32, [_vp] * 4 + [_u32, _u32, _u32, _u64, _f32, _u32, _vp, _u64, _vp]),
+    "vb_op_mla_latent_append": (_i32, [_vp, _vp, _vp, _u32, _u64, _vp]),
+    "vb_op_mla_head_product": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp]),
     "vb_op_quantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
     "vb_op_dequantize": (_i32, [_vp, _vp, _vp, _i32, _u64, _u64, _vp]),
     "vb_op_unpack_gguf": (_i32, [_vp, _vp, _vp, _i32, _u64, _vp]),
