@@ -17,8 +17,10 @@ The same line carries two more objects:
           the unsharded model measured on rank 0's GPU in the same run, plus a parity flag (a 2-layer model of the
           same width gives the same 32 greedy tokens sharded and unsharded);
   "bs32"  at N = 1: Qwen2.5-7B-shape int8 per-channel model, 32 sequences with prompt lengths uniform in
-          [256, 2048], paged fp16 KV.
---workload NAME makes NAME the headline instead (the two extra objects are then left out).
+          [256, 2048], paged fp16 KV;
+  "mla"   at N = 1: the absorbed multi-head latent attention decode kernel on the DeepSeek-V3-style shape (128 heads,
+          latent 512 + 64, batch 64, contexts uniform in [1024, 8192]).
+--workload NAME makes NAME the headline instead (the extra objects are then left out).
 
 --impl reference times the CPU restatement of the reference runtime (oracle/, OpenMP on all host cores) on
 a bounded sample of the headline workload; rank 0 only.
@@ -444,6 +446,60 @@ def tp_object(args, R: Ranks):
     return obj
 
 
+def mla_object(R: Ranks, iters: int = 20):
+    """The absorbed multi-head latent attention decode kernel on the DeepSeek-V3-style shape of the benchmark
+    configuration: 128 heads, latent 512 + 64, batch 64, context lengths uniform in [1024, 8192], bf16 latent cache.
+    One launch = the attention of one layer for the whole batch; both bounds are reported (cache bytes against the
+    copy peak, products against the dense bf16 peak)."""
+    import ctypes as C
+    torch = R.torch
+    from velox_b200 import lib as L
+    lib = L.load()
+    B, H, W, DC, split = 64, 128, 576, 512, 1024
+    rng = np.random.default_rng(SEED)
+    lens = rng.integers(1024, 8193, size=B).astype(np.uint32)
+    max_ctx = int(lens.max())
+    dev = torch.device("cuda", R.local_rank)
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    cache = torch.randn((B, max_ctx, W), device=dev, dtype=torch.float32, generator=g).to(torch.bfloat16)
+    q = torch.randn((B, H, W), device=dev, dtype=torch.float32, generator=g)
+    out = torch.empty((B, H, DC), device=dev, dtype=torch.float32)
+    d_len = torch.from_numpy(lens.astype(np.int32)).to(dev)
+    need = lib.vb_op_mla_decode_scratch_bytes(B, H, max_ctx, split)
+    scratch = torch.empty(need, device=dev, dtype=torch.uint8)
+    stream = torch.cuda.current_stream(dev)
+    scale = 1.0 / float(np.sqrt(128 + 64))
+
+    def launch():
+        L.check(lib.vb_op_mla_decode(C.c_void_p(out.data_ptr()), C.c_void_p(q.data_ptr()), C.c_void_p(cache.data_ptr()), C.c_void_p(d_len.data_ptr()),
+                                     B, H, max_ctx, max_ctx, scale, split, C.c_void_p(scratch.data_ptr()), need, C.c_void_p(stream.cuda_stream)))
+    for _ in range(3):
+        launch()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        launch()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / iters
+    rows = int(lens.astype(np.int64).sum())
+    flops = 2.0 * rows * H * (W + DC)
+    nbytes = rows * W * 2 + q.numel() * 4 + out.numel() * 4
+    peak, kind = load_peaks()
+    try:
+        tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+    except Exception:
+        tpeak = 1590.0
+    return {"workload": "deepseek-mla-bs64", "kernel": "k_mla_decode + k_mla_merge (one layer's attention for the batch)", "batch": B, "heads": H,
+            "latent": "512 + 64 bf16", "context": "uniform in [1024, 8192], mean %d" % (rows // B), "ms_per_launch": ms, "gpu_launches": 2 * iters,
+            "l2_policy": "inputs larger than L2: %.2f GB of latent cache per launch" % (rows * W * 2 / 1e9),
+            "roofline_tensor": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s",
+                                "frac": flops / (ms * 1e-3) / 1e12 / tpeak, "flops_per_launch": flops},
+            "roofline_hbm": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
+                             "bytes_per_launch": nbytes, "peak_kind": kind}}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -495,6 +551,7 @@ def main():
         line["tp"] = tp_object(args, R)
         if world == 1:
             b = measure(args, R, BS32_WORKLOAD, args.steps, args.warmup, 0, sharded=False, with_e2e=True)
+            line["mla"] = mla_object(R)
             line["bs32"] = {"workload": BS32_WORKLOAD, "model": b["spec"].name, "batch": 32, "prompt_len": "uniform in [256, 2048]",
                             "ms_per_step": b["ms_per_step"], "tok_s": b["value"], "e2e_tok_s": b["e2e"]["value"],
                             "roofline": b["roofline"], "gpu_launches": b["launches"], "ttft_ms": b["ttft_ms"]}

@@ -205,18 +205,29 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "prefill_chunk"  prompt tokens that go through the layers together in vb_prefill (16; 1 = token by token)
  *   "prefill_gemm"   1: prompts longer than "prefill_gemm_min" (48) tokens go through the layers in chunks of up to
  *                    "prefill_rows" (2048) tokens whose products run on the tcgen05 tensor cores; 0: batched kernels
+ *   "prefill_split"  how those chunk products treat the 11 significant bits of fp16 operands: 2 (default): x and the
+ *                    weights fp16 cannot hold exactly are multiplied as hi + lo parts (3 tensor-core products, results equal
+ *                    to fp32 products to ~2^-22); 1: only x is split; 0: single fp16 operands (fastest; at 32 layers and 2048
+ *                    cached rows the rounding moves the logits by up to 2.8e-2).  Set before the first long prefill.
  *   "prefill_flash"  1: those chunks use the causal tile attention kernel (head_dim 64 or 128); 0: one row per token
  *   "prefill_two_per_sm" 1 (default): 128-row tiles run two blocks per SM with half the ring depth each
  *   "prefill_wide"   1: 256 rows of x per tensor-core tile when a chunk has more than 128 rows (default 0)
  *   "decode_gemm"    1: the products of a decode step (lm_head included) run as tensor-core GEMMs, one row of x per
  *                    slot; default 1 when max_batch >= 16 and the weights are int8 per channel or fp16, else 0
+ *   "decode_gemm_i8" 1 (default): those products over int8 per-channel weights (batches of up to 32) run on the integer
+ *                    tensor cores straight from the stored bytes (exact arithmetic, one byte per weight from HBM); 0: through
+ *                    resident fp16 copies
  *   "decode_split_k" 1 (default): decode-batch products with few 128-row tiles split K over several blocks per tile
  *                    (partials summed in a fixed order: results do not depend on scheduling)
  *   "tc_resident_gb" budget in GB for resident fp16 copies of the layer matrices used by those GEMMs (40; 0: convert
  *                    per call into the workspace)
  *   "pdl"            1: programmatic dependent launch between the kernels of a step
+ *   "attn_splits"    slices of the context per (sequence, KV head) in the decode attention (1..8; default: one per 32 tokens
+ *                    of max_seq_len up to 8, fewer when the batch alone fills the GPU)
  *   "trace"          1: device time stamps per kernel (vb_trace_read)
  *   "tp_p2p"         1: NVLink push exchange when peer regions are open, 0: NCCL
+ *   "tp_fused_push"  1: the row-parallel products send their rows to the peers from their own epilogue;
+ *   "tp_fused_reduce" 1: ... and gather the peers' copies of their own rows, so the exchange needs no kernel of its own
  *   "tp_poll_ms"     limit of one exchange poll (default ~10000)
  *   "tp_p2p_standin" diagnostic: private stand-in regions instead of peers (every exchange then runs into its
  *                    poll limit; used by the time-out test) */

@@ -182,17 +182,20 @@ def test_batched_variable_length_sequences(spec_i):
     eng.close()
 
 
-@pytest.mark.parametrize("spec_i", [2, 4, 6, 7, 10, 11])
-def test_batched_decode_on_the_tensor_core_products(spec_i):
+@pytest.mark.parametrize("spec_i,i8", [(2, 1), (4, 1), (4, 0), (6, 1), (7, 1), (9, 1), (9, 0), (10, 1), (11, 1)])
+def test_batched_decode_on_the_tensor_core_products(spec_i, i8):
     """Option decode_gemm: the decode steps of a batch (one row per slot, one slot inactive, lm_head included) run
     their products as tcgen05 GEMMs; every sequence still matches its own CPU run (int4, int8, bf16, QKV bias; the
-    long-FFN shapes split the K of the down projection over 8 blocks per tile, the others over 1 or 2)."""
+    long-FFN shapes split the K of the down projection over 8 blocks per tile, the others over 1 or 2).  int8 per-channel
+    weights take the integer tensor-core kernel that reads the stored bytes (i8 = 1) or, with decode_gemm_i8 = 0, the
+    fp16 copies."""
     spec = SMALL_SPECS[spec_i]
     seed, n_new = 33, 10
     lens = [5, 23, 16, 1, 9]
     max_seq = max(lens) + n_new + 1
     ora, _ = H.build_oracle(spec, seed, max_seq, n_seqs=len(lens))
     eng = H.build_engine(spec, seed, max_seq, max_batch=len(lens) + 1)
+    eng.set_option("decode_gemm_i8", i8)   # process-wide switch: set in every case
     eng.set_option("decode_gemm", 1)
     prompts = [H.prompt_tokens(spec, seed, n, stream=(1 << 20) + i) for i, n in enumerate(lens)]
     for i, p in enumerate(prompts):
@@ -204,6 +207,7 @@ def test_batched_decode_on_the_tensor_core_products(spec_i):
         want = ora.generate_greedy(p, n_new, seq=i)
         assert np.array_equal(eng.read_tokens(i, len(p) - 1, n_new), want), i
         assert float(np.max(np.abs(eng.logits(i) - ora.logits))) <= LOGIT_TOL
+    eng.set_option("decode_gemm_i8", 1)
     eng.close()
 
 

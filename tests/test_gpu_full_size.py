@@ -14,19 +14,31 @@ LOGIT_TOL = 2e-2  # max-abs on the logits; greedy tokens must agree for the firs
 
 
 def test_llama3_8b_int4_full_model_32_steps():
-    """Llama-3-8B shape, int4 g32, all 32 layers, vocabulary 128256: 16-token prompt + 32 greedy steps."""
+    """Llama-3-8B shape, int4 g32, all 32 layers, vocabulary 128256: a 16-token prompt and 32 greedy steps, both engines fed
+    the checker's token at every position (so that one near-tie cannot hide the steps after it): logits within the budget
+    at every position; the greedy token equal wherever the checker's own top-two margin exceeds twice the budget (seeded
+    N(0, 0.02) weights give nearly flat logits: margins below the budget do occur, and there either winner is right)."""
     spec, n_prompt, n_new = LLAMA3_8B_INT4, 16, 32
     t0 = time.time()
     ora, _ = H.build_oracle(spec, 2025, n_prompt + n_new + 1)
-    prompt = H.prompt_tokens(spec, 2025, n_prompt)
-    want = ora.generate_greedy(prompt, n_new)
     eng = H.build_engine(spec, 2025, n_prompt + n_new + 16)
-    got = eng.generate_greedy(prompt, n_new)
-    err = float(np.max(np.abs(eng.logits() - ora.logits)))
+    eng.reserve(0, n_prompt + n_new + 16)
+    prompt = H.prompt_tokens(spec, 2025, n_prompt)
+    worst, near_ties, tok = 0.0, 0, None
+    for pos in range(n_prompt + n_new):
+        t = int(prompt[pos]) if pos < n_prompt else tok
+        tok = ora.forward_step(t, pos)
+        got = eng.forward_step(t, pos)
+        lo = ora.logits
+        worst = max(worst, float(np.max(np.abs(eng.logits() - lo))))
+        if got != tok:
+            top2 = np.partition(lo, -2)[-2:]
+            assert float(top2[1] - top2[0]) < 2 * LOGIT_TOL, "position %d: token %d vs %d with a margin of %g" % (pos, got, tok, float(top2[1] - top2[0]))
+            near_ties += 1
     eng.close()
-    print("8B full depth: logits max-abs %.3g, checker %.0f s" % (err, time.time() - t0))
-    assert err <= LOGIT_TOL
-    assert np.array_equal(got, want)
+    print("8B full depth: logits max-abs %.3g over %d positions, %d near-tie(s), %.0f s" % (worst, n_prompt + n_new, near_ties, time.time() - t0))
+    assert worst <= LOGIT_TOL
+    assert near_ties <= 3
 
 
 def test_llama3_8b_long_prompt_through_the_tensor_core_prefill():

@@ -49,13 +49,16 @@ def test_matmul_rows_parity(vb, oracle, dev, fmt, shape):
     x = oracle.fill_normal(n_rows * in_dim, 15, 2, 1.0).reshape(n_rows, in_dim)
     got = run_rows(vb, dev, data, scales, c, x, in_dim, out_dim)
     scale = np.sqrt(in_dim) * 0.02
-    # 1. the kernel's own arithmetic (fp16 operands, exact products, fp32 accumulation) restated in float64
-    xh = x.astype(np.float16).astype(np.float64)
+    # 1. the kernel's own arithmetic restated in float64: decode batches (up to 32 rows) multiply single fp16 operands;
+    #    larger chunks multiply x, and weights fp16 cannot hold exactly, as fp16 hi + lo parts, i.e. the fp32 values
+    split = n_rows > 32
+    xh = (x if split else x.astype(np.float16)).astype(np.float64)
     if fmt == "i8pc":
         wh = data.astype(np.float64)
         want16 = (xh @ wh.T) * scales.view(np.float16).astype(np.float64)[None, :]
     else:
-        wh = oracle.dequantize(data, scales, c, out_dim, in_dim).astype(np.float16).astype(np.float64)
+        wd = oracle.dequantize(data, scales, c, out_dim, in_dim)
+        wh = (wd if split else wd.astype(np.float16)).astype(np.float64)
         want16 = xh @ wh.T
     assert np.max(np.abs(got - want16)) <= 1e-4 * scale + 1e-6  # fp32 accumulation in the tensor cores only
     # 2. the reference's fp32 product: the two operand roundings to fp16 (2^-11 relative each) stay far below the

@@ -132,6 +132,7 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
     return r;
 }
+__device__ __forceinline__ float half_round(float v) { return __half2float(__float2half_rn(v)); }
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     const __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
@@ -162,7 +163,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     constexpr int ROW16 = D * sizeof(KVT) / 16;               // 16-byte pieces per K or V row
     static_assert(NV <= 32 && (NV & (NV - 1)) == 0, "values per lane must be a power of two <= 32");
     __shared__ float q_s[GM][D];
-    __shared__ float sc_s[ATTN_WARPS][32];
+    __shared__ float sc_s[MMA ? 1 : ATTN_WARPS][32];   // scalar path: a warp's scores
     __shared__ float part_ml[ATTN_WARPS][GM][2];
     __shared__ float gath[GM * (D + 32)];   // partials of all splits for this block's slice of the head dimension
     __shared__ float rope_cs[D / 2], rope_sn[D / 2];
@@ -172,6 +173,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     KVT* kv_s = reinterpret_cast<KVT*>(dyn_smem);
     float* part_acc = reinterpret_cast<float*>(dyn_smem + SM::kv_bytes);  // [ATTN_WARPS][GM][D]
+    // tensor-core path: until the warps' partials are written there (after the last chunk's barrier), the same bytes hold
+    // the low halves of Q (q - fp16(q)) as B fragments, the same for every warp: [k step][lane], 16 * D bytes
+    uint2* qlo_s = reinterpret_cast<uint2*>(part_acc);
 
     trace_mark(a.trace, 0);
     pdl_launch_dependents();
@@ -394,9 +398,18 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
             for (int ks = 0; ks < MT; ++ks) {
                 const bool on = n < (uint32_t)GM;
                 const float* qrow = q_s[on ? n : 0];
-                qb[ks][0] = on ? pack_half2(qrow[ks * 16 + k0], qrow[ks * 16 + k0 + 1]) : 0u;
-                qb[ks][1] = on ? pack_half2(qrow[ks * 16 + k0 + 8], qrow[ks * 16 + k0 + 9]) : 0u;
+                const float q0 = on ? qrow[ks * 16 + k0] : 0.0f, q1 = on ? qrow[ks * 16 + k0 + 1] : 0.0f;
+                const float q8 = on ? qrow[ks * 16 + k0 + 8] : 0.0f, q9 = on ? qrow[ks * 16 + k0 + 9] : 0.0f;
+                qb[ks][0] = pack_half2(q0, q1);
+                qb[ks][1] = pack_half2(q8, q9);
+                // Q and the probabilities go through the fp16 tensor cores as a high and a low half each (two products
+                // into the same fp32 accumulators): with one half alone their 11-bit rounding, amplified over 32 layers,
+                // moved the logits as much as the fp16 cache itself does.  The low halves of Q wait in shared memory.
+                if (warp == 0)
+                    qlo_s[ks * 32 + lane] = make_uint2(pack_half2(q0 - half_round(q0), q1 - half_round(q1)),
+                                                       pack_half2(q8 - half_round(q8), q9 - half_round(q9)));
             }
+            __syncthreads();
         }
 
         // ---- the slice, CH tokens at a time through the two buffers (both were requested above) ----------------
@@ -425,7 +438,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     for (int ks = 0; ks < MT; ++ks) {
                         uint32_t af[4];
                         ldsm_x4(af, k_addr + ks * 32);
+                        const uint2 ql = qlo_s[ks * 32 + lane];
                         mma_f16_16816(sc4, af, qb[ks][0], qb[ks][1]);
+                        mma_f16_16816(sc4, af, ql.x, ql.y);
                     }
                     // this thread: tokens tA = lane / 4 and tA + 8 of the tile, heads 2 * (lane & 3) and + 1
                     const uint32_t tA = c0 + tok0 + (lane >> 2);
@@ -449,6 +464,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     // P^T as B fragments (k = token, n = head): transpose the two 8x8 halves of the score tile
                     const uint32_t pb0 = movmatrix_trans(pack_half2(p0, p1));
                     const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
+                    const uint32_t pl0 = movmatrix_trans(pack_half2(p0 - half_round(p0), p1 - half_round(p1)));
+                    const uint32_t pl1 = movmatrix_trans(pack_half2(p2 - half_round(p2), p3 - half_round(p3)));
                     const uint32_t v_addr = smem_u32(kb + ((size_t)CH + tok0 + (mi >> 1) * 8 + r8) * RS + (mi & 1) * 8);
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
@@ -456,6 +473,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                         uint32_t af[4];
                         ldsm_x4_trans(af, v_addr + mt * 32);
                         mma_f16_16816(o_t[mt], af, pb0, pb1);
+                        mma_f16_16816(o_t[mt], af, pl0, pl1);
                     }
                 }
             } else

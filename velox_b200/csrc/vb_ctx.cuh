@@ -42,6 +42,7 @@ struct vb_ctx {
     TpLinks links;                        // NVLink peer mappings (vb_tp_p2p_open); used instead of NCCL when open
     bool links_open = false, use_links = true, links_standin = false;
     bool tp_fused_push = true;            // row-parallel products send their rows to the peers from their own epilogue
+    bool tp_fused_reduce = true;          // ... and gather the peers' copies of their own rows: no exchange kernel at all
     uint32_t ring_role[4] = {0, 0, 0, 0};   // per product (qkv, o, gate/up, down): 0 = gemv_ring
     uint32_t gemv_ring = 4, head_ring = 4;  // weight ring depth of the int4 kernel for the layers / the head (GemvArgs::max_ring)
     uint32_t* err_word = nullptr;         // device word that bounded waits set when they run out
@@ -90,6 +91,8 @@ struct vb_ctx {
     uint32_t prefill_rows = 2048, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
     uint64_t tc_ws_bytes = 0;
+    void* i8_ws = nullptr;      // workspace of the int8 tensor-core products of decode batches (x planes, split-K partials)
+    uint64_t i8_ws_bytes = 0;
     // resident fp16 copies of the layer matrices for those products, made once when they fit `tc_resident_gb`
     // (HBM is plentiful: 14 GB for an 8B model); otherwise every call converts into the workspace
     void* f16_pool = nullptr;
@@ -134,6 +137,8 @@ struct StepIO {
     bool fused_append;  // false: K/V of all rows are appended by a kernel of their own before attention
     void* tc_ws = nullptr;  // != null: the layer products run as tensor-core GEMMs with this workspace
     uint64_t tc_ws_bytes = 0;
+    void* i8_ws = nullptr;  // != null: decode batches over int8 weights take the integer tensor-core kernel
+    uint64_t i8_ws_bytes = 0;
     uint32_t first = 0;     // tensor-core chunks: position of row 0 (row j is position first + j of one sequence)
     bool causal_chunk = false;  // rows are consecutive positions of one sequence (prefill chunk), not one row per slot
 };

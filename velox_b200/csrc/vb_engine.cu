@@ -271,9 +271,13 @@ int32_t ensure_f16_copies(vb_ctx* c) {
     c->f16_tried = true;
     if (c->d.weight_fmt == VB_FMT_F16 || c->tc_resident_gb == 0) return VB_OK;
     const uint64_t dm = c->d.d_model;
-    const uint64_t per_layer = ((uint64_t)c->qkv_rows * dm + dm * c->qdim + 3ull * c->ffn * dm) * 2 + 5 * 1024;
+    // weights fp16 does not hold exactly also get the part its rounding dropped (prefill chunks multiply hi + lo)
+    const bool with_lo = gemm_tc_split >= 2 && gemm_tc_weights_inexact((int32_t)c->d.weight_fmt);
+    const uint64_t per_layer = (((uint64_t)c->qkv_rows * dm + dm * c->qdim + 3ull * c->ffn * dm) * 2 + 5 * 1024) * (with_lo ? 2 : 1);
     Tensor& head = c->tensor(VB_ROLE_LM_HEAD, 0);
-    const bool with_head = c->decode_gemm && head.m.fmt != VB_FMT_F16 && head.m.data != nullptr;  // decode batches run the lm_head here too
+    // decode batches run the lm_head as a tensor-core product too: through a resident fp16 copy unless the integer kernel reads int8 directly
+    const bool with_head = c->decode_gemm && head.m.fmt != VB_FMT_F16 && head.m.data != nullptr &&
+                           !(gemm_i8_enabled && head.m.fmt == VB_FMT_I8PC && c->d.max_batch <= 32);
     const uint64_t total = per_layer * c->d.n_layers + (with_head ? (uint64_t)head.m.rows * head.m.cols * 2 + 1024 : 0);
     if (total > (uint64_t)c->tc_resident_gb << 30) return VB_OK;
     if (cudaMalloc(&c->f16_pool, total + 1024) != cudaSuccess) { cudaGetLastError(); c->f16_pool = nullptr; return VB_OK; }
@@ -284,9 +288,11 @@ int32_t ensure_f16_copies(vb_ctx* c) {
             Tensor& t = c->tensor(role, (int)l);
             WMat m = t.m;
             if (role == VB_ROLE_WQ) m.rows = c->qkv_rows;
-            VB_CUDA(weights_to_f16(lcfg(c, false), p, m));
+            const uint64_t bytes = ((uint64_t)m.rows * m.cols * 2 + 1023) / 1024 * 1024;
+            VB_CUDA(weights_to_f16(lcfg(c, false), p, m, with_lo ? p + bytes : nullptr));
             t.m.f16 = p;
-            p += ((uint64_t)m.rows * m.cols * 2 + 1023) / 1024 * 1024;
+            t.m.f16_lo = with_lo ? p + bytes : nullptr;
+            p += bytes * (with_lo ? 2 : 1);
         }
     if (with_head) {
         VB_CUDA(weights_to_f16(lcfg(c, false), p, head.m));
@@ -306,6 +312,14 @@ int32_t prepare_decode_gemm(vb_ctx* c) {
     }
     int32_t rc = ensure_f16_copies(c);
     if (rc != VB_OK) return rc;
+    if (gemm_i8_enabled && c->d.weight_fmt == VB_FMT_I8PC && c->d.max_batch <= 32 && !c->i8_ws) {
+        const uint64_t need = gemm_i8_workspace_bytes(std::max(std::max(c->d.d_model, c->ffn), c->qdim));
+        if (cudaMalloc(&c->i8_ws, need + 1024) != cudaSuccess) { cudaGetLastError(); c->i8_ws = nullptr; }
+        else {
+            c->i8_ws_bytes = need;
+            VB_CUDA(cudaMemsetAsync((void*)(((uintptr_t)c->i8_ws + 1023) & ~(uintptr_t)1023), 0, gemm_i8_workspace_zero_bytes(), c->stream));
+        }
+    }
     return ensure_tc_ws(c, std::max(c->d.max_batch, c->prefill_rows), true);
 }
 
@@ -326,7 +340,10 @@ void* tc_ws_aligned(vb_ctx* c) { return (void*)(((uintptr_t)c->tc_ws + 1023) & ~
 StepIO decode_io(vb_ctx* c) {
     StepIO io{c->hidden, c->qkv, c->q, c->attn_out, c->act, c->logits, c->block_table_dev, c->d.max_batch, true};
     // wide batches: the products (lm_head included) as tensor-core GEMMs, one row of x per slot
-    if (c->decode_gemm && c->tc_ws && c->d.tp_size <= 1) { io.tc_ws = tc_ws_aligned(c); io.tc_ws_bytes = c->tc_ws_bytes; }
+    if (c->decode_gemm && c->tc_ws && c->d.tp_size <= 1) {
+        io.tc_ws = tc_ws_aligned(c); io.tc_ws_bytes = c->tc_ws_bytes;
+        if (c->i8_ws) { io.i8_ws = (void*)(((uintptr_t)c->i8_ws + 1023) & ~(uintptr_t)1023); io.i8_ws_bytes = c->i8_ws_bytes; }
+    }
     return io;
 }
 
@@ -353,12 +370,15 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
     float* row_dst = p2p ? c->partial : io.hidden;
     if (p2p) VB_TRY(tp_epoch_advance(lcfg(c, false), c->links));
     bool pushed = false;  // set by the row-parallel product when its own epilogue sent the rows to the peers
+    bool reduced = false; // ... and when it also gathered the peers' rows and updated the residual stream itself
     auto exchange = [&](uint32_t site) -> cudaError_t {
         if (!tp) return cudaSuccess;
+        if (p2p && reduced) return cudaSuccess;
         if (p2p) return tp_reduce(lcfg(c, true), c->links, io.hidden, c->partial, B * d.d_model, site, n_sites, c->err_word, pushed, state, d.d_model);
         return nccl_allreduce_sum_f32(c->nccl, io.hidden, (size_t)B * d.d_model, c->stream) == VB_OK ? cudaSuccess : cudaErrorUnknown;
     };
     auto product = [&](const GemvArgs& ga) -> cudaError_t {
+        if (io.i8_ws && gemm_i8_supported(ga)) return gemm_i8(lcfg(c, true), ga, io.i8_ws, io.i8_ws_bytes, true);
         if (io.tc_ws) return gemm_tc(lcfg(c, true), ga, io.tc_ws, io.tc_ws_bytes, true);
         return gemv(lcfg(c, true), ga, c->gemv_path);
     };
@@ -400,8 +420,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         o.state = state; o.batch = B; o.x = io.attn_out; o.dst = row_dst; o.epilogue = row_epi;
         o.w = c->tensor(VB_ROLE_WO, L).m;
         o.trace = next_trace(); o.max_ring = c->ring_role[1] ? c->ring_role[1] : c->gemv_ring;
-        pushed = false;
-        if (p2p && c->tp_fused_push) { o.push.links = &c->links; o.push.site = 2 * l; o.push.n_sites = n_sites; o.pushed = &pushed; }
+        pushed = false; reduced = false;
+        if (p2p && c->tp_fused_push) {
+            o.push.links = &c->links; o.push.site = 2 * l; o.push.n_sites = n_sites; o.pushed = &pushed;
+            if (c->tp_fused_reduce && B == 1) { o.push.reduce_hidden = io.hidden; o.push.err = c->err_word; o.reduced = &reduced; }
+        }
         VB_TRY(product(o));
         VB_TRY(exchange(2 * l));
         // RMSNorm + gate/up + SiLU*up
@@ -416,8 +439,11 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         dn.state = state; dn.batch = B; dn.x = io.act; dn.dst = row_dst; dn.epilogue = row_epi;
         dn.w = c->tensor(VB_ROLE_WDOWN, L).m;
         dn.trace = next_trace(); dn.max_ring = c->ring_role[3] ? c->ring_role[3] : c->gemv_ring;
-        pushed = false;
-        if (p2p && c->tp_fused_push) { dn.push.links = &c->links; dn.push.site = 2 * l + 1; dn.push.n_sites = n_sites; dn.pushed = &pushed; }
+        pushed = false; reduced = false;
+        if (p2p && c->tp_fused_push) {
+            dn.push.links = &c->links; dn.push.site = 2 * l + 1; dn.push.n_sites = n_sites; dn.pushed = &pushed;
+            if (c->tp_fused_reduce && B == 1) { dn.push.reduce_hidden = io.hidden; dn.push.err = c->err_word; dn.reduced = &reduced; }
+        }
         VB_TRY(product(dn));
         VB_TRY(exchange(2 * l + 1));
     }
@@ -427,7 +453,8 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         h.norm_w = c->tensor(VB_ROLE_FINAL_NORM, 0).m.data; h.norm_fmt = c->tensor(VB_ROLE_FINAL_NORM, 0).m.fmt; h.eps = d.rms_eps;
         h.w = c->tensor(VB_ROLE_LM_HEAD, 0).m;
         h.trace = next_trace(); h.max_ring = c->head_ring;
-        if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes, true));
+        if (io.i8_ws && gemm_i8_supported(h)) VB_TRY(gemm_i8(lcfg(c, true), h, io.i8_ws, io.i8_ws_bytes, true));
+        else if (io.tc_ws && gemm_tc_supported(h)) VB_TRY(gemm_tc(lcfg(c, true), h, io.tc_ws, io.tc_ws_bytes, true));
         else VB_TRY(gemv(lcfg(c, true), h, c->gemv_path));
         if (!tp && c->sample_probs && c->sample_temperature > 1e-5f && c->sample_top_p > 0.0f && io.logits == c->logits) {
             VB_TRY(sample_top_p(lcfg(c, true), nullptr, io.logits, c->sample_probs, c->vocab, B, c->sample_temperature, c->sample_top_p,
@@ -539,6 +566,13 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     c->max_blocks = (d.max_seq_len + d.kv_block_tokens - 1) / d.kv_block_tokens;
     c->n_blocks = d.kv_blocks_total ? d.kv_blocks_total : d.max_batch * c->max_blocks;
     c->n_splits = attn_pick_splits(d.max_seq_len);
+    {
+        // wide batches already fill the SMs with (sequence, KV head) pairs: fewer, longer slices per pair then stream the
+        // cache instead of paying a block's fixed costs (table fetch, cluster merge) for every ~150 rows
+        const uint32_t g = c->hq / c->hkv, pairs = d.max_batch * c->hkv * ((g + 7) / 8);
+        const uint32_t fit = pairs ? (2u * 148u) / pairs : 8u;
+        if (c->n_splits > (fit ? fit : 1u)) c->n_splits = fit ? fit : 1u;
+    }
     c->tokens_per_split = attn_tokens_per_split(d.max_seq_len);
     c->t.resize((size_t)VB_ROLE_COUNT * d.n_layers);
     int32_t rc = VB_OK;
@@ -614,7 +648,7 @@ int32_t vb_destroy(vb_ctx* c) {
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
                      c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool, c->sample_probs,
-                     c->spec_logits, c->spec_cand_v, c->spec_cand_i, c->spec_tokens};
+                     c->spec_logits, c->spec_cand_v, c->spec_cand_i, c->spec_tokens, c->i8_ws};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
     if (c->ev0) cudaEventDestroy(c->ev0);
@@ -712,7 +746,7 @@ static int32_t mark_loaded(vb_ctx* c, int32_t role, int32_t layer, Tensor* t) {
         if (owner_role == VB_ROLE_WQ) m.rows = c->qkv_rows;
         LaunchCfg lc = lcfg(c, false);
         lc.counter = nullptr;
-        VB_CUDA(weights_to_f16(lc, const_cast<void*>(o.m.f16), m));
+        VB_CUDA(weights_to_f16(lc, const_cast<void*>(o.m.f16), m, const_cast<void*>(o.m.f16_lo)));
         VB_CUDA(cudaStreamSynchronize(c->stream));
     }
     return VB_OK;
@@ -1032,6 +1066,7 @@ static int32_t check_device_error(vb_ctx* c) {
         *reinterpret_cast<volatile uint32_t*>(w) = 0;
         // a split-K product that gave up leaves its tile counters between 0 and the split count: start them over
         if (c->tc_ws) cudaMemsetAsync(tc_ws_aligned(c), 0, gemm_tc_workspace_zero_bytes(), c->stream);
+        if (c->i8_ws) cudaMemsetAsync((void*)(((uintptr_t)c->i8_ws + 1023) & ~(uintptr_t)1023), 0, gemm_i8_workspace_zero_bytes(), c->stream);
         set_error("a bounded device-side wait expired (code 0x%x): results of the last launches are invalid", v);
         return VB_ERR_TIMEOUT;
     }
@@ -1163,9 +1198,16 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         c->decode_gemm_auto = false;
         return VB_OK;
     }
+    if (!strcmp(name, "decode_gemm_i8")) { gemm_i8_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "tc_resident_gb")) { c->tc_resident_gb = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_two_per_sm")) { gemm_tc_two_per_sm = value != 0; return VB_OK; }
     if (!strcmp(name, "decode_split_k")) { gemm_tc_split_k = value != 0; return VB_OK; }
+    if (!strcmp(name, "prefill_split")) {
+        VB_REQUIRE(value >= 0 && value <= 2, "vb_set_option: prefill_split is 0, 1 or 2");
+        VB_REQUIRE(!c->f16_tried, "vb_set_option: prefill_split must be set before the first long prefill (the resident copies are made then)");
+        gemm_tc_split = (int)value;
+        return VB_OK;
+    }
     if (!strcmp(name, "prefill_wide")) { gemm_tc_wide = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_flash")) { c->prefill_flash = value != 0; return VB_OK; }
     if (!strcmp(name, "prefill_gemm_min")) { c->prefill_gemm_min = (uint32_t)value; return VB_OK; }
@@ -1184,6 +1226,11 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         }
         return VB_OK;
     }
+    if (!strcmp(name, "attn_splits")) {
+        VB_REQUIRE(value >= 1 && value <= 8, "vb_set_option: attn_splits is 1..8 (a thread-block cluster)");
+        c->n_splits = (uint32_t)value;
+        return VB_OK;
+    }
     if (!strcmp(name, "gemv_ring")) { c->gemv_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "ring_qkv")) { c->ring_role[0] = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "ring_o")) { c->ring_role[1] = (uint32_t)value; return VB_OK; }
@@ -1192,6 +1239,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "head_ring")) { c->head_ring = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "tp_p2p")) { c->use_links = value != 0; return VB_OK; }
     if (!strcmp(name, "tp_fused_push")) { c->tp_fused_push = value != 0; return VB_OK; }
+    if (!strcmp(name, "tp_fused_reduce")) { c->tp_fused_reduce = value != 0; return VB_OK; }
     if (!strcmp(name, "tp_poll_ms")) {  // limit of one exchange poll (default ~10 s), at a nominal 2 GHz
         VB_REQUIRE(value > 0, "vb_set_option: tp_poll_ms must be positive");
         c->links.poll_clocks = (long long)value * 2000000LL;

@@ -99,15 +99,26 @@ struct GemmParams {
     // counter sums the partials in split order (the same bits whoever is last) and runs the epilogue
     float* part;          // [split][tile][BN / 32][32][128]
     uint32_t* counters;   // [tile], zero between launches (the last block puts the zero back)
+    // Operand splitting (prefill chunks): fp16 holds 11 significant bits, and over 32 layers and thousands of cached
+    // positions that rounding reaches the logits (2.8e-2 at 2048 rows of the 8B shape).  x_parts = 2: x = x_hi + x_lo,
+    // both fp16, x_lo rows lie `x_lo_row` rows below x_hi in the same tensor map; w_parts = 2: W = W_hi + W_lo likewise
+    // (second tensor maps).  The products W_hi.x_hi + W_hi.x_lo + W_lo.x_hi accumulate into the same tensor-memory
+    // columns, so the epilogue does not change; what is dropped (W_lo.x_lo) is 2^-22 of the result.
+    uint32_t x_parts, w_parts, x_lo_row;
+    uint32_t stages;      // ring depth for this operand set
 };
 
 template <bool DUAL, int BN, int PER_SM = 1>
 __global__ void __launch_bounds__(128, PER_SM)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
-          const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
-    constexpr int STAGES = stages_for(DUAL, BN, PER_SM);
+          const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wl, const __grid_constant__ CUtensorMap map_wl2,
+          const GemmParams p) {
     constexpr int W_TILES = DUAL ? 2 : 1, X_TILES = BN / 128;  // BN = 32: one box of 32 rows
-    constexpr int STAGE_BYTES = stage_bytes_for(DUAL, BN);
+    constexpr int X_BYTES = BN * BK * 2;                        // one part of the x operand of a stage
+    const int STAGES = (int)p.stages;
+    const int WP = (int)p.w_parts, XP = (int)p.x_parts;
+    const int STAGE_BYTES = W_TILES * WP * TILE_BYTES + XP * X_BYTES;  // [W hi (,W2 hi)][W lo (,W2 lo)][x hi][x lo]
+    const int X_OFF = W_TILES * WP * TILE_BYTES;
     constexpr uint32_t IDESC = idesc_for(BN);
     constexpr uint32_t TMEM_COLS = DUAL ? 2 * BN : BN;
     extern __shared__ unsigned char smem_raw[];
@@ -156,8 +167,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const int kx = (kb_first + kb) * BK;
             tma_load_2d(st, &map_w, kx, row0, full);
             if (DUAL) tma_load_2d(st + TILE_BYTES, &map_w2, kx, row0, full);
-            tma_load_2d(st + W_TILES * TILE_BYTES, &map_x, kx, tok0, full);
-            if (X_TILES == 2) tma_load_2d(st + (W_TILES + 1) * TILE_BYTES, &map_x, kx, tok0 + 128, full);  // rows 128..255: the next 16 groups of 8
+            if (WP == 2) {
+                tma_load_2d(st + W_TILES * TILE_BYTES, &map_wl, kx, row0, full);
+                if (DUAL) tma_load_2d(st + (W_TILES + 1) * TILE_BYTES, &map_wl2, kx, row0, full);
+            }
+            for (int xp = 0; xp < XP; ++xp) {
+                const int xr = tok0 + xp * (int)p.x_lo_row;
+                tma_load_2d(st + X_OFF + xp * X_BYTES, &map_x, kx, xr, full);
+                if (X_TILES == 2) tma_load_2d(st + X_OFF + xp * X_BYTES + TILE_BYTES, &map_x, kx, xr + 128, full);  // rows 128..255: the next 16 groups of 8
+            }
         }
     } else if (warp == 1 && lane == 0) {
         // ---- tensor-core issue ----
@@ -167,12 +185,19 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (!wait_or_abort(bars + s * 8, ph, abort_flag)) break;
             tc_fence_after();
             const uint32_t st = base + s * STAGE_BYTES;
-            const uint64_t da = smem_desc(st), da2 = smem_desc(st + TILE_BYTES), db = smem_desc(st + W_TILES * TILE_BYTES);
+            const uint64_t da = smem_desc(st), da2 = smem_desc(st + TILE_BYTES), db = smem_desc(st + X_OFF);
+            const uint64_t dal = smem_desc(st + W_TILES * TILE_BYTES), dal2 = smem_desc(st + (W_TILES + 1) * TILE_BYTES), dbl = smem_desc(st + X_OFF + X_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {  // 16 fp16 = 32 bytes further along the swizzled row: +2 in the address field
                 const uint32_t acc = (kb | k) != 0 ? 1u : 0u;
                 mma_f16(tmem, da + 2u * k, db + 2u * k, IDESC, acc);
-                if (DUAL) mma_f16(tmem + BN, da2 + 2u * k, db + 2u * k, IDESC, acc);
+                if (XP == 2) mma_f16(tmem, da + 2u * k, dbl + 2u * k, IDESC, 1u);
+                if (WP == 2) mma_f16(tmem, dal + 2u * k, db + 2u * k, IDESC, 1u);
+                if (DUAL) {
+                    mma_f16(tmem + BN, da2 + 2u * k, db + 2u * k, IDESC, acc);
+                    if (XP == 2) mma_f16(tmem + BN, da2 + 2u * k, dbl + 2u * k, IDESC, 1u);
+                    if (WP == 2) mma_f16(tmem + BN, dal2 + 2u * k, db + 2u * k, IDESC, 1u);
+                }
             }
             mma_commit(bars + (STAGES + s) * 8);  // the stage is free again once these products have read it
         }
@@ -276,8 +301,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 // ---- operand conversion -------------------------------------------------------------------------------------
 // One block per row of x: y = fp16( (x * inv_rms) * w ) (the reference's RMSNorm, runtime.rs:588-601) or fp16(x).
 // Rows of inactive slots and rows beyond n_rows (up to the tile boundary) become zeros.
+// dst_lo != null: the part fp16 cannot hold goes there, x = fp16 hi + fp16 lo to ~22 bits.
 __global__ void __launch_bounds__(256)
-k_rows_to_f16(__half* __restrict__ dst, const float* __restrict__ x, const void* __restrict__ norm_w, int norm_fmt, float eps,
+k_rows_to_f16(__half* __restrict__ dst, __half* __restrict__ dst_lo, const float* __restrict__ x, const void* __restrict__ norm_w, int norm_fmt, float eps,
               const SeqState* __restrict__ state, uint32_t K, uint32_t n_rows) {
     pdl_wait();
     pdl_launch_dependents();
@@ -285,7 +311,7 @@ k_rows_to_f16(__half* __restrict__ dst, const float* __restrict__ x, const void*
     __half* out = dst + (size_t)r * K;
     const bool live = r < n_rows && (!state || state[r].active);
     if (!live) {
-        for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) out[k] = __float2half_rn(0.0f);
+        for (uint32_t k = threadIdx.x; k < K; k += blockDim.x) { out[k] = __float2half_rn(0.0f); if (dst_lo) dst_lo[(size_t)r * K + k] = __float2half_rn(0.0f); }
         return;
     }
     const float4* in4 = reinterpret_cast<const float4*>(x + (size_t)r * K);  // K is a multiple of 8
@@ -322,12 +348,17 @@ k_rows_to_f16(__half* __restrict__ dst, const float* __restrict__ x, const void*
         }
         const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
         out2[k] = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
+        if (dst_lo) {
+            const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+            const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+            reinterpret_cast<uint2*>(dst_lo + (size_t)r * K)[k] = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
+        }
     }
 }
 
 // Weights -> fp16 [rows][K], eight elements (one packed int4 word, one 16-byte store) per thread.
 __global__ void __launch_bounds__(256)
-k_weights_to_f16(uint4* __restrict__ dst, const void* __restrict__ data, const void* __restrict__ scales, int fmt, uint64_t n8, uint32_t K) {
+k_weights_to_f16(uint4* __restrict__ dst, uint4* __restrict__ dst_lo, const void* __restrict__ data, const void* __restrict__ scales, int fmt, uint64_t n8, uint32_t K) {
     pdl_wait();
     pdl_launch_dependents();
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -369,6 +400,12 @@ k_weights_to_f16(uint4* __restrict__ dst, const void* __restrict__ data, const v
 #pragma unroll
         for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
         dst[i] = *reinterpret_cast<const uint4*>(h);
+        if (dst_lo) {  // what the rounding to fp16 dropped (exact as a difference of nearby floats), rounded to fp16 in turn
+            __half2 l[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 hf = __half22float2(h[j]); l[j] = __floats2half2_rn(f[2 * j] - hf.x, f[2 * j + 1] - hf.y); }
+            dst_lo[i] = *reinterpret_cast<const uint4*>(l);
+        }
     }
 }
 
@@ -407,6 +444,7 @@ bool g_tc_init = false;
 
 bool gemm_tc_two_per_sm = true;  // vb_set_option("prefill_two_per_sm", 0): one block of twice the ring depth per SM (measured 4 % slower)
 bool gemm_tc_split_k = true;  // vb_set_option("decode_split_k", 0): one block per tile of 128 weight rows
+int gemm_tc_split = 2;  // vb_set_option("prefill_split", n): prefill chunks multiply 0: fp16(x).fp16(W); 1: x as hi + lo; 2: x and W as hi + lo
 bool gemm_tc_wide = false;  // vb_set_option("prefill_wide", 1): 256 rows of x per tile when a chunk has more than 128 (measured slower at 512 rows: fewer blocks than SMs)
 
 cudaError_t gemm_tc_init() {
@@ -432,12 +470,15 @@ cudaError_t gemm_tc_init() {
 }
 
 // fp16 [rows][cols] copy of a weight matrix (int8 per channel: the integers; the row scale stays with the caller)
-cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m) {
+cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m, void* dst_lo) {
     const uint64_t n8 = (uint64_t)m.rows * m.cols / 8;
     uint64_t blocks = (n8 + 255) / 256;
     if (blocks > 148ull * 64) blocks = 148ull * 64;
-    return launch(lc, k_weights_to_f16, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<uint4*>(dst), m.data, m.scales, (int)m.fmt, n8, m.cols);
+    return launch(lc, k_weights_to_f16, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<uint4*>(dst), reinterpret_cast<uint4*>(dst_lo), m.data,
+                  m.scales, (int)m.fmt, n8, m.cols);
 }
+// formats whose values fp16 does not hold exactly (int8 per channel: the integers are exact, the row scale stays in fp32)
+bool gemm_tc_weights_inexact(int32_t fmt) { return fmt == VB_FMT_Q4G32 || fmt == VB_FMT_Q4G64REF || fmt == VB_FMT_F32 || fmt == VB_FMT_BF16; }
 
 bool gemm_tc_supported(const GemvArgs& a) {
     if (a.w.rows == 0 || a.w.cols == 0 || a.w.cols % 8 != 0 || !fmt_shape_ok(a.w.fmt, a.w.cols) || !a.w.data) return false;
@@ -459,7 +500,7 @@ uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_r
 uint64_t gemm_tc_operand_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual) {
     const uint64_t xb = (gemm_tc_rows_padded(n_rows) * in_dim * 2 + 1023) / 1024 * 1024;
     const uint64_t wb = ((uint64_t)out_dim * in_dim * 2 + 1023) / 1024 * 1024;
-    return xb + (dual ? 2 : 1) * wb;
+    return 2 * xb + (dual ? 2 : 1) * 2 * wb;  // room for the hi and lo parts of both operands
 }
 
 cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed) {
@@ -472,29 +513,47 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     if (e != cudaSuccess) return e;
     const uint64_t rows_pad = gemm_tc_rows_padded(n_rows);
     const uint64_t xb = (rows_pad * K * 2 + 1023) / 1024 * 1024, wb = ((uint64_t)out_dim * K * 2 + 1023) / 1024 * 1024;
+    const bool narrow = n_rows <= 32;  // decode batches: 32 rows of x per tile, no tensor-core work on padding
+    // prefill chunks: hi + lo parts of x (and of weights fp16 does not hold exactly); decode batches keep single parts
+    const uint32_t x_parts = (!narrow && gemm_tc_split >= 1) ? 2u : 1u;
+    const bool w_inexact = gemm_tc_weights_inexact(a.w.fmt) || (dual && gemm_tc_weights_inexact(a.w2.fmt));
+    const uint32_t w_parts = (!narrow && gemm_tc_split >= 2 && w_inexact) ? 2u : 1u;
     __half* xh = reinterpret_cast<__half*>(reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES);
-    unsigned char* wbase = reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES + xb;
+    __half* xl = x_parts == 2 ? xh + rows_pad * K : nullptr;  // directly below the hi rows: one tensor map covers both
+    unsigned char* wbase = reinterpret_cast<unsigned char*>(workspace) + WS_HEAD_BYTES + 2 * xb;
 
     // decode batches (<= 32 rows, one 32-row box of x): only those 32 rows are ever read
-    e = launch(lc, k_rows_to_f16, dim3(n_rows <= 32 ? 32u : (unsigned)rows_pad), dim3(256), 0, xh, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    e = launch(lc, k_rows_to_f16, dim3(narrow ? 32u : (unsigned)rows_pad), dim3(256), 0, xh, xl, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
     if (e != cudaSuccess) return e;
     const void* wh[2] = {a.w.data, a.w2.data};
+    const void* wl[2] = {nullptr, nullptr};
     const WMat* mats[2] = {&a.w, &a.w2};
     for (int i = 0; i < (dual ? 2 : 1); ++i) {
-        if (mats[i]->fmt == VB_FMT_F16) continue;  // used where it lies
-        if (mats[i]->f16) { wh[i] = mats[i]->f16; continue; }  // resident fp16 copy
+        const bool need_lo = w_parts == 2;
+        if (mats[i]->fmt == VB_FMT_F16) {  // used where it lies (exact)
+            if (need_lo) return cudaErrorInvalidValue;  // cannot happen: fp16 weights are never inexact
+            continue;
+        }
+        if (mats[i]->f16 && (!need_lo || mats[i]->f16_lo)) { wh[i] = mats[i]->f16; wl[i] = mats[i]->f16_lo; continue; }  // resident copies
         const uint64_t n8 = (uint64_t)out_dim * K / 8;
         uint64_t blocks = (n8 + 255) / 256;
         if (blocks > 148ull * 64) blocks = 148ull * 64;
-        e = launch(lc, k_weights_to_f16, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<uint4*>(wbase + i * wb), mats[i]->data,
+        unsigned char* hi = wbase + (size_t)i * 2 * wb;
+        unsigned char* lo = need_lo ? hi + wb : nullptr;
+        e = launch(lc, k_weights_to_f16, dim3((unsigned)blocks), dim3(256), 0, reinterpret_cast<uint4*>(hi), reinterpret_cast<uint4*>(lo), mats[i]->data,
                    mats[i]->scales, (int)mats[i]->fmt, n8, K);
         if (e != cudaSuccess) return e;
-        wh[i] = wbase + i * wb;
+        wh[i] = hi;
+        wl[i] = lo;
     }
-    CUtensorMap mw, mw2, mx;
-    const bool narrow = n_rows <= 32;  // decode batches: 32 rows of x per tile, no tensor-core work on padding
-    if (!make_map(&mw, wh[0], out_dim, K) || !make_map(&mx, xh, rows_pad, K, narrow ? 32 : BM)) return cudaErrorNotSupported;
+    CUtensorMap mw, mw2, mx, mwl, mwl2;
+    if (!make_map(&mw, wh[0], out_dim, K) || !make_map(&mx, xh, rows_pad * x_parts, K, narrow ? 32 : BM)) return cudaErrorNotSupported;
     if (dual) { if (!make_map(&mw2, wh[1], out_dim, K)) return cudaErrorNotSupported; } else mw2 = mw;
+    mwl = mw; mwl2 = mw2;
+    if (w_parts == 2) {
+        if (!make_map(&mwl, wl[0], out_dim, K)) return cudaErrorNotSupported;
+        if (dual && !make_map(&mwl2, wl[1], out_dim, K)) return cudaErrorNotSupported;
+    }
     GemmParams p;
     p.dst = a.dst + a.dst_offset;
     p.row_scale = a.w.fmt == VB_FMT_I8PC ? (const __half*)a.w.scales : nullptr;
@@ -507,6 +566,11 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     fast_error_word(&p.err);
     p.counters = reinterpret_cast<uint32_t*>(workspace);
     p.part = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(workspace) + WS_COUNTER_BYTES);
+    p.x_parts = x_parts; p.w_parts = w_parts; p.x_lo_row = (uint32_t)rows_pad;
+    auto stages_of = [&](int bn, int ring_kb) {
+        const int stage = (dual ? 2 : 1) * (int)w_parts * TILE_BYTES + (int)x_parts * bn * BK * 2;
+        return ring_kb * 1024 / stage;
+    };
     if (narrow) {
         // few row tiles (QKV, O, down of a decode batch: 28-36 blocks on 148 SMs): split K so that every SM streams
         const uint32_t tiles = (out_dim + BM - 1) / BM, nk = (K + BK - 1) / BK;
@@ -516,22 +580,27 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
             if ((uint64_t)splits * tiles * 128 * 32 * 4 > WS_PART_BYTES || tiles * 4 > WS_COUNTER_BYTES) splits = 1;
         }
         const dim3 grid(1, tiles, splits);
-        if (dual) return launch(lc, k_gemm_tc<true, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
-        return launch(lc, k_gemm_tc<false, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+        p.stages = (uint32_t)stages_of(32, 192);
+        if (dual) return launch(lc, k_gemm_tc<true, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
+        return launch(lc, k_gemm_tc<false, 32>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
     }
     // 256 rows of x per tile (half the weight traffic per flop) once there are more than 128 rows
-    if (n_rows > 128 && gemm_tc_wide) {
+    if (n_rows > 128 && gemm_tc_wide && stages_of(256, 192) >= 2) {
         const dim3 grid((unsigned)((rows_pad + 255) / 256), (out_dim + BM - 1) / BM);
-        if (dual) return launch(lc, k_gemm_tc<true, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
-        return launch(lc, k_gemm_tc<false, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+        p.stages = (uint32_t)stages_of(256, 192);
+        if (dual) return launch(lc, k_gemm_tc<true, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
+        return launch(lc, k_gemm_tc<false, 256>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
     }
     const dim3 grid((unsigned)(rows_pad / 128), (out_dim + BM - 1) / BM);
-    if (gemm_tc_two_per_sm) {  // 3 (2 for gate/up) stages per block, two blocks per SM
-        if (dual) return launch(lc, k_gemm_tc<true, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, p);
-        return launch(lc, k_gemm_tc<false, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, p);
+    if (gemm_tc_two_per_sm && stages_of(128, 96) >= 2) {  // half the ring per block, two blocks per SM
+        p.stages = (uint32_t)stages_of(128, 96);
+        if (dual) return launch(lc, k_gemm_tc<true, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, mwl, mwl2, p);
+        return launch(lc, k_gemm_tc<false, 128, 2>, grid, dim3(128), SMEM_BYTES_HALF, mw, mw2, mx, mwl, mwl2, p);
     }
-    if (dual) return launch(lc, k_gemm_tc<true, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
-    return launch(lc, k_gemm_tc<false, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, p);
+    p.stages = (uint32_t)stages_of(128, 192);
+    if (p.stages < 2) return cudaErrorInvalidConfiguration;
+    if (dual) return launch(lc, k_gemm_tc<true, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
+    return launch(lc, k_gemm_tc<false, 128>, grid, dim3(128), SMEM_BYTES, mw, mw2, mx, mwl, mwl2, p);
 }
 
 }  // namespace vb

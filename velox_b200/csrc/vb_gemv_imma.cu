@@ -6,13 +6,13 @@
 // only has to become a byte: one AND per FOUR weights (`w & 0x0F0F0F0F`, and the same of `w >> 4`), and
 // mma.sync.m16n8k32.s8 multiplies the bytes 0..15 directly.
 //
-// Activations.  x is staged in shared memory as 15-bit fixed point per quantization group of 32:
-// X = rint(x * p_g), p_g the power of two that brings the group's largest magnitude into [8192, 16384),
+// Activations.  x is staged in shared memory as 16-bit fixed point per quantization group of 32:
+// X = rint(x * p_g), p_g = 32000 / (the group's largest magnitude): 16-bit fixed point,
 // split into two signed bytes X = 256*H + L (L in [-128,127]).  One m16n8k32 covers exactly one group of 32
 // along K for 16 rows, with H and L in two of the eight B columns; four consecutive groups use the four
 // column pairs of the same accumulator, so after the four mma of a 16x128 block lane (g,t) holds, for rows
 // g and g+8, the exact integers sum(q*H) and sum(q*L) of group t.  The zero point is removed with the
-// group's sum(X):  sum((q-8)*X) = 256*C_H + C_L - 8*SX, an exact int32 (< 2^24), converted once and scaled
+// group's sum(X):  sum((q-8)*X) = 256*C_H + C_L - 8*SX, an exact int32 (|.| <= 32*8*32639 < 2^23), converted once and scaled
 // by fp32(scale[row][group]) / p_g.  Nothing is rounded between x's 15-bit quantization and the final fp32
 // accumulation.
 //
@@ -38,6 +38,7 @@
 
 #include "vb_internal.cuh"
 #include "vb_kernels.cuh"
+#include "vb_tp_ll.cuh"
 
 namespace vb {
 
@@ -73,7 +74,15 @@ struct ImmaArgs {
     unsigned char* push_base[8];
     uint32_t push_rank, push_size, push_site, push_n_sites, push_max_pairs;
     uint64_t push_epoch_off, push_data_off;
+    // ... and, with reduce_hidden, each block then gathers the peers' copies of ITS OWN rows and finishes the exchange
+    // itself: hidden[row] += sum over ranks (rank order) of the partial rows.  Every rank runs the same tiles at about
+    // the same time, so a block waits roughly one NVLink latency after its last push instead of the exchange being a
+    // kernel of its own (launch, dependency wait, poll, exit).  At most IM_RED_TILES tiles per tile group.
+    float* reduce_hidden;
+    uint32_t* reduce_err;
+    long long reduce_poll_clocks;
 };
+constexpr int IM_RED_TILES = 4;
 
 __device__ __forceinline__ void imma_16832(int d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
                                            const int c[4]) {
@@ -103,14 +112,18 @@ __device__ __forceinline__ void im_stage_chunk(unsigned char* __restrict__ xq, i
     for (int i = 0; i < 8; ++i) gmax = fmaxf(gmax, fabsf(v[i]));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 1));
     gmax = fmaxf(gmax, __shfl_xor_sync(0xFFFFFFFFu, gmax, 2));
-    float p = 1.0f;  // power of two with gmax * p in [8192, 16384); 1 for an all-zero or non-finite group
-    if (gmax > 0.0f && gmax < 3.0e38f) p = exp2f((float)(13 - ilogbf(gmax)));
+    // scale that brings the group's largest magnitude to 32000: the two signed byte planes hold X in [-32639, 32639], so
+    // every group uses the full 16 bits (a power-of-two scale would leave between one and two of them unused, and at 32
+    // layers that rounding alone moved the logits by ~1e-2); 1 for an all-zero or non-finite group
+    float p = 1.0f;
+    if (gmax > 0.0f && gmax < 3.0e38f) p = __fdividef(32000.0f, gmax);
+    if (!(p < 3.0e38f)) p = 1.0f;
     int X[8], s = 0;
     uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         X[i] = __float2int_rn(v[i] * p);
-        X[i] = max(-16383, min(16383, X[i]));
+        X[i] = max(-32639, min(32639, X[i]));
         s += X[i];
         const int H = (X[i] + 128) >> 8, L = X[i] - (H << 8);
         hw[i >> 2] |= (uint32_t)(H & 0xFF) << (8 * (i & 3));
@@ -409,6 +422,8 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
 
     // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
     uint32_t parity = 0, cslot = 0;  // cslot: byte offset of the ring slot read next
+    float2 own_pair[IM_RED_TILES];   // fused exchange: this thread's own pair of rows of each tile it pushed
+    uint32_t n_own = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     // single row: column g of B is (group gj of a block, plane); multi-row: (row gj of x, plane) of one group at a time
     const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)(gj % NB) * xrow + plane * 32 + 8 * t;
@@ -484,7 +499,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                                 const uint2 bx = *reinterpret_cast<const uint2*>(xb + j * 64);
                                 int d[4] = {0, 0, 0, 0};
                                 imma_16832(d, war[j] & msk, wbr[j] & msk, (war[j] >> 4) & msk, (wbr[j] >> 4) & msk, bx.x, bx.y, d);
-                                const int r0 = d[0] * 256 + d[1] - 8 * sx[j];  // |r| <= 32 * 8 * 16383 < 2^22
+                                const int r0 = d[0] * 256 + d[1] - 8 * sx[j];  // |r| <= 32 * 8 * 32639 < 2^23
                                 const int r1 = d[2] * 256 + d[3] - 8 * sx[j];
                                 const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&scr[j]));
                                 acc0 = fmaf((float)r0 * ip[j], s2.x, acc0);
@@ -595,8 +610,34 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                             asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(seq),
                                          "r"(__float_as_uint(other)), "r"(seq) : "memory");
                         }
+                        if (a.reduce_hidden && n_own < (uint32_t)IM_RED_TILES) own_pair[n_own++] = make_float2(v, other);
                     }
                 }
+            }
+        }
+    }
+    if constexpr (NB == 1) {
+        // fused exchange: gather the peers' copies of the rows this thread pushed and add everything onto the residual stream
+        if (a.push_size > 1 && a.reduce_hidden && gt < 16 && (gt & 1) == 0 && active) {
+            const uint32_t seq = (uint32_t)(push_epoch * a.push_n_sites + a.push_site) + 1u;
+            uint32_t k = 0;
+            for (uint32_t tile = vtile0; tile < n_tiles && k < n_own; tile += vstride, ++k) {
+                const uint32_t row = a.dst_offset + tile * 16 + gt;
+                const size_t pair = row >> 1;
+                const uint4* recv = reinterpret_cast<const uint4*>(a.push_base[a.push_rank] + a.push_data_off) +
+                                    (size_t)(a.push_site % TP_BUFS) * a.push_size * a.push_max_pairs + pair;
+                float2 acc = *reinterpret_cast<const float2*>(a.reduce_hidden + row);
+                for (uint32_t p = 0; p < a.push_size; ++p) {
+                    float2 v = own_pair[k];
+                    if (p != a.push_rank) {
+                        uint4 raw;
+                        poll_ll(recv + (size_t)p * a.push_max_pairs, seq, &raw, a.reduce_err, 0x300u | p, a.reduce_poll_clocks);
+                        v = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.z));
+                    }
+                    acc.x += v.x;
+                    acc.y += v.y;
+                }
+                *reinterpret_cast<float2*>(a.reduce_hidden + row) = acc;
             }
         }
     }
@@ -702,6 +743,16 @@ static size_t imma_ring_depth(uint32_t K, int nb, size_t blk_bytes) {
     return ((size_t)IM_MAX_SMEM - fixed) / stage;
 }
 
+static int sm_count() {
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
+    }
+    return n_sm;
+}
+
 template <int W, int NB>
 static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t max_ring) {
     const size_t fixed = imma_fixed_smem(f.K, NB);
@@ -711,12 +762,7 @@ static cudaError_t imma_launch(const LaunchCfg& lc, const ImmaArgs& f, uint32_t 
     if (max_ring >= 2 && ns > max_ring) ns = max_ring;
     if (NB > 1 && ns > 4) ns = 4;
     ns = ns >= 8 ? 8 : (ns >= 4 ? 4 : (ns >= 3 ? 3 : 2));  // ring depth per warp (template parameter); 4 measured fastest
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) n_sm = 148;
-    }
+    const int n_sm = sm_count();
     const uint32_t n_tiles = f.rows / 16;
     const uint32_t want = f.spread ? n_tiles : (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
     const dim3 grid(want < (uint32_t)n_sm ? want : (uint32_t)n_sm);
@@ -756,12 +802,20 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
     f.trace = a.trace;
     f.spread = imma_spread ? 1u : 0u;
     f.push_size = 0;
+    f.reduce_hidden = nullptr; f.reduce_err = nullptr; f.reduce_poll_clocks = 0;
     if (!multi && a.push.links && a.epilogue == EPI_STORE && a.push.links->size > 1 && a.dst_offset % 2 == 0) {
         const TpLinks& l = *a.push.links;
         for (int r = 0; r < 8; ++r) f.push_base[r] = l.base[r];
         f.push_rank = l.rank; f.push_size = l.size; f.push_site = a.push.site; f.push_n_sites = a.push.n_sites;
         f.push_max_pairs = l.max_pairs; f.push_epoch_off = l.epoch_off; f.push_data_off = l.data_off;
         if (a.pushed) *a.pushed = true;
+        // the block finishes the exchange itself when every tile group has few enough tiles to remember
+        const uint32_t n_tiles = rows / 16, want = imma_spread ? n_tiles : (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
+        const uint32_t blocks = want < (uint32_t)sm_count() ? want : (uint32_t)sm_count(), groups = IM_GROUPS * blocks;
+        if (a.push.reduce_hidden && a.dst_offset == 0 && (n_tiles + groups - 1) / groups <= (uint32_t)IM_RED_TILES) {
+            f.reduce_hidden = a.push.reduce_hidden; f.reduce_err = a.push.err; f.reduce_poll_clocks = l.poll_clocks;
+            if (a.reduced) *a.reduced = true;
+        }
     }
     *handled = true;
     // two blocks per step when every warp's share of a tile is a whole number of pairs

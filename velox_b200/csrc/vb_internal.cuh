@@ -52,8 +52,10 @@ struct WMat {
     const void* v3 = nullptr;
     const void* v3_scales = nullptr;
     const void* v3_swiglu = nullptr;
-    // resident fp16 [rows][cols] copy for the tensor-core GEMMs (vb_gemm_tc.cu); null: converted per call
+    // resident fp16 [rows][cols] copy for the tensor-core GEMMs (vb_gemm_tc.cu); null: converted per call.
+    // f16_lo: what that copy's rounding dropped, as a second fp16 matrix (prefill chunks multiply hi + lo)
     const void* f16 = nullptr;
+    const void* f16_lo = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {

@@ -53,6 +53,9 @@ cudaError_t tp_reduce(const LaunchCfg& lc, const TpLinks& l, float* hidden, cons
 struct TpPush {
     const TpLinks* links = nullptr;  // null: no push
     uint32_t site = 0, n_sites = 1;
+    // != null: the product may also finish the exchange (gather the peers' rows, add everything onto this vector)
+    float* reduce_hidden = nullptr;
+    uint32_t* err = nullptr;
 };
 constexpr uint32_t TP_BUFS = 4;  // receive buffers used round-robin by consecutive exchange sites
 cudaError_t tp_argmax(const LaunchCfg& lc, const TpLinks& l, const void* pairs, uint32_t batch, uint32_t site, uint32_t n_sites,
@@ -85,6 +88,7 @@ struct GemvArgs {
     uint32_t max_ring = 12;          // cap on the weight ring depth per warp
     TpPush push;                     // EPI_STORE only: also send the rows to the tensor-parallel peers
     bool* pushed = nullptr;          // out: set when the kernel that ran did send them
+    bool* reduced = nullptr;         // out: set when it also finished the exchange (TpPush::reduce_hidden)
     unsigned long long* trace = nullptr;  // 3-slot timestamp record of this launch (tuned kernels only)
 };
 cudaError_t gemv(const LaunchCfg& lc, const GemvArgs& a, int path);
@@ -123,11 +127,21 @@ extern bool gemm_tc_split_k;
 uint64_t gemm_tc_operand_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
 uint64_t gemm_tc_workspace_zero_bytes();  // leading bytes of the workspace that must be zero before the first call
 extern bool gemm_tc_two_per_sm;
-cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m);
+cudaError_t weights_to_f16(const LaunchCfg& lc, void* dst, const WMat& m, void* dst_lo = nullptr);
+bool gemm_tc_weights_inexact(int32_t fmt);
+extern int gemm_tc_split;
 bool gemm_tc_supported(const GemvArgs& a);
 uint64_t gemm_tc_workspace_bytes(uint32_t out_dim, uint32_t in_dim, uint32_t n_rows, bool dual);
 // counters_zeroed: the caller zeroed the head of the workspace once (allows the split-K path)
 cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed = false);
+
+// vb_gemm_i8.cu: decode batches (<= 32 rows) over int8 per-channel weights on the integer tensor cores, weights read
+// where they lie (one byte per weight), exact arithmetic; workspace head (gemm_i8_workspace_zero_bytes) zero before first use
+extern bool gemm_i8_enabled;
+bool gemm_i8_supported(const GemvArgs& a);
+uint64_t gemm_i8_workspace_bytes(uint32_t in_dim);
+inline uint64_t gemm_i8_workspace_zero_bytes() { return 64 * 1024; }
+cudaError_t gemm_i8(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed);
 
 // vb_attn.cu
 struct AttnArgs {
