@@ -68,3 +68,51 @@ def test_two_rank_gloo_exchange_matches_unsharded(tmp_path):
     assert int(res["token_tp"]) == int(res["token_ref"])
     assert int(res["tie_token_tp"]) == int(res["tie_token_ref"]) == int(res["tie_expected"])
     assert res["id_ok"]
+
+
+def _run_membership(mode, tmp_path, port):
+    import json
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE="2",
+                   PYTHONPATH=ROOT, OMP_NUM_THREADS="1")
+        procs.append(subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_membership_worker.py"), "--mode", mode,
+                                       "--out", str(tmp_path)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=120)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append(out)
+    for p, out in zip(procs, outs):
+        assert p.returncode == 0, out[-3000:]
+    return [json.load(open(os.path.join(str(tmp_path), "rank%d.json" % r))) for r in range(2)]
+
+
+def test_gloo_ranks_with_different_descriptions_are_refused(tmp_path):
+    """Rank 1 was started on a 3-layer description, rank 0 on 2 layers: both raise before any exchange is set up,
+    naming rank 1; identical descriptions pass."""
+    res = _run_membership("mismatch", tmp_path, 29621)
+    for r in res:
+        assert r["raised"] is not None and "[1]" in r["raised"], r
+        assert r["same_ok"]
+
+
+def test_gloo_rank_leaves_between_steps_and_is_noticed_on_the_host(tmp_path):
+    """Rank 1 serves three steps, then leaves with nothing in flight and says so in the group's store; rank 0 learns
+    of it from the store before its fourth launch (no collective is entered that nobody would answer)."""
+    r0, r1 = _run_membership("leave", tmp_path, 29623)
+    assert r1["done"] == 3 and r1["noticed"] is None
+    assert r0["done"] == 3 and r0["failure"] is None
+    assert r0["noticed"] is not None and r0["noticed"]["step"] == 3 and "[1]" in r0["noticed"]["what"]
+
+
+def test_gloo_rank_that_is_simply_gone_ends_the_next_collective_with_an_error(tmp_path):
+    """Rank 1 exits after three steps without a word: rank 0's next exchange fails within the group's short
+    timeout (an exception on the host, not a hang) and rank 0 exits cleanly."""
+    r0, r1 = _run_membership("vanish", tmp_path, 29625)
+    assert r1["done"] == 3
+    assert r0["done"] == 3 and r0["noticed"] is None
+    assert r0["failure"] is not None and r0["failure"]["step"] == 3

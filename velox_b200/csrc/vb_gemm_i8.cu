@@ -341,6 +341,108 @@ k_rows_to_i8(int8_t* __restrict__ planes, float* __restrict__ inv_scale, const f
     }
 }
 
+// The same conversion for rows of up to 4096 * XR elements in one trip through memory: 1024 threads hold the row in
+// registers (XR float4 each), so the sum of squares, the largest magnitude and the two byte planes all come from one
+// load; the three passes of the kernel above cost three dependent round trips per row (5-9 us, four times a layer).
+template <int XR>
+__global__ void __launch_bounds__(1024)
+k_rows_to_i8_regs(int8_t* __restrict__ planes, float* __restrict__ inv_scale, const float* __restrict__ x, const void* __restrict__ norm_w,
+                  int norm_fmt, float eps, const SeqState* __restrict__ state, uint32_t K, uint32_t n_rows) {
+    pdl_launch_dependents();  // the product's set-up (tensor maps, tensor memory, its first weight tiles) runs beside this
+    const uint32_t r = blockIdx.x, K4 = K / 4, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int8_t* hp = planes + (size_t)r * K;
+    int8_t* lp = planes + (size_t)(32 + r) * K;
+    __shared__ float red[32];
+    __shared__ float bc[2];
+    // norm weights are weights: on their way before the producer of x is done
+    float4 w[XR];
+    if (norm_w) {
+#pragma unroll
+        for (int i = 0; i < XR; ++i) {
+            const uint32_t k = threadIdx.x + i * 1024;
+            w[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < K4) {
+                if (norm_fmt == VB_FMT_F16) {
+                    const uint2 raw = reinterpret_cast<const uint2*>(norm_w)[k];
+                    const float2 w01 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x)), w23 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                    w[i] = make_float4(w01.x, w01.y, w23.x, w23.y);
+                } else {
+                    w[i] = reinterpret_cast<const float4*>(norm_w)[k];
+                }
+            }
+        }
+    }
+    pdl_wait();
+    const bool live = r < n_rows && (!state || state[r].active);
+    if (!live) {
+        for (uint32_t k = threadIdx.x; k < K4; k += blockDim.x) { reinterpret_cast<uint32_t*>(hp)[k] = 0u; reinterpret_cast<uint32_t*>(lp)[k] = 0u; }
+        if (threadIdx.x == 0) inv_scale[r] = 0.0f;
+        return;
+    }
+    const float4* in4 = reinterpret_cast<const float4*>(x + (size_t)r * K);
+    float4 v[XR];
+#pragma unroll
+    for (int i = 0; i < XR; ++i) {
+        const uint32_t k = threadIdx.x + i * 1024;
+        v[i] = k < K4 ? in4[k] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (norm_w) {
+        // the same order of squares within a thread as the three-pass kernel would not be reproducible anyway (other
+        // thread count); the checker's bound is on the product, not on these bits
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < XR; ++i) { ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss); ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss); }
+        ss = warp_sum(ss);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (warp == 0) {
+            float t = warp_sum(red[lane]);
+            if (lane == 0) bc[0] = 1.0f / sqrtf(t / (float)K + eps);
+        }
+        __syncthreads();
+        const float inv = bc[0];
+#pragma unroll
+        for (int i = 0; i < XR; ++i) {
+            v[i].x = (v[i].x * inv) * w[i].x; v[i].y = (v[i].y * inv) * w[i].y; v[i].z = (v[i].z * inv) * w[i].z; v[i].w = (v[i].w * inv) * w[i].w;
+        }
+    }
+    float mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < XR; ++i) mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+    mx = warp_max(mx);
+    __syncthreads();  // red[] is read no more
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    if (warp == 0) {
+        const float g = warp_max(red[lane]);
+        if (lane == 0) bc[1] = g;
+    }
+    __syncthreads();
+    const float gmax = bc[1];
+    float pw = 1.0f;  // brings the row's largest magnitude to 32000; 1 for an all-zero or non-finite row
+    if (gmax > 0.0f && gmax < 3.0e38f) pw = __fdividef(32000.0f, gmax);
+    if (!(pw < 3.0e38f)) pw = 1.0f;
+    if (threadIdx.x == 0) inv_scale[r] = 1.0f / pw;
+#pragma unroll
+    for (int i = 0; i < XR; ++i) {
+        const uint32_t k = threadIdx.x + i * 1024;
+        if (k < K4) {
+            const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+            uint32_t hw = 0, lw = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int X = __float2int_rn(e[j] * pw);
+                X = max(-32639, min(32639, X));
+                const int H = (X + 128) >> 8, L = X - (H << 8);
+                hw |= (uint32_t)(H & 0xFF) << (8 * j);
+                lw |= (uint32_t)(L & 0xFF) << (8 * j);
+            }
+            reinterpret_cast<uint32_t*>(hp)[k] = hw;
+            reinterpret_cast<uint32_t*>(lp)[k] = lw;
+        }
+    }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -409,7 +511,14 @@ cudaError_t gemm_i8(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
     unsigned char* ws = reinterpret_cast<unsigned char*>(workspace);
     int8_t* planes = reinterpret_cast<int8_t*>(ws + I8_COUNTER_BYTES + I8_PART_BYTES);
     float* inv_scale = reinterpret_cast<float*>(ws + I8_COUNTER_BYTES + I8_PART_BYTES + (((uint64_t)64 * K + 1023) / 1024 * 1024));
-    e = launch(lc, k_rows_to_i8, dim3(32), dim3(256), 0, planes, inv_scale, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    if (K <= 4096)
+        e = launch(lc, k_rows_to_i8_regs<1>, dim3(32), dim3(1024), 0, planes, inv_scale, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    else if (K <= 8192)
+        e = launch(lc, k_rows_to_i8_regs<2>, dim3(32), dim3(1024), 0, planes, inv_scale, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    else if (K <= 20480)
+        e = launch(lc, k_rows_to_i8_regs<5>, dim3(32), dim3(1024), 0, planes, inv_scale, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
+    else
+        e = launch(lc, k_rows_to_i8, dim3(32), dim3(256), 0, planes, inv_scale, a.x, a.norm_w, a.norm_fmt, a.eps, a.state, K, n_rows);
     if (e != cudaSuccess) return e;
     CUtensorMap mw, mw2, mx;
     if (!make_map_i8(&mw, a.w.data, out_dim, K, I8_BM) || !make_map_i8(&mx, planes, 64, K, I8_BN)) return cudaErrorNotSupported;

@@ -225,14 +225,14 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     const unsigned char* my_ring_ptr = ring + (size_t)wid * NS * BLK;
     const uint32_t my_ring = (uint32_t)__cvta_generic_to_shared(my_ring_ptr);
     BlockCursor icur{vtile0, warp};  // next block to request
-    uint32_t islot = 0;              // byte offset of the ring slot the next request fills (wraps at NS slots)
+    uint32_t issued = 0;  // (slot = counter % NS measured faster than a wrapping byte offset)
     if (warp >= KT) icur.tile = n_tiles;  // fewer k-blocks than warps: this warp has no blocks at all
 #pragma unroll
     for (int i = 0; i < NS - 1; ++i) {
         if (icur.valid(n_tiles)) {
-            issue_block<W>(a.w, KT, icur, my_ring + islot, lane);
+            issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane);
             icur.advance(KT, warp, vstride);
-            islot = islot + BLK == NS * BLK ? 0u : islot + BLK;
+            ++issued;
         }
         cp_async_commit();
     }
@@ -421,9 +421,7 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
     }
 
     // ---- main loop: per tile, this warp's k-blocks in order; the ring stays NS-1 blocks ahead ----------------------
-    uint32_t parity = 0, cslot = 0;  // cslot: byte offset of the ring slot read next
-    float2 own_pair[IM_RED_TILES];   // fused exchange: this thread's own pair of rows of each tile it pushed
-    uint32_t n_own = 0;
+    uint32_t parity = 0, consumed = 0;
     const uint32_t gj = g >> 1, plane = g & 1;  // this lane feeds column g of B: group gj of a block, H or L bytes
     // single row: column g of B is (group gj of a block, plane); multi-row: (row gj of x, plane) of one group at a time
     const unsigned char* xq_lane = NB == 1 ? xq + (size_t)gj * 64 + plane * 32 + 8 * t : xq + (size_t)(gj % NB) * xrow + plane * 32 + 8 * t;
@@ -450,18 +448,18 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
             }
         }
         float acc0 = 0.0f, acc1 = 0.0f;  // rows g and g+8, this lane's groups (t of every block it sees)
-        for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, cslot = cslot + BLK == NS * BLK ? 0u : cslot + BLK) {
+        for (uint32_t kk = warp; kk < KT; kk += IM_WARPS, ++consumed) {
             // request the block NS-1 ahead (its slot was read in the previous iteration), then wait for this one
             if (icur.valid(n_tiles)) {
-                issue_block<W>(a.w, KT, icur, my_ring + islot, lane);
+                issue_block<W>(a.w, KT, icur, my_ring + (issued % NS) * BLK, lane);
                 icur.advance(KT, warp, vstride);
-                islot = islot + BLK == NS * BLK ? 0u : islot + BLK;
+                ++issued;
             }
             cp_async_commit();
             cp_async_wait<NS - 1>();
             __syncwarp();
             if (active) {
-                const unsigned char* blk = my_ring_ptr + cslot;
+                const unsigned char* blk = my_ring_ptr + (consumed % NS) * BLK;
                 if constexpr (NB > 1) {
 #pragma unroll
                     for (int sub = 0; sub < SUB; ++sub) {
@@ -605,12 +603,12 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
                         const size_t slot = ((size_t)(a.push_site % TP_BUFS) * a.push_size + a.push_rank) * a.push_max_pairs +
                                             ((a.dst_offset + tile * 16 + gt) >> 1);
                         for (uint32_t p = 0; p < a.push_size; ++p) {
-                            if (p == a.push_rank) continue;
+                            // with the fused gather this rank's own pair goes through its own region too (a local store)
+                            if (p == a.push_rank && !a.reduce_hidden) continue;
                             uint4* dst = reinterpret_cast<uint4*>(a.push_base[p] + a.push_data_off) + slot;
                             asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(v)), "r"(seq),
                                          "r"(__float_as_uint(other)), "r"(seq) : "memory");
                         }
-                        if (a.reduce_hidden && n_own < (uint32_t)IM_RED_TILES) own_pair[n_own++] = make_float2(v, other);
                     }
                 }
             }
@@ -620,22 +618,17 @@ __global__ void __launch_bounds__(IM_CONSUMERS, 1) k_gemv_q4_imma(ImmaArgs a) {
         // fused exchange: gather the peers' copies of the rows this thread pushed and add everything onto the residual stream
         if (a.push_size > 1 && a.reduce_hidden && gt < 16 && (gt & 1) == 0 && active) {
             const uint32_t seq = (uint32_t)(push_epoch * a.push_n_sites + a.push_site) + 1u;
-            uint32_t k = 0;
-            for (uint32_t tile = vtile0; tile < n_tiles && k < n_own; tile += vstride, ++k) {
+            for (uint32_t tile = vtile0; tile < n_tiles; tile += vstride) {
                 const uint32_t row = a.dst_offset + tile * 16 + gt;
                 const size_t pair = row >> 1;
                 const uint4* recv = reinterpret_cast<const uint4*>(a.push_base[a.push_rank] + a.push_data_off) +
                                     (size_t)(a.push_site % TP_BUFS) * a.push_size * a.push_max_pairs + pair;
                 float2 acc = *reinterpret_cast<const float2*>(a.reduce_hidden + row);
                 for (uint32_t p = 0; p < a.push_size; ++p) {
-                    float2 v = own_pair[k];
-                    if (p != a.push_rank) {
-                        uint4 raw;
-                        poll_ll(recv + (size_t)p * a.push_max_pairs, seq, &raw, a.reduce_err, 0x300u | p, a.reduce_poll_clocks);
-                        v = make_float2(__uint_as_float(raw.x), __uint_as_float(raw.z));
-                    }
-                    acc.x += v.x;
-                    acc.y += v.y;
+                    uint4 raw;  // p == this rank: the pair this thread stored itself, there at once
+                    poll_ll(recv + (size_t)p * a.push_max_pairs, seq, &raw, a.reduce_err, 0x300u | p, a.reduce_poll_clocks);
+                    acc.x += __uint_as_float(raw.x);
+                    acc.y += __uint_as_float(raw.z);
                 }
                 *reinterpret_cast<float2*>(a.reduce_hidden + row) = acc;
             }
@@ -809,7 +802,7 @@ cudaError_t gemv_imma(const LaunchCfg& lc, const GemvArgs& a, bool* handled) {
         f.push_rank = l.rank; f.push_size = l.size; f.push_site = a.push.site; f.push_n_sites = a.push.n_sites;
         f.push_max_pairs = l.max_pairs; f.push_epoch_off = l.epoch_off; f.push_data_off = l.data_off;
         if (a.pushed) *a.pushed = true;
-        // the block finishes the exchange itself when every tile group has few enough tiles to remember
+        // the block finishes the exchange itself when every tile group has only a few tiles to gather (the gather is serial)
         const uint32_t n_tiles = rows / 16, want = imma_spread ? n_tiles : (n_tiles + IM_GROUPS - 1) / IM_GROUPS;
         const uint32_t blocks = want < (uint32_t)sm_count() ? want : (uint32_t)sm_count(), groups = IM_GROUPS * blocks;
         if (a.push.reduce_hidden && a.dst_offset == 0 && (n_tiles + groups - 1) / groups <= (uint32_t)IM_RED_TILES) {

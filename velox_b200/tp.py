@@ -8,10 +8,20 @@ barriers / max-over-ranks of timings.
 """
 from __future__ import annotations
 
+import dataclasses
+import hashlib
 import os
 
 from .engine import Engine
 from .modelspec import ModelSpec
+
+
+class TpConfigMismatch(RuntimeError):
+    """The ranks of one group were started on different model descriptions (or group sizes)."""
+
+
+class TpPeerLeft(RuntimeError):
+    """A rank of the group announced that it is gone (or stopped answering) between two steps."""
 
 
 def env_rank():
@@ -45,12 +55,67 @@ def share_unique_id(make_id) -> bytes:
     return box[0]
 
 
+def config_fingerprint(spec: ModelSpec, tp_size: int, **extra) -> str:
+    """SHA-256 over everything the ranks of one model must agree on before their kernels wait on each other:
+    every field of the model description (shapes, formats, theta, eps, seed of synthetic weights), the group
+    size, and whatever the caller adds (max_batch, max_seq_len, exchange kind ...)."""
+    items = sorted(dataclasses.asdict(spec).items()) + [("tp_size", int(tp_size))] + sorted(extra.items())
+    return hashlib.sha256(repr(items).encode()).hexdigest()
+
+
+def check_same_config(fingerprint: str):
+    """Every rank contributes its fingerprint; all of them raise TpConfigMismatch (naming the ranks that differ from
+    rank 0) when they are not identical.  Host-side only, before any peer mapping or communicator exists: a rank
+    built from another description fails here instead of inside an exchange that its peers would wait on."""
+    import torch.distributed as dist
+    seen = [None] * dist.get_world_size()
+    dist.all_gather_object(seen, fingerprint)
+    odd = [r for r, f in enumerate(seen) if f != seen[0]]
+    if odd:
+        raise TpConfigMismatch("ranks %s were started on a different model description than rank 0" % odd)
+
+
+class Membership:
+    """Who is still there, asked on the host between steps (never from a kernel).
+
+    A rank that stops serving calls ``leave()`` once none of its kernels or collectives is in flight; it writes
+    one key into the group's store.  Every other rank calls ``check()`` before its next launch: a counter read,
+    no collective, no wait; it raises TpPeerLeft naming the ranks that are gone, so that no kernel is launched
+    that would poll a peer region nobody writes to any more (those polls are bounded, but they take seconds)."""
+
+    def __init__(self, store=None, rank: int | None = None, world: int | None = None, prefix: str = "vb_tp"):
+        import torch.distributed as dist
+        self.store = store if store is not None else dist.distributed_c10d._get_default_store()
+        self.rank = dist.get_rank() if rank is None else rank
+        self.world = dist.get_world_size() if world is None else world
+        self.prefix = prefix
+        self.store.add(self._key("left_count"), 0)  # the key exists from now on
+
+    def _key(self, name: str) -> str:
+        return "%s/%s" % (self.prefix, name)
+
+    def leave(self, reason: str = ""):
+        self.store.set(self._key("left/%d" % self.rank), reason or "left")
+        self.store.add(self._key("left_count"), 1)
+
+    def gone(self) -> list[int]:
+        if self.store.add(self._key("left_count"), 0) == 0:
+            return []
+        return [r for r in range(self.world) if r != self.rank and self.store.check([self._key("left/%d" % r)])]
+
+    def check(self):
+        gone = self.gone()
+        if gone:
+            raise TpPeerLeft("ranks %s left the group" % gone)
+
+
 def connect(eng: Engine, exchange: str = "p2p"):
     """Gives a sharded engine its exchange: "nccl" (communicator inside the library) or "p2p" (NVLink peer
     mappings, 2..8 ranks; the NCCL communicator is still created so that option "tp_p2p"=0 can fall back)."""
     import torch.distributed as dist
     if exchange not in ("p2p", "nccl"):
         raise ValueError(exchange)
+    check_same_config(config_fingerprint(eng.spec, eng.tp_size, max_batch=eng.max_batch, exchange=exchange))
     eng.tp_init(share_unique_id(Engine.tp_unique_id))
     if exchange == "p2p":
         handles = [None] * dist.get_world_size()
