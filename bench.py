@@ -248,7 +248,7 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
     world = 1 if solo else R.world
     tp = is_tp(workload)
     prompt_lens = [prompt_len] * batch
-    if workload == BS32_WORKLOAD:
+    if workload == BS32_WORKLOAD and not args.same_prompt_len:
         prompt_lens = [int(x) for x in np.random.default_rng(SEED).integers(256, 2049, size=batch)]
     max_seq = max(prompt_lens) + warmup + 2 * steps + 16
 
@@ -512,6 +512,8 @@ def main():
     ap.add_argument("--gemv-path", type=int, default=1)
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--prompt-len", type=int, default=0)
+    ap.add_argument("--same-prompt-len", action="store_true", help="batch workloads: every sequence gets --prompt-len tokens "
+                    "instead of lengths uniform in [256, 2048] (shows what uneven lengths cost)")
     ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (quick checks)")
     ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],

@@ -50,7 +50,9 @@ def build(force: bool = False) -> None:
     """Compile the checker with the Makefile beside this file (gcc, a few seconds)."""
     if force or _stale(os.path.join(_HERE, "libvelox_oracle.so")):
         subprocess.check_call(["make", "-C", _HERE, "libvelox_oracle.so"], stdout=subprocess.DEVNULL)
-    if force or not os.path.exists(os.path.join(_HERE, "_ref", "libvelox_ref_smollm.so")):
+    ref_so, harness = os.path.join(_HERE, "_ref", "libvelox_ref_smollm.so"), os.path.join(_HERE, "ref_smollm_harness.c")
+    # (where the reference tree is absent the recipe keeps the prebuilt file, so a newer harness is harmless there)
+    if force or not os.path.exists(ref_so) or os.path.getmtime(harness) > os.path.getmtime(ref_so):
         subprocess.call(["make", "-C", _HERE, "ref"], stdout=subprocess.DEVNULL)
 
 
@@ -148,6 +150,9 @@ def ref_lib():
         R.refsm_gqa.argtypes = [C.c_void_p] * 5 + [C.c_uint64] * 4
         R.refsm_argmax.restype = C.c_uint32
         R.refsm_argmax.argtypes = [C.c_void_p, C.c_uint64]
+        if hasattr(R, "refsm_sample_top_p"):
+            R.refsm_sample_top_p.restype = C.c_uint32
+            R.refsm_sample_top_p.argtypes = [C.c_void_p, C.c_uint64, C.c_float, C.c_float, C.c_float]
         R.refsm_mla.argtypes = [C.c_void_p] * 7 + [C.c_uint64, C.c_uint64, C.c_float]
         R.refsm_dim.restype = C.c_uint64
         R.refsm_dim.argtypes = [C.c_int]

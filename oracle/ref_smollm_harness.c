@@ -98,6 +98,9 @@ void refsm_gqa(float* out, float* scores, const float* q, const float* k, const 
     velox_c99_gqa_attention_step_f32(out, scores, q, k, v, (size_t)nq, (size_t)nkv, (size_t)hd, (size_t)pos);
 }
 uint32_t refsm_argmax(const float* logits, uint64_t n) { return velox_c99_sample_argmax_f32(logits, (size_t)n); }
+uint32_t refsm_sample_top_p(const float* logits, uint64_t n, float temperature, float top_p, float coin) {
+    return velox_c99_sample_top_p_f32(logits, (size_t)n, temperature, top_p, coin);
+}
 /* hidden 576, latent 512, max_seq 2048 are compiled into the emitted function */
 void refsm_mla(float* dst, const float* x, const float* w_norm, const float* w_dkv, const float* w_q,
                const float* w_o, float* pool, uint64_t layer, uint64_t step, float eps) {
