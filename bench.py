@@ -10,7 +10,7 @@ HBM, timed by CUDA events on the library's stream around K CUDA-graph replays; `
 every step is driven from the host through the C ABI (token and position sent in, sampled token read back).
 N>1 runs N independent replicas of that model (it fits one GPU): weak scaling, no data-path collective.
 
-The same line carries two more objects:
+The same line carries three more objects:
   "tp"    at every N: ONE Qwen2-72B-shape int4-g32 model, batch 1, 1024-token prompt, sharded over the N ranks
           (tensor parallel: column-parallel QKV / gate / up, row-parallel O / down, one exchange after each; N = 1
           is the unsharded model on one GPU): per-token latency, per-GPU roofline, and at N > 1 the speed-up over
@@ -446,6 +446,9 @@ def tp_object(args, R: Ranks):
     return obj
 
 
+MLA_WORKLOAD = "deepseek-mla-bs64"
+
+
 def mla_object(R: Ranks, iters: int = 20):
     """The absorbed multi-head latent attention decode kernel on the DeepSeek-V3-style shape of the benchmark
     configuration: 128 heads, latent 512 + 64, batch 64, context lengths uniform in [1024, 8192], bf16 latent cache.
@@ -491,7 +494,7 @@ def mla_object(R: Ranks, iters: int = 20):
         tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
     except Exception:
         tpeak = 1590.0
-    return {"workload": "deepseek-mla-bs64", "kernel": "k_mla_decode + k_mla_merge (one layer's attention for the batch)", "batch": B, "heads": H,
+    return {"workload": MLA_WORKLOAD, "kernel": "k_mla_decode_tc (tcgen05) + k_mla_merge (one layer's attention for the batch)", "batch": B, "heads": H,
             "latent": "512 + 64 bf16", "context": "uniform in [1024, 8192], mean %d" % (rows // B), "ms_per_launch": ms, "gpu_launches": 2 * iters,
             "l2_policy": "inputs larger than L2: %.2f GB of latent cache per launch" % (rows * W * 2 / 1e9),
             "roofline_tensor": {"bound": "tensor", "achieved": flops / (ms * 1e-3) / 1e12, "peak": tpeak, "unit": "TFLOP/s",
@@ -514,6 +517,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=0)
     ap.add_argument("--same-prompt-len", action="store_true", help="batch workloads: every sequence gets --prompt-len tokens "
                     "instead of lengths uniform in [256, 2048] (shows what uneven lengths cost)")
+    ap.add_argument("--mla-path", type=int, default=1, choices=[0, 1], help="MLA workload: 1 tcgen05 kernel (default), 0 mma.sync kernel")
     ap.add_argument("--layers", type=int, default=0, help="run the workload's shape with this many layers (quick checks)")
     ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
@@ -529,6 +533,22 @@ def main():
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.workload == MLA_WORKLOAD:
+        # the attention kernel of the MLA configuration alone (what the "mla" object of the default line holds)
+        R = Ranks()
+        from velox_b200 import lib as L
+        L.check(L.load().vb_op_mla_set_path(args.mla_path))
+        obj = mla_object(R, iters=max(1, args.steps))
+        obj["kernel_path"] = "tcgen05" if args.mla_path == 1 else "mma.sync"
+
+        R.close()
+        if rank == 0:
+            print(json.dumps({"metric": "mla_attention_tflops", "value": obj["roofline_tensor"]["achieved"], "unit": "TFLOP/s", "n_gpus": 1,
+                              "steps": args.steps, "warmup": 3, "ms_per_step": obj["ms_per_launch"], "higher_is_better": True,
+                              "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": MLA_WORKLOAD}, "roofline": obj["roofline_tensor"], "mla": obj,
+                              "gpu_launches": obj["gpu_launches"]}), flush=True)
+        return
     spec, batch = workload_spec(args.workload)
     if args.layers > 0:
         spec = spec.scaled(name="%s-%dlayers" % (spec.name, args.layers), n_layers=args.layers)

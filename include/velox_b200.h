@@ -347,11 +347,14 @@ int32_t vb_op_mla_absorbed(float* dst, const float* x, const float* w_norm, cons
  * q fp32 [batch][n_heads][576] = [q_nope . W_uk (512) | q_rope (64)]; latent_cache bf16 [batch][cache_stride_rows][576] =
  * [c_kv | k_rope] per token; ctx_len on the device (a captured graph serves growing contexts).  Products run in bf16 on
  * the tensor cores with fp32 accumulation; the context is cut into slices of split_tokens rows (0 = 1024) merged by a
- * second kernel.  scratch: vb_op_mla_decode_scratch_bytes, 16-byte aligned. */
+ * second kernel.  scratch: vb_op_mla_decode_scratch_bytes, 16-byte aligned.  Default kernel: tcgen05.mma with S and O
+ * in tensor memory, the latent tiles brought in by tiled TMA; vb_op_mla_set_path(0) selects the mma.sync kernel (process-wide;
+ * 1 selects tcgen05 again).  A tcgen05 kernel whose bounded waits run out fills `out` with NaN. */
 uint64_t vb_op_mla_decode_scratch_bytes(uint32_t batch, uint32_t n_heads, uint32_t max_ctx, uint32_t split_tokens);
 int32_t vb_op_mla_decode(float* out, const float* q, const void* latent_cache, const uint32_t* ctx_len, uint32_t batch, uint32_t n_heads,
                          uint32_t max_ctx, uint64_t cache_stride_rows, float scale, uint32_t split_tokens, void* scratch, uint64_t scratch_bytes,
                          void* stream);
+int32_t vb_op_mla_set_path(int32_t path);
 /* LatentKVAppend (src/ir.rs:90, `kv_latent.append_latent`): cache[b][pos[b]][:] = bf16(rows[b][:576]). */
 int32_t vb_op_mla_latent_append(void* latent_cache, const float* rows, const uint32_t* pos, uint32_t batch, uint64_t cache_stride_rows, void* stream);
 /* The per-head products of the absorbed form: dst[b][h][:n_out] = src[b][h][:n_in] . W_h, W bf16 [n_heads][..][..] with

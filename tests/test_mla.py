@@ -36,10 +36,12 @@ def test_absorbed_equals_explicit():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("n_heads,split", [(128, 1024), (128, 256), (40, 1024), (16, 64)])
-def test_cuda_mla_decode_matches_checker(vb, n_heads, split):
+@pytest.mark.parametrize("path", [1, 0], ids=["tcgen05", "mma_sync"])
+@pytest.mark.parametrize("n_heads,split", [(128, 1024), (128, 256), (40, 1024), (16, 64), (160, 512)])
+def test_cuda_mla_decode_matches_checker(vb, n_heads, split, path):
     from velox_b200.engine import DeviceBuffer as dev
     lib = vb.load()
+    vb.check(lib.vb_op_mla_set_path(path))
     rng = np.random.default_rng(n_heads + split)
     lens = [1, 31, 32, 33, 700, 1024, 1025, 2500] if n_heads == 128 and split == 1024 else [5, 64, 65, 900]
     B, max_ctx = len(lens), max(lens)
@@ -65,6 +67,7 @@ def test_cuda_mla_decode_matches_checker(vb, n_heads, split):
     # one row: every head returns that row (softmax weight 1), exactly up to bf16 -> fp32 products
     assert np.max(np.abs(got[0] - cache[0, 0, :DC])) <= 1e-6 if lens[0] == 1 else True
     assert lib.vb_op_mla_decode(d_out.ptr, d_q.ptr, d_cache.ptr, d_len.ptr, B, n_heads, max_ctx, stride, scale, 48, d_scratch.ptr, need, None) == vb.ERR_INVALID
+    vb.check(lib.vb_op_mla_set_path(1))
 
 
 @pytest.mark.gpu

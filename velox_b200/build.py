@@ -14,7 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB = os.path.join(_HERE, "libvelox_b200.so")
 RUNNER = os.path.join(_HERE, "velox_b200_runner")
-SOURCES = ["vb_basic.cu", "vb_gemv.cu", "vb_gemv_fast.cu", "vb_gemv_imma.cu", "vb_attn.cu", "vb_attn_prefill.cu", "vb_mla.cu", "vb_gemm_tc.cu", "vb_engine.cu", "vb_nccl.cu", "vb_tp.cu", "vb_sample.cu", "vb_spec.cu", "vb_gguf.cu", "vb_fused.cu", "vb_mla_decode.cu", "vb_gemm_i8.cu"]
+SOURCES = ["vb_basic.cu", "vb_gemv.cu", "vb_gemv_fast.cu", "vb_gemv_imma.cu", "vb_attn.cu", "vb_attn_prefill.cu", "vb_mla.cu", "vb_gemm_tc.cu", "vb_engine.cu", "vb_nccl.cu", "vb_tp.cu", "vb_sample.cu", "vb_spec.cu", "vb_gguf.cu", "vb_fused.cu", "vb_mla_decode.cu", "vb_gemm_i8.cu", "vb_mla_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
               "--use_fast_math=false", "-Xptxas", "-v"]
 

@@ -22,6 +22,8 @@
 
 namespace vb {
 
+bool mla_use_tc = true;  // vb_op_mla_set_path(0): the mma.sync kernel of this file instead of the tcgen05 one
+
 namespace {
 
 constexpr int ML_LAT = 576;            // latent row: 512 + 64
@@ -187,8 +189,14 @@ __global__ void __launch_bounds__(ML_THREADS, 1) k_mla_decode(MlaArgs a) {
 
 // out[b][h][:] = sum over the live slices of partial * exp(m - M) / L; grid (n_heads, B), 128 threads x 4 dimensions
 __global__ void __launch_bounds__(128) k_mla_merge(float* __restrict__ out, const float* __restrict__ partial, const uint32_t* __restrict__ ctx_len,
-                                                   uint32_t n_heads, uint32_t n_splits, uint32_t split_tokens) {
+                                                   uint32_t n_heads, uint32_t n_splits, uint32_t split_tokens, const uint32_t* __restrict__ status) {
     const uint32_t h = blockIdx.x, b = blockIdx.y;
+    if (status && *status) {
+        // a wait in the tensor-core kernel ran out: the partials are not to be trusted, and the caller must see it
+        float* o = out + ((size_t)b * n_heads + h) * ML_V + threadIdx.x * 4;
+        o[0] = o[1] = o[2] = o[3] = __int_as_float(0x7FC00000);
+        return;
+    }
     const uint32_t ctx = ctx_len[b];
     const uint32_t live = ctx == 0 ? 0 : min(n_splits, (ctx + split_tokens - 1) / split_tokens);
     const float* base = partial + (((size_t)b * n_splits) * n_heads + h) * (ML_V + 2);
@@ -252,10 +260,22 @@ using namespace vb;
 
 extern "C" {
 
+static uint64_t mla_partial_bytes(uint32_t batch, uint32_t n_heads, uint32_t max_ctx, uint32_t split_tokens) {
+    const uint64_t n_splits = ((uint64_t)max_ctx + split_tokens - 1) / split_tokens;
+    const uint64_t b = (uint64_t)batch * (n_splits ? n_splits : 1) * n_heads * (ML_V + 2) * 4;
+    return (b + 1023) / 1024 * 1024;
+}
+
 uint64_t vb_op_mla_decode_scratch_bytes(uint32_t batch, uint32_t n_heads, uint32_t max_ctx, uint32_t split_tokens) {
     if (split_tokens == 0) split_tokens = 1024;
-    const uint64_t n_splits = ((uint64_t)max_ctx + split_tokens - 1) / split_tokens;
-    return (uint64_t)batch * (n_splits ? n_splits : 1) * n_heads * (ML_V + 2) * 4;
+    // the slices' partial outputs, then the tensor-core path's status word and bf16 copy of q
+    return mla_partial_bytes(batch, n_heads, max_ctx, split_tokens) + mla_tc_extra_scratch_bytes(batch, n_heads);
+}
+
+int32_t vb_op_mla_set_path(int32_t path) {
+    VB_REQUIRE(path == 0 || path == 1, "vb_op_mla_set_path: 0 (mma.sync kernel) or 1 (tcgen05 kernel)");
+    mla_use_tc = path == 1;
+    return VB_OK;
 }
 
 int32_t vb_op_mla_decode(float* out, const float* q, const void* latent_cache, const uint32_t* ctx_len, uint32_t batch, uint32_t n_heads,
@@ -279,9 +299,18 @@ int32_t vb_op_mla_decode(float* out, const float* q, const void* latent_cache, c
     a.cache_stride = cache_stride_rows; a.scale = scale;
     LaunchCfg lc;
     lc.stream = (cudaStream_t)stream;
+    if (mla_use_tc) {
+        // tcgen05 path: both products on the 5th-generation tensor cores (vb_mla_tc.cu)
+        void* extra = reinterpret_cast<unsigned char*>(scratch) + mla_partial_bytes(batch, n_heads, max_ctx, split_tokens);
+        VB_CUDA(mla_decode_tc(lc, q, latent_cache, ctx_len, (float*)scratch, extra, batch, n_heads, a.n_splits, split_tokens, cache_stride_rows, scale));
+        VB_CUDA(launch(lc, k_mla_merge, dim3(n_heads, batch), dim3(128), 0, out, (const float*)scratch, ctx_len, n_heads, a.n_splits, split_tokens,
+                       (const uint32_t*)extra));
+        return VB_OK;
+    }
     const dim3 grid(a.n_splits, (n_heads + ML_HEADS_PER_BLOCK - 1) / ML_HEADS_PER_BLOCK, batch);
     VB_CUDA(launch(lc, k_mla_decode, grid, dim3(ML_THREADS), ML_SMEM, a));
-    VB_CUDA(launch(lc, k_mla_merge, dim3(n_heads, batch), dim3(128), 0, out, (const float*)scratch, ctx_len, n_heads, a.n_splits, split_tokens));
+    VB_CUDA(launch(lc, k_mla_merge, dim3(n_heads, batch), dim3(128), 0, out, (const float*)scratch, ctx_len, n_heads, a.n_splits, split_tokens,
+                   (const uint32_t*)nullptr));
     return VB_OK;
 }
 

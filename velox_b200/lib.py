@@ -106,6 +106,7 @@ SIGNATURES = {
     "vb_op_swiglu": (_i32, [_vp] * 5 + [_u32, _u32, _vp, _u64, _vp]),
     "vb_op_mla_absorbed": (_i32, [_vp] * 7 + [_u32] * 4 + [_f32, _vp, _u64, _vp]),
     "vb_op_mla_decode_scratch_bytes": (_u64, [_u32] * 4),
+    "vb_op_mla_set_path": (_i32, [_i32]),
     "vb_op_mla_decode": (_i32, [_vp] * 4 + [_u32, _u32, _u32, _u64, _f32, _u32, _vp, _u64, _vp]),
     "vb_op_mla_latent_append": (_i32, [_vp, _vp, _vp, _u32, _u64, _vp]),
     "vb_op_mla_head_product": (_i32, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _i32, _vp]),
