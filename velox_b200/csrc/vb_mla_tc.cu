@@ -35,15 +35,18 @@ namespace {
 constexpr int MT_LAT = 576, MT_V = 512;
 constexpr int MT_M = 128;                 // heads per block = tensor-memory lanes
 constexpr int MT_T = 32;                  // tokens per tile
+constexpr int MT_NBUF = 2;                // tile buffers in flight
+constexpr int MT_NP = 1;                  // probability buffers
 constexpr int MT_KB = MT_LAT / 64;        // nine column blocks of 64 elements (128 bytes)
 constexpr int MT_DH = 256;                // output dimensions per block
 constexpr int MT_Q_BYTES = MT_KB * MT_M * 128;   // 147,456
-constexpr int MT_L_BYTES = MT_KB * MT_T * 128;   // 36,864 per buffer
-constexpr int MT_P_BYTES = MT_M * MT_T * 2;      // 8,192
+constexpr int MT_L_BYTES = MT_KB * MT_T * 128;   // per tile buffer
+constexpr int MT_P_BYTES = MT_M * MT_T * 2;      // per probability buffer
 constexpr int MT_BAR_BYTES = 256;
-constexpr int MT_SMEM = MT_Q_BYTES + 2 * MT_L_BYTES + MT_P_BYTES + MT_BAR_BYTES + 1024;
+constexpr int MT_SMEM = MT_Q_BYTES + MT_NBUF * MT_L_BYTES + MT_NP * MT_P_BYTES + MT_BAR_BYTES + 1024;
+static_assert(MT_SMEM <= 232448, "shared memory of one block");
 constexpr int MT_THREADS = 192;
-constexpr uint32_t MT_TMEM_COLS = 512;    // S: 2 x 32 columns at 0, O: 256 columns at 64 (allocation sizes are powers of two)
+constexpr uint32_t MT_TMEM_COLS = 512;    // S: 2 x MT_T columns at 0, O: 256 columns at 64 (allocation sizes are powers of two)
 constexpr float MT_LAZY = 8.0f;
 
 // instruction descriptors, kind::f16: fp32 accumulate (bit 4), A and B bf16 (1 at bits 7 and 10), N >> 3 at bit 17,
@@ -141,19 +144,19 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t q_s = base, l_s = base + MT_Q_BYTES, p_s = l_s + 2 * MT_L_BYTES, bars = p_s + MT_P_BYTES;
-    // barriers (8 bytes each): 0 q_full, 1-2 l_full, 3-4 l_empty, 5-6 s_full, 7-8 s_free, 9 p_full, 10 p_free, 11 o_full
+    constexpr uint32_t L_OFF = MT_Q_BYTES, P_OFF = L_OFF + MT_NBUF * MT_L_BYTES, BAR_OFF = P_OFF + MT_NP * MT_P_BYTES;
+    const uint32_t q_s = base, l_s = base + L_OFF, p_s = base + P_OFF, bars = base + BAR_OFF;
+    // barriers (8 bytes each)
+    constexpr int B_QFULL = 0, B_LFULL = 1, B_LEMPTY = B_LFULL + MT_NBUF, B_SFULL = B_LEMPTY + MT_NBUF, B_SFREE = B_SFULL + 2,
+                  B_PFULL = B_SFREE + 2, B_OFULL = B_PFULL + 2, B_COUNT = B_OFULL + 1;
+    static_assert(B_COUNT * 8 + 8 <= MT_BAR_BYTES, "barrier area");
     auto bar = [&](int i) { return bars + 8u * (uint32_t)i; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + MT_Q_BYTES + 2 * MT_L_BYTES + MT_P_BYTES + 12 * 8);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + BAR_OFF + B_COUNT * 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        mbar_init(bar(0), 1);
-        for (int i = 1; i <= 6; ++i) mbar_init(bar(i), 1);
-        mbar_init(bar(7), 4); mbar_init(bar(8), 4);   // the four softmax warps
-        mbar_init(bar(9), 4);
-        mbar_init(bar(10), 1); mbar_init(bar(11), 1);
+        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_SFREE && i < B_OFULL) ? 4 : 1);  // s_free, p_full: the four softmax warps
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -168,59 +171,62 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_o = tmem + 64;
 
+    // Tile i lives in ring slot i % MT_NBUF; its S in S buffer i & 1, its probabilities in P buffer i % MT_NP.
+    // Completion counts: l_full[slot] and l_empty[slot] once per MT_NBUF tiles, the others once per 2 tiles.
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer: Q once, then the latent tiles -------------------------------------------------------------
-            mbar_expect_tx(bar(0), MT_Q_BYTES);
+            mbar_expect_tx(bar(B_QFULL), MT_Q_BYTES);
             const int q_row = (int)(b * p.q_rows_per_seq + hb * MT_M);
-            for (int kb = 0; kb < MT_KB; ++kb) tma_2d(q_s + kb * (MT_M * 128), &map_q, kb * 64, q_row, bar(0));
+            for (int kb = 0; kb < MT_KB; ++kb) tma_2d(q_s + kb * (MT_M * 128), &map_q, kb * 64, q_row, bar(B_QFULL));
             const long long row0 = (long long)b * (long long)p.cache_stride + t_lo;
             for (uint32_t i = 0; i < n_tiles; ++i) {
-                const uint32_t buf = i & 1;
-                if (i >= 2 && !wait_abort(bar(3 + buf), ((i >> 1) + 1) & 1, abort_flag)) break;  // P . L of tile i-2 is done
-                mbar_expect_tx(bar(1 + buf), MT_L_BYTES);
+                const uint32_t slot = i % MT_NBUF, round = i / MT_NBUF;
+                if (round >= 1 && !wait_abort(bar(B_LEMPTY + slot), (round + 1) & 1, abort_flag)) break;  // P . L of tile i - MT_NBUF is done
+                mbar_expect_tx(bar(B_LFULL + slot), MT_L_BYTES);
                 const int y = (int)(row0 + (long long)i * MT_T);
-                for (int kb = 0; kb < MT_KB; ++kb) tma_2d(l_s + buf * MT_L_BYTES + kb * (MT_T * 128), &map_l, kb * 64, y, bar(1 + buf));
+                for (int kb = 0; kb < MT_KB; ++kb) tma_2d(l_s + slot * MT_L_BYTES + kb * (MT_T * 128), &map_l, kb * 64, y, bar(B_LFULL + slot));
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- tensor-core issue --------------------------------------------------------------------------------
             auto issue_s = [&](uint32_t i) {
-                const uint32_t buf = i & 1;
-                const uint32_t lt = l_s + buf * MT_L_BYTES;
+                const uint32_t lt = l_s + (i % MT_NBUF) * MT_L_BYTES;
 #pragma unroll 1
                 for (int kb = 0; kb < MT_KB; ++kb) {
                     const uint64_t da = desc_k_sw128(q_s + kb * (MT_M * 128)), db = desc_k_sw128(lt + kb * (MT_T * 128));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) mma_bf16_ss(tmem + buf * MT_T, da + 2u * k, db + 2u * k, MT_IDESC_S, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k) mma_bf16_ss(tmem + (i & 1) * MT_T, da + 2u * k, db + 2u * k, MT_IDESC_S, (kb | k) != 0 ? 1u : 0u);
                 }
-                commit_to(bar(5 + buf));
+                commit_to(bar(B_SFULL + (i & 1)));
             };
-            bool ok = wait_abort(bar(0), 0u, abort_flag) && wait_abort(bar(1), 0u, abort_flag);
-            if (ok) {
+            // may S of tile i be issued?  its rows have landed and the softmax of tile i - 2 has read the S buffer
+            auto ready_s = [&](uint32_t i) {
+                if (!wait_abort(bar(B_LFULL + i % MT_NBUF), (i / MT_NBUF) & 1, abort_flag)) return false;
+                if (i >= 2 && !wait_abort(bar(B_SFREE + (i & 1)), ((i >> 1) + 1) & 1, abort_flag)) return false;
                 fence_after();
+                return true;
+            };
+            bool ok = wait_abort(bar(B_QFULL), 0u, abort_flag) && ready_s(0);
+            if (ok) {
                 issue_s(0);
                 for (uint32_t i = 0; i < n_tiles; ++i) {
                     if (i + 1 < n_tiles) {
-                        const uint32_t nb = (i + 1) & 1;
-                        if (!wait_abort(bar(1 + nb), ((i + 1) >> 1) & 1, abort_flag)) break;
-                        if (i + 1 >= 2 && !wait_abort(bar(7 + nb), (((i + 1) >> 1) + 1) & 1, abort_flag)) break;  // S buffer read by the softmax of tile i-1
-                        fence_after();
+                        if (!ready_s(i + 1)) break;
                         issue_s(i + 1);
                     }
-                    if (!wait_abort(bar(9), i & 1, abort_flag)) break;  // probabilities of tile i are in shared memory
+                    if (!wait_abort(bar(B_PFULL + (i & 1)), (i >> 1) & 1, abort_flag)) break;  // probabilities of tile i are in shared memory
                     fence_after();
-                    const uint32_t lt = l_s + (i & 1) * MT_L_BYTES + dh * 4 * (MT_T * 128);
+                    const uint32_t lt = l_s + (i % MT_NBUF) * MT_L_BYTES + dh * 4 * (MT_T * 128);
 #pragma unroll
                     for (int kk = 0; kk < MT_T / 16; ++kk) {
-                        const uint64_t da = desc_k_plain(p_s + kk * 256, 128, 512);
+                        const uint64_t da = desc_k_plain(p_s + (i % MT_NP) * MT_P_BYTES + kk * 256, 128, MT_T * 16);
                         const uint64_t db = desc_mn_sw128(lt + kk * 2048, MT_T * 128);
                         mma_bf16_ss(tmem_o, da, db, MT_IDESC_O, (i | (uint32_t)kk) != 0 ? 1u : 0u);
                     }
-                    commit_to(bar(3 + (i & 1)));
-                    commit_to(bar(10));
-                    if (i + 1 == n_tiles) commit_to(bar(11));
+                    commit_to(bar(B_LEMPTY + i % MT_NBUF));  // the slot, and the P buffer, of tile i are free
+                    if (i + 1 == n_tiles) commit_to(bar(B_OFULL));
                 }
             }
         }
@@ -231,20 +237,21 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t lane_addr = (lg * 32u) << 16;
         float m_use = -INFINITY, l_run = 0.0f;
         bool ok = true;
+        // has P . L of tile j completed?  (its slot's l_empty barrier; at most one completion behind or ahead of the caller)
+        auto pv_done = [&](uint32_t j) { return warp_wait(bar(B_LEMPTY + j % MT_NBUF), (j / MT_NBUF) & 1, abort_flag); };
         for (uint32_t i = 0; i < n_tiles && ok; ++i) {
-            const uint32_t buf = i & 1;
-            ok = warp_wait(bar(5 + buf), (i >> 1) & 1, abort_flag);
+            ok = warp_wait(bar(B_SFULL + (i & 1)), (i >> 1) & 1, abort_flag);
             if (!ok) break;
             fence_after();
             float s[32];
-            tmem_ld32(tmem + lane_addr + buf * MT_T, s);
+            tmem_ld32(tmem + lane_addr + (i & 1) * MT_T, s);   // 32 columns read, the first MT_T are this tile's
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(7 + buf));
+            if (lane == 0) mbar_arrive(bar(B_SFREE + (i & 1)));
             const uint32_t valid = min((uint32_t)MT_T, n_tok - i * MT_T);
             float mx = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < MT_T; ++j) {
                 s[j] = (uint32_t)j < valid ? s[j] * p.scale : -INFINITY;
                 mx = fmaxf(mx, s[j]);
             }
@@ -252,55 +259,57 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             const bool move = mx > m_use + MT_LAZY || i == 0;
             const float m_new = move ? mx : m_use;
             const float alpha = move ? (i == 0 ? 0.0f : __expf(m_use - m_new)) : 1.0f;
-            uint32_t packed[16];
+            uint32_t packed[MT_T / 2];
             float sum = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < MT_T / 2; ++j) {
                 const __nv_bfloat162 pr = __floats2bfloat162_rn(__expf(s[2 * j] - m_new), __expf(s[2 * j + 1] - m_new));
                 sum += __bfloat162float(pr.x) + __bfloat162float(pr.y);  // the rounded values: numerator and denominator agree
                 packed[j] = *reinterpret_cast<const uint32_t*>(&pr);
             }
             l_run = l_run * alpha + sum;
             m_use = m_new;
-            if (i >= 1) {
-                ok = warp_wait(bar(10), (i + 1) & 1, abort_flag);  // P . L of tile i-1 is done: P and O are ours
+            if (i >= 1 && __any_sync(0xFFFFFFFFu, move)) {
+                // rescale this warp's 32 rows of O (256 columns) once every product issued so far is done; lanes that did
+                // not move multiply by 1
+                ok = pv_done(i - 1);
                 if (!ok) break;
                 fence_after();
-                if (__any_sync(0xFFFFFFFFu, move)) {
-                    // rescale this warp's 32 rows of O (256 columns); lanes that did not move multiply by 1
 #pragma unroll 1
-                    for (int c = 0; c < MT_DH / 32; ++c) {
-                        float o[32];
-                        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+                for (int c = 0; c < MT_DH / 32; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_addr + c * 32, o);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                        tmem_st32(tmem_o + lane_addr + c * 32, o);
-                    }
-                    tmem_st_wait();
+                    for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                    tmem_st32(tmem_o + lane_addr + c * 32, o);
                 }
+                tmem_st_wait();
+            } else if (i >= (uint32_t)MT_NP) {
+                ok = pv_done(i - MT_NP);  // the P buffer of this tile was read by the product of tile i - MT_NP
+                if (!ok) break;
             }
             if (valid < (uint32_t)MT_T) {
                 // the last tile: rows past the context's end hold whatever followed in the cache; zero them for P . L
                 // (the tile has landed: S of this tile was computed from it)
-                const uint32_t lt = (uint32_t)(MT_Q_BYTES + buf * MT_L_BYTES) + dh * 4 * (MT_T * 128);
+                const uint32_t lt = L_OFF + (i % MT_NBUF) * MT_L_BYTES + dh * 4 * (MT_T * 128);
                 const uint32_t n_zero = (MT_T - valid) * 4 * 8;  // (row, column block, 16-byte piece)
                 for (uint32_t z = (warp - 2) * 32 + lane; z < n_zero; z += 128) {
                     const uint32_t piece = z & 7, cb = (z >> 3) & 3, r = valid + (z >> 5);
                     *reinterpret_cast<uint4*>(gen + lt + cb * (MT_T * 128) + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            // P row: 32 bf16 = four 16-byte pieces, piece c of row r at (r / 8) * 512 + c * 128 + (r % 8) * 16
-            unsigned char* prow = gen + MT_Q_BYTES + 2 * MT_L_BYTES + (row >> 3) * 512 + (row & 7) * 16;
+            // P row: MT_T bf16 = MT_T / 8 16-byte pieces, piece c of row r at (r / 8) * (MT_T * 16) + c * 128 + (r % 8) * 16
+            unsigned char* prow = gen + P_OFF + (i % MT_NP) * MT_P_BYTES + (row >> 3) * (MT_T * 16) + (row & 7) * 16;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < MT_T / 8; ++c)
                 *reinterpret_cast<uint4*>(prow + c * 128) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(9));
+            if (lane == 0) mbar_arrive(bar(B_PFULL + (i & 1)));
         }
         // ---- this slice's unnormalised output, maximum in use and sum ------------------------------------------------
-        if (ok) ok = warp_wait(bar(11), 0u, abort_flag);
+        if (ok) ok = warp_wait(bar(B_OFULL), 0u, abort_flag);
         if (ok) {
             fence_after();
             const uint32_t h = hb * MT_M + row;
