@@ -7,21 +7,28 @@
 //
 // One block = 128 heads (the tensor-memory lanes) x one slice of the context x one half of the 512 output dimensions
 // (O needs 128 lanes x 512 fp32 columns = all of tensor memory, so two blocks split the columns and each computes S
-// for itself).  Per 32-token tile:
-//   * warp 0 (one lane): tiled TMA brings the tile in as nine [32 rows][64 columns] boxes with the 128-byte swizzle
-//     (two buffers); Q, converted to bf16 once by a small kernel, came in the same way as nine [128][64] boxes;
-//   * warp 1 (one lane): S = Q . L^T -- 36 tcgen05.mma kind::f16 (bf16 operands, M 128, N 32, K 16), both operands
-//     K-major -- into one of two 32-column S buffers; later O += P . L[:, half] -- 2 instructions (M 128, N 256, K 16)
-//     with P from shared memory (8x16-byte core matrices, no swizzle) and the SAME staged tile as the B operand, read
+// for itself).  Per 16-token tile:
+//   * warp 0 (one lane): tiled TMA brings the tile in as nine [16 rows][64 columns] boxes with the 128-byte swizzle
+//     (ring of four); Q, converted to bf16 once by a small kernel, came in the same way as nine [128][64] boxes;
+//   * three issuing warps (one lane each): S = Q . L^T -- 36 tcgen05.mma kind::f16 (bf16 operands, M 128, N 16, K 16,
+//     both operands K-major from shared memory), twelve per issuer into its own partial sum.  One thread gets about
+//     64 clocks per instruction whatever its N (measured: 1.2 us for the 36 of a tile at N = 16 and at N = 32, from
+//     shared or tensor memory alike), so the instructions are shared out; the first issuer also does O += P . L[:, half]
+//     -- one instruction (M 128, N 256, K 16) with P read FROM TENSOR MEMORY (bf16 pairs written by the softmax warps
+//     with tcgen05.st: no shared-memory round trip, no proxy fence) and the SAME staged tile as the B operand, read
 //     MN-major this time (tokens are K): no transposed copy of the latent rows exists anywhere;
-//   * warps 2-5 (128 threads, one head row = one tensor-memory lane each): read their S row (tcgen05.ld), running
-//     maximum and sum without any shuffle, probabilities to bf16 into shared memory.  The maximum is lazy: O is
-//     rescaled (tcgen05.ld / st of 256 columns) only when a tile's maximum exceeds the one in use by more than 8, so
-//     that probabilities stay below e^8 and almost every tile skips the rescale.
-// S of tile i+1 is issued before the softmax of tile i is done; every hand-over is an mbarrier with a bounded wait and
-// a block-wide abort flag (a wait that runs out sets a status word at the head of the scratch area: the merge kernel
-// then fills the output with NaN).  Rows of the last tile past the end of the context are zeroed in shared memory
-// before P . L (their probabilities are 0, but 0 x garbage must not be NaN).
+//   * warps 2-5 (128 threads, one head row = one tensor-memory lane each): read their S row (tcgen05.ld, the three
+//     partial sums), running maximum and sum without any shuffle, probabilities to bf16 into tensor memory.  The
+//     maximum is lazy: O is rescaled (tcgen05.ld / st of 256 columns) only when a tile's maximum exceeds the one in
+//     use by more than 8, so that probabilities stay below e^8 and almost every tile skips the rescale.
+// S of tile i+1 is issued before the softmax of tile i is done (two S and two P buffers); every hand-over is an
+// mbarrier with a bounded wait and a block-wide abort flag (a wait that runs out sets a status word at the head of the
+// scratch area: the merge kernel then fills the output with NaN).  Rows of the last tile past the end of the context
+// are zeroed in shared memory before P . L (their probabilities are 0, but 0 x garbage must not be NaN).
+// Tried on the way (same workload, 64 sequences of 1024..8192 tokens): 32-token tiles with two slots and P in shared
+// memory 0.49 ms; Q in tensor memory as the A operand with a four-way split of the output columns and a five-slot
+// ring 0.66 ms (the S product is no faster from tensor memory and is computed four times); one issuer 0.49, two 0.44,
+// three 0.44; P in tensor memory 0.41 ms.  The mma.sync kernel of vb_mla_decode.cu takes 0.65 ms.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -34,19 +41,26 @@ namespace {
 
 constexpr int MT_LAT = 576, MT_V = 512;
 constexpr int MT_M = 128;                 // heads per block = tensor-memory lanes
-constexpr int MT_T = 32;                  // tokens per tile
-constexpr int MT_NBUF = 2;                // tile buffers in flight
-constexpr int MT_NP = 1;                  // probability buffers
+constexpr int MT_T = 16;                  // tokens per tile
+constexpr int MT_NBUF = 4;                // tile buffers in flight
+constexpr int MT_NP = 2;                  // probability buffers
 constexpr int MT_KB = MT_LAT / 64;        // nine column blocks of 64 elements (128 bytes)
 constexpr int MT_DH = 256;                // output dimensions per block
 constexpr int MT_Q_BYTES = MT_KB * MT_M * 128;   // 147,456
 constexpr int MT_L_BYTES = MT_KB * MT_T * 128;   // per tile buffer
 constexpr int MT_P_BYTES = MT_M * MT_T * 2;      // per probability buffer
 constexpr int MT_BAR_BYTES = 256;
-constexpr int MT_SMEM = MT_Q_BYTES + MT_NBUF * MT_L_BYTES + MT_NP * MT_P_BYTES + MT_BAR_BYTES + 1024;
+constexpr int MT_SMEM = MT_Q_BYTES + MT_NBUF * MT_L_BYTES + MT_BAR_BYTES + 1024;
 static_assert(MT_SMEM <= 232448, "shared memory of one block");
-constexpr int MT_THREADS = 192;
-constexpr uint32_t MT_TMEM_COLS = 512;    // S: 2 x MT_T columns at 0, O: 256 columns at 64 (allocation sizes are powers of two)
+constexpr int MT_NI = 3;                  // warps that issue the S product (each its own column blocks and partial sum): one thread
+                                          // gets ~64 clocks per tcgen05.mma whatever its N, so 36 of them per tile are shared out
+constexpr int MT_THREADS = 192 + 32 * (MT_NI - 1);
+constexpr uint32_t MT_TMEM_COLS = 512;    // S: 2 buffers x MT_NI partial sums x MT_T columns at 0, then O: 256 columns (allocation sizes are powers of two)
+constexpr uint32_t MT_TM_P = 2 * MT_NI * MT_T;          // probabilities as bf16 pairs: MT_NP buffers of MT_T / 2 columns
+constexpr uint32_t MT_TM_O = MT_TM_P + 32;              // (room for two buffers of 16 columns)
+static_assert(MT_NP * MT_T / 2 <= 32 && MT_T == 16, "probability buffers in tensor memory (the store below writes 8 columns)");
+static_assert(MT_TM_O + MT_DH <= MT_TMEM_COLS && MT_KB % MT_NI == 0, "tensor memory columns / column blocks per issuer");
+constexpr int MT_KB_I = MT_KB / MT_NI;    // column blocks per issuer
 constexpr float MT_LAZY = 8.0f;
 
 // instruction descriptors, kind::f16: fp32 accumulate (bit 4), A and B bf16 (1 at bits 7 and 10), N >> 3 at bit 17,
@@ -74,6 +88,15 @@ __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int
 __device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                  ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+// A from tensor memory (lane = row, two bf16 of K per 32-bit column), B from shared memory
+__device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st8u(uint32_t taddr, const uint32_t r[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
 __device__ __forceinline__ void commit_to(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -144,8 +167,8 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     extern __shared__ unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     unsigned char* gen = smem_raw + (base - smem_u32(smem_raw));
-    constexpr uint32_t L_OFF = MT_Q_BYTES, P_OFF = L_OFF + MT_NBUF * MT_L_BYTES, BAR_OFF = P_OFF + MT_NP * MT_P_BYTES;
-    const uint32_t q_s = base, l_s = base + L_OFF, p_s = base + P_OFF, bars = base + BAR_OFF;
+    constexpr uint32_t L_OFF = MT_Q_BYTES, BAR_OFF = L_OFF + MT_NBUF * MT_L_BYTES;
+    const uint32_t q_s = base, l_s = base + L_OFF, bars = base + BAR_OFF;
     // barriers (8 bytes each)
     constexpr int B_QFULL = 0, B_LFULL = 1, B_LEMPTY = B_LFULL + MT_NBUF, B_SFULL = B_LEMPTY + MT_NBUF, B_SFREE = B_SFULL + 2,
                   B_PFULL = B_SFREE + 2, B_OFULL = B_PFULL + 2, B_COUNT = B_OFULL + 1;
@@ -156,7 +179,8 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_SFREE && i < B_OFULL) ? 4 : 1);  // s_free, p_full: the four softmax warps
+        // s_free, p_full: the four softmax warps; s_full: the issuers of S
+        for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_SFREE && i < B_OFULL) ? 4 : ((i >= B_SFULL && i < B_SFREE) ? MT_NI : 1));
         *abort_flag = 0u;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -169,7 +193,7 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     __syncthreads();
     fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_o = tmem + 64;
+    const uint32_t tmem_o = tmem + MT_TM_O;
 
     // Tile i lives in ring slot i % MT_NBUF; its S in S buffer i & 1, its probabilities in P buffer i % MT_NP.
     // Completion counts: l_full[slot] and l_empty[slot] once per MT_NBUF tiles, the others once per 2 tiles.
@@ -194,10 +218,10 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             auto issue_s = [&](uint32_t i) {
                 const uint32_t lt = l_s + (i % MT_NBUF) * MT_L_BYTES;
 #pragma unroll 1
-                for (int kb = 0; kb < MT_KB; ++kb) {
+                for (int kb = 0; kb < MT_KB_I; ++kb) {
                     const uint64_t da = desc_k_sw128(q_s + kb * (MT_M * 128)), db = desc_k_sw128(lt + kb * (MT_T * 128));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) mma_bf16_ss(tmem + (i & 1) * MT_T, da + 2u * k, db + 2u * k, MT_IDESC_S, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k) mma_bf16_ss(tmem + (i & 1) * MT_NI * MT_T, da + 2u * k, db + 2u * k, MT_IDESC_S, (kb | k) != 0 ? 1u : 0u);
                 }
                 commit_to(bar(B_SFULL + (i & 1)));
             };
@@ -221,13 +245,32 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     const uint32_t lt = l_s + (i % MT_NBUF) * MT_L_BYTES + dh * 4 * (MT_T * 128);
 #pragma unroll
                     for (int kk = 0; kk < MT_T / 16; ++kk) {
-                        const uint64_t da = desc_k_plain(p_s + (i % MT_NP) * MT_P_BYTES + kk * 256, 128, MT_T * 16);
                         const uint64_t db = desc_mn_sw128(lt + kk * 2048, MT_T * 128);
-                        mma_bf16_ss(tmem_o, da, db, MT_IDESC_O, (i | (uint32_t)kk) != 0 ? 1u : 0u);
+                        mma_bf16_ts(tmem_o, tmem + MT_TM_P + (i % MT_NP) * (MT_T / 2) + kk * 8, db, MT_IDESC_O, (i | (uint32_t)kk) != 0 ? 1u : 0u);
                     }
                     commit_to(bar(B_LEMPTY + i % MT_NBUF));  // the slot, and the P buffer, of tile i are free
                     if (i + 1 == n_tiles) commit_to(bar(B_OFULL));
                 }
+            }
+        }
+    } else if (warp >= 6) {
+        if (lane == 0) {
+            // ---- further issuers: their column blocks of the S product into their own partial sums --------------------------
+            const int q = (int)warp - 5;  // 1 .. MT_NI - 1
+            bool ok = wait_abort(bar(B_QFULL), 0u, abort_flag);
+            for (uint32_t i = 0; i < n_tiles && ok; ++i) {
+                if (!wait_abort(bar(B_LFULL + i % MT_NBUF), (i / MT_NBUF) & 1, abort_flag)) break;
+                if (i >= 2 && !wait_abort(bar(B_SFREE + (i & 1)), ((i >> 1) + 1) & 1, abort_flag)) break;
+                fence_after();
+                const uint32_t lt = l_s + (i % MT_NBUF) * MT_L_BYTES;
+#pragma unroll 1
+                for (int kb = q * MT_KB_I; kb < (q + 1) * MT_KB_I; ++kb) {
+                    const uint64_t da = desc_k_sw128(q_s + kb * (MT_M * 128)), db = desc_k_sw128(lt + kb * (MT_T * 128));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_bf16_ss(tmem + ((i & 1) * MT_NI + q) * MT_T, da + 2u * k, db + 2u * k, MT_IDESC_S, (kb > q * MT_KB_I || k != 0) ? 1u : 0u);
+                }
+                commit_to(bar(B_SFULL + (i & 1)));
             }
         }
     } else {
@@ -244,7 +287,14 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             if (!ok) break;
             fence_after();
             float s[32];
-            tmem_ld32(tmem + lane_addr + (i & 1) * MT_T, s);   // 32 columns read, the first MT_T are this tile's
+            tmem_ld32(tmem + lane_addr + (i & 1) * MT_NI * MT_T, s);   // the issuers' partial sums
+#pragma unroll 1
+            for (int q = 1; q < MT_NI; ++q) {
+                float s2[32];
+                tmem_ld32(tmem + lane_addr + ((i & 1) * MT_NI + q) * MT_T, s2);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) s[c] += s2[c];
+            }
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_SFREE + (i & 1)));
@@ -297,13 +347,11 @@ k_mla_decode_tc(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                     const uint32_t piece = z & 7, cb = (z >> 3) & 3, r = valid + (z >> 5);
                     *reinterpret_cast<uint4*>(gen + lt + cb * (MT_T * 128) + r * 128 + piece * 16) = make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic stores, read by the tensor core
             }
-            // P row: MT_T bf16 = MT_T / 8 16-byte pieces, piece c of row r at (r / 8) * (MT_T * 16) + c * 128 + (r % 8) * 16
-            unsigned char* prow = gen + P_OFF + (i % MT_NP) * MT_P_BYTES + (row >> 3) * (MT_T * 16) + (row & 7) * 16;
-#pragma unroll
-            for (int c = 0; c < MT_T / 8; ++c)
-                *reinterpret_cast<uint4*>(prow + c * 128) = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P row: MT_T bf16 as pairs into this lane's columns of the probability buffer (the A operand of P . L)
+            tmem_st8u(tmem + lane_addr + MT_TM_P + (i % MT_NP) * (MT_T / 2), packed);
+            tmem_st_wait();
             fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_PFULL + (i & 1)));
