@@ -316,8 +316,11 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
                                         "operand conversion and the last token's decode-path step)"}}
     eng.build_graph()
     qd_, kd_ = spec.n_q_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
+    # decode batches over int8 weights read the stored bytes (k_gemm_i8); only with that path switched off do they read
+    # resident fp16 copies of the layer matrices, 2 bytes per weight where the algorithm counts 1
+    i8_off = any(kv.replace(" ", "") == "decode_gemm_i8=0" for kv in args.set)
     tc_extra_bytes = (spec.d_model * (qd_ + 2 * kd_) + qd_ * spec.d_model + 3 * spec.ffn_dim * spec.d_model) * spec.n_layers \
-        if "int8" in spec.name else 0
+        if "int8" in spec.name and i8_off else 0
 
     # ---- device-resident timing: K graph replays between CUDA events on the library's stream ----------
     sampler = ClockSampler(R.local_rank)
@@ -384,11 +387,12 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
                    "gemv_path": args.gemv_path, "replicas": groups, "tensor_parallel": world if sharded else 1,
                    "tp_exchange": (args.tp_exchange if sharded and world > 1 else None)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     # dram read+write of one step: ncu on the 4-layer case of this workload measured 1.006x the
-                     # algorithmic bytes per layer, and every layer is the same five kernels; scaled by depth
-                     # (batch >= 16 with int8 weights: the decode products read resident fp16 copies of the layer
-                     # matrices, 2 bytes per weight where the algorithm counts 1 -- added to the traffic figure)
-                     "traffic": int(step_bytes * 1.006) + (tc_extra_bytes if batch >= 16 and not tp else 0), "peak_kind": peak_kind,
+                     # dram read+write of one step: ncu on the 4-layer case of the batch-1 workload measured 1.006x the
+                     # algorithmic bytes per layer, on the 2-layer case of the batch-32 workload 1.03x (products 1.01x,
+                     # attention 1.12x: block tables, queries, split partials); every layer is the same kernels, so the
+                     # ratio is applied to the full depth
+                     "traffic": int(step_bytes * (1.03 if batch >= 16 else 1.006)) + (tc_extra_bytes if batch >= 16 and not tp else 0),
+                     "peak_kind": peak_kind,
                      "frac_of_8TBs": achieved / 8000.0,
                      "kernel": "decode step (one CUDA-graph launch = one token)" + (", per GPU" if tp else ""),
                      "bytes_per_launch": step_bytes},
