@@ -570,7 +570,7 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
         // wide batches already fill the SMs with (sequence, KV head) pairs: fewer, longer slices per pair then stream the
         // cache instead of paying a block's fixed costs (table fetch, cluster merge) for every ~150 rows
         const uint32_t g = c->hq / c->hkv, pairs = d.max_batch * c->hkv * ((g + 7) / 8);
-        const uint32_t fit = pairs ? (2u * 148u) / pairs : 8u;
+        const uint32_t fit = pairs ? 148u / pairs : 8u;  // one block per SM: two 128-token staging buffers take most of its shared memory
         if (c->n_splits > (fit ? fit : 1u)) c->n_splits = fit ? fit : 1u;
     }
     c->tokens_per_split = attn_tokens_per_split(d.max_seq_len);
