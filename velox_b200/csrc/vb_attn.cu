@@ -31,6 +31,9 @@
 #include <stdlib.h>
 
 #include "vb_internal.cuh"
+#include <cuda.h>
+#include <string.h>
+
 #include "vb_kernels.cuh"
 #include "vb_tma.cuh"
 
@@ -51,6 +54,7 @@ struct AttnKArgs {
     size_t kv_batch_stride;  // contiguous: elements between sequences
     uint32_t inv_freq_n;     // > 0: the rotary frequencies below are valid
     float inv_freq[256];     // [D/2], in parameter space: no memory trip before the angles can be computed
+    alignas(64) CUtensorMap kv_map;  // tensor-core path: the paged pool as [token rows][D]
 };
 
 template <typename KVT, int EPL>
@@ -144,7 +148,11 @@ struct AttnSmem {
     static constexpr int D = EPL * 32;
     // staged row stride in elements: the tensor-core path pads rows by 16 bytes so that the 8 rows of an
     // ldmatrix tile fall into different banks
-    static constexpr int RS = D + (MMA ? 8 : 0);
+    static constexpr int RS = D;
+    // Tensor-core path: a staged chunk is [K|V][64-column half][CH tokens][128 bytes] with the 128-byte swizzle (what a
+    // tiled TMA copy of [16 tokens][64 columns] writes): the 16-byte piece c of row r sits at piece c ^ (r & 7), so the 8
+    // rows of an ldmatrix tile fall into different banks without padding, and one copy moves a KV block's 16 rows.
+    static constexpr int HALVES = D / 64;
     // tokens per staged chunk: K+V of a chunk take at most 32 KB, at most 64 tokens; tensor-core path: up to 64 KB and
     // 128 tokens, a 16-token tile for each of the 8 warps (with 64 only four warps had work between two block-wide
     // barriers: batch 1 went 1.349 -> 1.300 ms per token, batch 32 3.55 -> 3.46 ms per step)
@@ -153,15 +161,16 @@ struct AttnSmem {
     static constexpr int CH = CH_FIT > CH_CAP ? CH_CAP : CH_FIT;
     static constexpr size_t kv_bytes = (size_t)2 * 2 * CH * RS * sizeof(KVT);  // [buffer][K|V][CH][RS]
     static constexpr size_t acc_bytes = (size_t)ATTN_WARPS * GM * D * sizeof(float);
-    static constexpr size_t total = kv_bytes + acc_bytes;
+    static constexpr size_t total = kv_bytes + acc_bytes + (MMA ? 1024 : 0);  // tensor-core path: staging aligned to 1024 bytes
 };
 
 template <typename KVT, int EPL, int GM, bool MMA>
-__global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
+__global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_constant__ AttnKArgs ka) {
     const AttnArgs& a = ka.a;
     using SM = AttnSmem<KVT, EPL, GM, MMA>;
     constexpr int D = EPL * 32, CH = SM::CH, RS = SM::RS;
-    static_assert(!MMA || sizeof(KVT) == 2, "the tensor-core path reads an fp16 cache");
+    static_assert(!MMA || (sizeof(KVT) == 2 && D % 64 == 0), "the tensor-core path reads an fp16 cache in 64-column halves");
+    constexpr int HV = MMA ? SM::HALVES : 1;
     constexpr int TCH = MMA ? 1 : ((EPL >= 8) ? 2 : ((GM >= 8) ? 4 : 8));  // scalar path: tokens a warp handles at once
     constexpr int NV = TCH * GM;                              // partial dot products per lane (<= 32)
     constexpr int ROW16 = D * sizeof(KVT) / 16;               // 16-byte pieces per K or V row
@@ -175,8 +184,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
     __shared__ int32_t blk_s[ATTN_SPEC_BLOCKS];             // the sequence's block-table row (short tables only)
     __shared__ __align__(16) KVT new_kv[2][D];  // the appended token's K and V (fused mode)
     extern __shared__ __align__(16) unsigned char dyn_smem[];
-    KVT* kv_s = reinterpret_cast<KVT*>(dyn_smem);
-    float* part_acc = reinterpret_cast<float*>(dyn_smem + SM::kv_bytes);  // [ATTN_WARPS][GM][D]
+    unsigned char* dyn_base = MMA ? dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u) : dyn_smem;
+    KVT* kv_s = reinterpret_cast<KVT*>(dyn_base);
+    float* part_acc = reinterpret_cast<float*>(dyn_base + SM::kv_bytes);  // [ATTN_WARPS][GM][D]
     // tensor-core path: until the warps' partials are written there (after the last chunk's barrier), the same bytes hold
     // the low halves of Q (q - fp16(q)) as B fragments, the same for every warp: [k step][lane], 16 * D bytes
     uint2* qlo_s = reinterpret_cast<uint2*>(part_acc);
@@ -238,7 +248,20 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
         const uint32_t NT = ATTN_WARPS * 32;
         const uint32_t me = (threadIdx.x + NT - rot) % NT;
         const uint32_t row_bytes = D * (uint32_t)sizeof(KVT);
-        if (a.block_table && !MMA) {
+        if constexpr (MMA) {
+            // one tiled copy per (KV block, K or V, 64-column half): 16 rows of 128 bytes, swizzled
+            const uint32_t nb = (n_tok + 15u) / 16u;
+            if (me == 0) mbar_expect_tx(bar, nb * 2 * HV * 2048u);
+            for (uint32_t i = me; i < nb * 2 * HV; i += NT) {
+                const uint32_t h = i % HV, kv = (i / HV) & 1, j = i / (2 * HV);
+                const uint32_t bi = c0 / 16u + j;
+                const int32_t blk = spec_table ? blk_s[bi] : a.block_table[(size_t)b * a.max_blocks + bi];
+                const int y = (int)(a.kv_map_row0 + (((uint32_t)blk * 2 + kv) * a.Hkv + kvh) * 16u);
+                const uint32_t dst = smem_u32(kb) + ((kv * HV + h) * CH + j * 16u) * 128u;
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(dst), "l"(&ka.kv_map), "r"((int)(h * 64u)), "r"(y), "r"(bar) : "memory");
+            }
+        } else if (a.block_table) {
             const uint32_t nb = (n_tok + a.block_tokens - 1) / a.block_tokens;
             const uint32_t blk_bytes = a.block_tokens * row_bytes;
             if (me == 0) mbar_expect_tx(bar, nb * 2 * blk_bytes);
@@ -250,7 +273,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                 tma_load_1d(smem_u32(kb + ((size_t)kv * CH + (size_t)j * a.block_tokens) * RS), src, blk_bytes, bar);
             }
         } else {
-            // one copy per row: the contiguous layout has no larger unit, and the tensor-core path pads the rows
+            // one copy per row: the contiguous layout has no larger unit
             if (me == 0) mbar_expect_tx(bar, n_tok * 2 * row_bytes);
             for (uint32_t i = me; i < n_tok * 2; i += NT) {
                 const uint32_t kv = i & 1, tok = i >> 1, tt = c0 + tok;
@@ -264,15 +287,6 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     src = reinterpret_cast<const KVT*>(kv ? a.v : a.k) + (size_t)b * ka.kv_batch_stride + (size_t)tt * a.Hkv * D + (size_t)kvh * D;
                 }
                 tma_load_1d(smem_u32(kb + ((size_t)kv * CH + tok) * RS), src, row_bytes, bar);
-            }
-            if constexpr (MMA) {
-                // rows up to the next multiple of 16 are multiplied (with probability 0): they must hold numbers
-                const uint32_t pad_hi = min((uint32_t)CH, (n_tok + 15u) & ~15u);
-                for (uint32_t i = me; i < (pad_hi - n_tok) * 2 * (row_bytes / 16); i += NT) {
-                    const uint32_t piece = i % (row_bytes / 16), rowi = i / (row_bytes / 16);
-                    const uint32_t kv = rowi & 1, tok = n_tok + (rowi >> 1);
-                    reinterpret_cast<uint4*>(kb + ((size_t)kv * CH + tok) * RS)[piece] = make_uint4(0, 0, 0, 0);
-                }
             }
         }
     };
@@ -421,7 +435,28 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
             const uint32_t c0 = t_lo + c * CH, buf = c & 1;
             if (!mbar_wait(smem_u32(&kv_bar[buf]), (c >> 1) & 1) && a.err) atomicOr(a.err, 0x400u);
             KVT* kb = kv_s + (size_t)buf * 2 * CH * RS;
-            if (appender && c0 <= pos && pos < c0 + CH) {
+            const uint32_t c_hi = min(t_hi, c0 + CH);
+            if constexpr (MMA) {
+                // the copies moved whole KV blocks: rows past the context's end hold whatever the pool held (they are
+                // multiplied with probability 0 and must be numbers), and the new token's row is older than this step
+                const bool patch = appender && c0 <= pos && pos < c0 + CH;
+                const uint32_t n_valid = c_hi - c0, n_landed = (n_valid + 15u) & ~15u;
+                if (patch || n_valid != n_landed) {
+                    for (uint32_t i = threadIdx.x; i < (n_landed - n_valid) * 2 * ROW16; i += blockDim.x) {
+                        const uint32_t piece = i % ROW16, rowi = i / ROW16, kv = rowi & 1, r = n_valid + (rowi >> 1);
+                        reinterpret_cast<uint4*>(kb + ((size_t)(kv * HV + (piece >> 3)) * CH + r) * 64)[piece & 7] = make_uint4(0, 0, 0, 0);
+                    }
+                    if (patch) {
+                        const uint32_t r = pos - c0;
+                        for (uint32_t i = threadIdx.x; i < 2 * ROW16; i += blockDim.x) {
+                            const uint32_t kv = i / ROW16, piece = i % ROW16;
+                            reinterpret_cast<uint4*>(kb + ((size_t)(kv * HV + (piece >> 3)) * CH + r) * 64)[(piece & 7) ^ (r & 7)] =
+                                reinterpret_cast<const uint4*>(new_kv[kv])[piece];
+                        }
+                    }
+                    __syncthreads();
+                }
+            } else if (appender && c0 <= pos && pos < c0 + CH) {
                 // overwrite the staged copy of the new token's row with the values just computed
                 for (uint32_t i = threadIdx.x; i < 2 * ROW16; i += blockDim.x) {
                     const uint32_t kv = i / ROW16, piece = i % ROW16;
@@ -429,7 +464,6 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                 }
                 __syncthreads();
             }
-            const uint32_t c_hi = min(t_hi, c0 + CH);
             if constexpr (MMA) {
                 const uint32_t n_tiles = (c_hi - c0 + 15) / 16;
                 const uint32_t mi = lane >> 3, r8 = lane & 7;
@@ -437,11 +471,14 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     const uint32_t tok0 = tile * 16;
                     // scores of 16 tokens x 8 heads
                     float sc4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    const uint32_t k_addr = smem_u32(kb + (size_t)(tok0 + (mi & 1) * 8 + r8) * RS + (mi >> 1) * 8);
+                    // row (tok0 + (mi & 1) * 8 + r8) of K, 16-byte piece q = 2 * ks + (mi >> 1) of its D / 8: half q >> 3,
+                    // piece (q & 7) ^ r8 of the 128-byte row
+                    const uint32_t k_row = smem_u32(kb) + (tok0 + (mi & 1) * 8 + r8) * 128u;
 #pragma unroll
                     for (int ks = 0; ks < MT; ++ks) {
                         uint32_t af[4];
-                        ldsm_x4(af, k_addr + ks * 32);
+                        const uint32_t q = 2u * ks + (mi >> 1);
+                        ldsm_x4(af, k_row + (q >> 3) * (CH * 128u) + (((q & 7u) ^ r8) << 4));
                         const uint2 ql = qlo_s[ks * 32 + lane];
                         mma_f16_16816(sc4, af, qb[ks][0], qb[ks][1]);
                         mma_f16_16816(sc4, af, ql.x, ql.y);
@@ -470,12 +507,13 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(AttnKArgs ka) {
                     const uint32_t pb1 = movmatrix_trans(pack_half2(p2, p3));
                     const uint32_t pl0 = movmatrix_trans(pack_half2(p0 - half_round(p0), p1 - half_round(p1)));
                     const uint32_t pl1 = movmatrix_trans(pack_half2(p2 - half_round(p2), p3 - half_round(p3)));
-                    const uint32_t v_addr = smem_u32(kb + ((size_t)CH + tok0 + (mi >> 1) * 8 + r8) * RS + (mi & 1) * 8);
+                    const uint32_t v_row = smem_u32(kb) + HV * (CH * 128u) + (tok0 + (mi >> 1) * 8 + r8) * 128u;
 #pragma unroll
                     for (int mt = 0; mt < MT; ++mt) {
                         o_t[mt][0] *= al0; o_t[mt][2] *= al0; o_t[mt][1] *= al1; o_t[mt][3] *= al1;
                         uint32_t af[4];
-                        ldsm_x4_trans(af, v_addr + mt * 32);
+                        const uint32_t q = 2u * mt + (mi & 1);
+                        ldsm_x4_trans(af, v_row + (q >> 3) * (CH * 128u) + (((q & 7u) ^ r8) << 4));
                         mma_f16_16816(o_t[mt], af, pb0, pb1);
                         mma_f16_16816(o_t[mt], af, pl0, pl1);
                     }
@@ -662,8 +700,9 @@ static cudaError_t launch_split_g(const LaunchCfg& lc, AttnKArgs ka) {
 
 template <typename KVT, int EPL>
 static cudaError_t launch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
-    if constexpr (sizeof(KVT) == 2 && EPL <= 8) {
-        if (attn_use_mma) {
+    if constexpr (sizeof(KVT) == 2 && EPL >= 2 && EPL <= 8) {
+        // tensor-core path: paged pool of 16-token blocks reachable through its tensor map
+        if (attn_use_mma && ka.a.kv_map && ka.a.block_table && ka.a.block_tokens == 16) {
             if (ka.G == 1) return launch_split_g<KVT, EPL, 1, true>(lc, ka);
             if (ka.G == 2) return launch_split_g<KVT, EPL, 2, true>(lc, ka);
             if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, true>(lc, ka);
@@ -696,7 +735,7 @@ template <typename KVT, int EPL, int GM>
 static cudaError_t opt_in_one() {
     cudaError_t e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)AttnSmem<KVT, EPL, GM, false>::total);
-    if constexpr (sizeof(KVT) == 2 && EPL <= 8) {
+    if constexpr (sizeof(KVT) == 2 && EPL >= 2 && EPL <= 8) {
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)AttnSmem<KVT, EPL, GM, true>::total);
@@ -733,6 +772,8 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
     }
     AttnKArgs ka;
     ka.a = a;
+    if (a.kv_map) memcpy(&ka.kv_map, a.kv_map, sizeof(CUtensorMap));
+    else memset(&ka.kv_map, 0, sizeof(CUtensorMap));
     ka.scale = (scale != 0.0f) ? scale : 1.0f / sqrtf((float)a.D);
     ka.G = a.Hq / a.Hkv;
     ka.g_chunks = 1;
@@ -747,6 +788,32 @@ cudaError_t attention_ex(const LaunchCfg& lc, const AttnArgs& a, float scale, si
 }
 
 cudaError_t attention(const LaunchCfg& lc, const AttnArgs& a) { return attention_ex(lc, a, 0.0f, 0); }
+
+bool attn_make_kv_map(void* map_out, const void* pool, uint64_t rows, uint32_t D) {
+    typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    if (!fn || !map_out || !pool || D % 64 != 0 || rows == 0 || rows > 0x7FFFFFFFull || ((uintptr_t)pool & 15) != 0) return false;
+    const cuuint64_t dims[2] = {D, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, 16};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(map_out, &m, sizeof(m));
+    return true;
+}
 
 }  // namespace vb
 

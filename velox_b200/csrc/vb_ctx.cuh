@@ -58,6 +58,8 @@ struct vb_ctx {
     // paged KV pool: per layer [block][K|V][kv_head][block_tokens][D] fp16
     __half* kv_pool = nullptr;
     uint64_t kv_layer_elems = 0;
+    alignas(64) unsigned char kv_map[128] = {};  // tiled-TMA tensor map over the whole KV pool as [token rows][head_dim] (attn_make_kv_map)
+    bool kv_map_ok = false;
     int32_t* block_table_dev = nullptr;
     std::vector<int32_t> block_table_host;
     std::vector<int32_t> free_blocks;

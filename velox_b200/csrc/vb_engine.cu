@@ -408,6 +408,7 @@ cudaError_t enqueue_step(vb_ctx* c, SeqState* state, bool with_head, const StepI
         a.out = io.attn_out; a.q = io.q; a.k = kv_layer; a.kv_fp16 = 1;
         if (fused_append) { a.qkv_raw = io.qkv; a.bq = bq; a.bk = bk; a.bv = bv; a.bias_fmt = bf; a.rope_inv_freq = c->rope_inv_freq; a.rope_inv_freq_host = c->rope_inv_freq_host.data(); }
         a.block_table = io.block_table; a.max_blocks = c->max_blocks; a.block_tokens = d.kv_block_tokens;
+        if (c->kv_map_ok) { a.kv_map = c->kv_map; a.kv_map_row0 = (uint32_t)((uint64_t)l * (c->kv_layer_elems / d.head_dim)); }
         a.state = state; a.Hq = c->hq; a.Hkv = c->hkv; a.D = d.head_dim; a.batch = B;
         a.max_splits = c->n_splits; a.tokens_per_split = c->tokens_per_split; a.scratch = c->attn_scratch;
         a.trace = next_trace(); a.err = c->err_word;
@@ -586,6 +587,8 @@ int32_t vb_create(const vb_model_desc* desc, int32_t device, vb_ctx** out) {
     c->kv_layer_elems = (uint64_t)c->n_blocks * 2 * c->hkv * d.kv_block_tokens * d.head_dim;
     VB_CREATE_TRY(dev_alloc(&c->kv_pool, c->kv_layer_elems * d.n_layers));
     VB_CREATE_CUDA(cudaMemsetAsync(c->kv_pool, 0, c->kv_layer_elems * d.n_layers * sizeof(__half), c->stream));
+    // the decode attention's tensor-core path stages whole KV blocks with tiled TMA copies
+    c->kv_map_ok = d.kv_block_tokens == 16 && attn_make_kv_map(c->kv_map, c->kv_pool, c->kv_layer_elems * d.n_layers / d.head_dim, d.head_dim);
     VB_CREATE_TRY(dev_alloc(&c->block_table_dev, (uint64_t)d.max_batch * c->max_blocks));
     c->block_table_host.assign((size_t)d.max_batch * c->max_blocks, 0);
     VB_CREATE_CUDA(cudaMemsetAsync(c->block_table_dev, 0, (size_t)d.max_batch * c->max_blocks * 4, c->stream));

@@ -85,6 +85,7 @@ struct I8Params {
     float* part;                // [split][tile][32 cols][128 lanes] fp32 partial tiles
     uint32_t* counters;         // [tile], zero between launches
     uint32_t stages;
+    unsigned long long* trace;  // time stamps of this launch (vb_trace_read), or null
 };
 
 template <bool DUAL>
@@ -107,6 +108,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int nk_all = (int)((p.K + I8_BK - 1) / I8_BK);
     const int kb_first = (int)(((long long)nk_all * blockIdx.z) / gridDim.z), kb_last = (int)(((long long)nk_all * (blockIdx.z + 1)) / gridDim.z);
     const int nk = kb_last - kb_first;
+    trace_mark(p.trace, 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(bars + s * 8, 1); mbar_init(bars + (STAGES + s) * 8, 1); }
@@ -136,6 +138,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (DUAL) tma_2d(st + I8_W_BYTES, &map_w2, kx, row0, full);
         }
         pdl_wait();
+        trace_mark(p.trace, 1);
         for (int kb = 0; kb < pre; ++kb) tma_2d(base + kb * STAGE_BYTES + W_TILES * I8_W_BYTES, &map_x, (kb_first + kb) * I8_BK, 0, bars + kb * 8);
         for (int kb = pre; kb < nk; ++kb) {
             const int s = kb % STAGES;
@@ -258,6 +261,7 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     fence_before();
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    trace_exit(p.trace);
 }
 
 // One block per row of x (32 blocks): planes[r][k] = H, planes[32 + r][k] = L of X = rint(norm(x) * p); inv_scale[r] = 1 / p.
@@ -543,6 +547,7 @@ cudaError_t gemm_i8(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
         if ((uint64_t)splits * tiles * 128 * 32 * 4 > I8_PART_BYTES || tiles * 4 > I8_COUNTER_BYTES) splits = 1;
     }
     p.stages = (uint32_t)(192 * 1024 / ((dual ? 2 : 1) * I8_W_BYTES + I8_X_BYTES));
+    p.trace = a.trace;
     const dim3 grid(1, tiles, splits);
     if (dual) return launch(lc, k_gemm_i8<true>, grid, dim3(128), I8_SMEM, mw, mw2, mx, p);
     return launch(lc, k_gemm_i8<false>, grid, dim3(128), I8_SMEM, mw, mw2, mx, p);

@@ -172,7 +172,14 @@ struct AttnArgs {
     unsigned long long* trace = nullptr;
     uint32_t* err = nullptr;       // device word that a bounded wait sets when it runs out
     float* scratch = nullptr;      // attn_scratch_floats(): partials, then the split counters (zero before the first launch)
+    // paged fp16 pool as a tiled-TMA tensor map (attn_make_kv_map; a CUtensorMap on the host) and the row of that map
+    // where this layer's part of the pool begins; without it the tensor-core path is not taken
+    const void* kv_map = nullptr;
+    uint32_t kv_map_row0 = 0;
 };
+// 128 bytes, 64-byte aligned: a tensor map over the whole pool as a matrix of token rows, [rows][D] fp16, boxes of
+// [block_tokens = 16 rows][64 columns] with the 128-byte swizzle.  False when the driver entry point is missing.
+bool attn_make_kv_map(void* map_out, const void* pool, uint64_t rows, uint32_t D);
 uint64_t attn_scratch_floats(uint32_t Hq, uint32_t D, uint32_t batch, uint32_t max_splits);
 uint32_t attn_pick_splits(uint32_t max_seq);
 uint32_t attn_tokens_per_split(uint32_t max_seq);

@@ -1,6 +1,6 @@
 """Per-kernel device timeline of one decode step (profiling aid).
 
-    python -m velox_b200.trace [--model llama3-8b|qwen2-72b] [--layers 4] [--prompt-len 512]
+    python -m velox_b200.trace [--model llama3-8b|qwen2-72b|qwen2.5-7b] [--layers 4] [--prompt-len 512] [--batch 32]
     python -m torch.distributed.run --nproc-per-node N -m velox_b200.trace --model qwen2-72b [--exchange p2p|nccl]
 
 Builds a Llama-3-8B- or Qwen2-72B-shape int4 model with synthetic weights (sharded over the launcher's ranks
@@ -17,7 +17,7 @@ import numpy as np
 
 from . import lib as L
 from .engine import Engine
-from .modelspec import LLAMA3_8B_INT4, PROMPT_STREAM, QWEN2_72B_INT4
+from .modelspec import LLAMA3_8B_INT4, PROMPT_STREAM, QWEN2_72B_INT4, QWEN25_7B_INT8
 from .tp import connect, env_rank, init_process_group, shutdown
 
 
@@ -25,11 +25,12 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--prompt-len", type=int, default=512)
-    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-72b"])
+    ap.add_argument("--model", default="llama3-8b", choices=["llama3-8b", "qwen2-72b", "qwen2.5-7b"])
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoding together (each prefilled with --prompt-len tokens)")
     ap.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"])
     ap.add_argument("--set", action="append", default=[], metavar="NAME=VALUE", help="engine option (vb_set_option), repeatable")
     args = ap.parse_args()
-    base = LLAMA3_8B_INT4 if args.model == "llama3-8b" else QWEN2_72B_INT4
+    base = {"llama3-8b": LLAMA3_8B_INT4, "qwen2-72b": QWEN2_72B_INT4, "qwen2.5-7b": QWEN25_7B_INT8}[args.model]
     spec = base.scaled(name="trace", n_layers=args.layers)
     rank, world, local = env_rank()
     dist = None
@@ -39,7 +40,7 @@ def main():
         eng = Engine(spec, max_seq_len=args.prompt_len + 64, device=local, tp_rank=rank, tp_size=world)
         connect(eng, args.exchange)
     else:
-        eng = Engine(spec, max_seq_len=args.prompt_len + 64)
+        eng = Engine(spec, max_seq_len=args.prompt_len + 64, max_batch=args.batch)
     eng.load_synthetic(1)
     if dist is not None:
         dist.barrier()
@@ -48,9 +49,10 @@ def main():
         name, _, val = kv.partition("=")
         eng.set_option(name, int(val))
     rng = np.random.default_rng(PROMPT_STREAM)
-    prompt = rng.integers(0, spec.vocab, args.prompt_len, dtype=np.uint32)
-    eng.reserve(0, args.prompt_len + 64)
-    eng.prefill(prompt, 0)
+    for slot in range(args.batch):
+        prompt = rng.integers(0, spec.vocab, args.prompt_len, dtype=np.uint32)
+        eng.reserve(slot, args.prompt_len + 64)
+        eng.prefill(prompt, slot)
     eng.build_graph()
     eng.decode(8)
     out = np.zeros(3 * 1024, dtype=np.uint64)
