@@ -322,26 +322,12 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
     tc_extra_bytes = (spec.d_model * (qd_ + 2 * kd_) + qd_ * spec.d_model + 3 * spec.ffn_dim * spec.d_model) * spec.n_layers \
         if "int8" in spec.name and i8_off else 0
 
-    # ---- device-resident timing: K graph replays between CUDA events on the library's stream ----------
     sampler = ClockSampler(R.local_rank)
-    sampler.start()          # nvidia-smi needs a moment to start: sample from the warm-up on, all under load
-    eng.decode(warmup)
-    eng.sync()
-    wbytes, kv0 = eng.step_bytes()
-    barrier()
-    l0 = eng.launch_count()
-    ms = eng.decode(steps, timed=True)
-    launches = eng.launch_count() - l0
-    eng.sync()
-    barrier()
-    _, kv1 = eng.step_bytes()
-    if not solo:
-        ms = R.max(ms)
-    ms_per_step = ms / steps
+    sampler.start()          # nvidia-smi needs a moment to start: sample from here on, all under load
     groups = 1 if (sharded or solo) else world  # independent model instances
-    value = groups * batch * 1e3 / ms_per_step
 
-    # ---- end to end: every step driven from the host through the C ABI ----------------------------------
+    # ---- end to end: every step driven from the host through the C ABI (measured first: the device-timed steps after
+    # it then run on a GPU that has been under load for a while, whatever the state it was handed over in) -----------
     e2e = None
     if with_e2e:
         tok, pos = eng.state(0)
@@ -363,6 +349,22 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
             e2e_s = R.max(e2e_s)
         e2e = {"value": groups * batch * steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 if batch == 1 else 0,
                "d2h_bytes_per_step": 4 * batch}
+    # ---- device-resident timing: K graph replays between CUDA events on the library's stream ----------
+    eng.decode(warmup)
+    eng.sync()
+    wbytes, kv0 = eng.step_bytes()
+    barrier()
+    l0 = eng.launch_count()
+    ms = eng.decode(steps, timed=True)
+    launches = eng.launch_count() - l0
+    eng.sync()
+    barrier()
+    _, kv1 = eng.step_bytes()
+    if not solo:
+        ms = R.max(ms)
+    ms_per_step = ms / steps
+    value = groups * batch * 1e3 / ms_per_step
+
     if sampler.rows == []:
         # very short runs: keep the GPU busy until the sampler has something to report
         t_end = time.perf_counter() + 1.0
