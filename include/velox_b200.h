@@ -217,6 +217,10 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "decode_gemm_i8" 1 (default): those products over int8 per-channel weights (batches of up to 32) run on the integer
  *                    tensor cores straight from the stored bytes (exact arithmetic, one byte per weight from HBM); 0: through
  *                    resident fp16 copies
+ *   "i8_tiles"       1 (default): those integer products stream tile-major copies of the int8 matrices (one contiguous 16 KB bulk
+ *                    copy per tile, made on first use within "tc_resident_gb"); 0: tiled TMA from the canonical matrices
+ *   "i8_half_ring"   1 (default): single integer products with more tiles than SMs (the lm_head) take half an SM's shared memory
+ *                    per block (two blocks per SM: one block's epilogue overlaps the other's weight stream); 0: the whole ring
  *   "decode_split_k" 1 (default): decode-batch products with few 128-row tiles split K over several blocks per tile
  *                    (partials summed in a fixed order: results do not depend on scheduling)
  *   "tc_resident_gb" budget in GB for resident fp16 copies of the layer matrices used by those GEMMs (40; 0: convert

@@ -93,6 +93,8 @@ struct vb_ctx {
     uint32_t prefill_rows = 2048, prefill_gemm_min = 48;
     void* tc_ws = nullptr;
     uint64_t tc_ws_bytes = 0;
+    void* i8_tiles_pool = nullptr;  // tile-major int8 copies of the layer matrices and the head for those products (WMat::i8_tiles)
+    bool i8_tiles_tried = false;
     void* i8_ws = nullptr;      // workspace of the int8 tensor-core products of decode batches (x planes, split-K partials)
     uint64_t i8_ws_bytes = 0;
     // resident fp16 copies of the layer matrices for those products, made once when they fit `tc_resident_gb`

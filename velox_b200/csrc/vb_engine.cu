@@ -302,6 +302,47 @@ int32_t ensure_f16_copies(vb_ctx* c) {
     return VB_OK;
 }
 
+// Tile-major int8 copies (shared-memory order) of every layer matrix and the head for the integer tensor-core decode
+// batches: one contiguous 16 KB bulk copy per tile.  Tried once per context; without them the kernel reads the canonical
+// matrices through tiled TMA.
+int32_t ensure_i8_tiles(vb_ctx* c) {
+    if (c->i8_tiles_tried) return VB_OK;
+    c->i8_tiles_tried = true;
+    if (!gemm_i8_tiles) return VB_OK;
+    const int roles[] = {VB_ROLE_WQ, VB_ROLE_WO, VB_ROLE_WGATE, VB_ROLE_WUP, VB_ROLE_WDOWN};
+    auto rows_of = [&](int role, const Tensor& t) { return role == VB_ROLE_WQ ? c->qkv_rows : t.m.rows; };
+    uint64_t total = 0;
+    for (uint32_t l = 0; l < c->d.n_layers; ++l)
+        for (int role : roles) {
+            const Tensor& t = c->tensor(role, (int)l);
+            if (t.m.fmt != VB_FMT_I8PC || !t.m.data) return VB_OK;
+            total += gemm_i8_tiles_bytes(rows_of(role, t), t.m.cols);
+        }
+    Tensor& head = c->tensor(VB_ROLE_LM_HEAD, 0);
+    const bool with_head = head.m.fmt == VB_FMT_I8PC && head.m.data != nullptr;
+    if (with_head) total += gemm_i8_tiles_bytes(head.m.rows, head.m.cols);
+    if (total == 0 || total > (uint64_t)c->tc_resident_gb << 30) return VB_OK;
+    if (cudaMalloc(&c->i8_tiles_pool, total + 1024) != cudaSuccess) { cudaGetLastError(); c->i8_tiles_pool = nullptr; return VB_OK; }
+    unsigned char* p = (unsigned char*)(((uintptr_t)c->i8_tiles_pool + 1023) & ~(uintptr_t)1023);
+    LaunchCfg lc = lcfg(c, false);
+    lc.counter = nullptr;
+    for (uint32_t l = 0; l < c->d.n_layers; ++l)
+        for (int role : roles) {
+            Tensor& t = c->tensor(role, (int)l);
+            const uint64_t bytes = gemm_i8_tiles_bytes(rows_of(role, t), t.m.cols);
+            if (bytes == 0) continue;
+            VB_CUDA(gemm_i8_make_tiles(lc, p, t.m.data, rows_of(role, t), t.m.cols));
+            t.m.i8_tiles = p;
+            p += bytes;
+        }
+    if (with_head && gemm_i8_tiles_bytes(head.m.rows, head.m.cols)) {
+        VB_CUDA(gemm_i8_make_tiles(lc, p, head.m.data, head.m.rows, head.m.cols));
+        head.m.i8_tiles = p;
+    }
+    VB_CUDA(cudaStreamSynchronize(c->stream));
+    return VB_OK;
+}
+
 // decode_gemm: make sure, outside any capture, that the products can take that path and that the workspace is there
 int32_t prepare_decode_gemm(vb_ctx* c) {
     if (!c->decode_gemm) return VB_OK;
@@ -320,6 +361,7 @@ int32_t prepare_decode_gemm(vb_ctx* c) {
             VB_CUDA(cudaMemsetAsync((void*)(((uintptr_t)c->i8_ws + 1023) & ~(uintptr_t)1023), 0, gemm_i8_workspace_zero_bytes(), c->stream));
         }
     }
+    if (c->i8_ws && (rc = ensure_i8_tiles(c)) != VB_OK) return rc;
     return ensure_tc_ws(c, std::max(c->d.max_batch, c->prefill_rows), true);
 }
 
@@ -650,7 +692,7 @@ int32_t vb_destroy(vb_ctx* c) {
     if (c->links.base[c->links.rank]) cudaFree(c->links.base[c->links.rank]);
     void* frees[] = {c->arena, c->kv_pool, c->block_table_dev, c->state, c->pf_state, c->pf_tokens, c->hidden, c->qkv, c->q,
                      c->attn_out, c->act, c->logits, c->attn_scratch, c->cand_v, c->cand_i, c->rope_inv_freq, c->trace, c->partial, c->tp_pair, c->tp_pairs,
-                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool, c->sample_probs,
+                     c->pfc_state, c->pfc_table, c->pfc_hidden, c->pfc_qkv, c->pfc_q, c->pfc_attn, c->pfc_act, c->tc_ws, c->f16_pool, c->i8_tiles_pool, c->sample_probs,
                      c->spec_logits, c->spec_cand_v, c->spec_cand_i, c->spec_tokens, c->i8_ws};
     for (void* p : frees) if (p) cudaFree(p);
     if (c->ring_host) cudaFreeHost(c->ring_host);
@@ -739,8 +781,10 @@ static int32_t mark_loaded(vb_ctx* c, int32_t role, int32_t layer, Tensor* t) {
     int32_t owner_role = (role == VB_ROLE_WK || role == VB_ROLE_WV) ? VB_ROLE_WQ : role;
     if (role == VB_ROLE_EMBED && c->d.tied_lm_head) {  // tied: the head reads the table
         const void* keep = c->tensor(VB_ROLE_LM_HEAD, 0).m.f16;
+        const void* keep8 = c->tensor(VB_ROLE_LM_HEAD, 0).m.i8_tiles;
         set_tied_head(c);
         c->tensor(VB_ROLE_LM_HEAD, 0).m.f16 = keep;
+        c->tensor(VB_ROLE_LM_HEAD, 0).m.i8_tiles = keep8;
         owner_role = VB_ROLE_LM_HEAD;
     }
     Tensor& o = c->tensor(owner_role, role_is_global(owner_role) ? 0 : layer);
@@ -750,6 +794,12 @@ static int32_t mark_loaded(vb_ctx* c, int32_t role, int32_t layer, Tensor* t) {
         LaunchCfg lc = lcfg(c, false);
         lc.counter = nullptr;
         VB_CUDA(weights_to_f16(lc, const_cast<void*>(o.m.f16), m, const_cast<void*>(o.m.f16_lo)));
+        VB_CUDA(cudaStreamSynchronize(c->stream));
+    }
+    if (o.m.i8_tiles && o.m.data && o.m.fmt == VB_FMT_I8PC) {  // the tile-major int8 copy follows the canonical one too
+        LaunchCfg lc = lcfg(c, false);
+        lc.counter = nullptr;
+        VB_CUDA(gemm_i8_make_tiles(lc, const_cast<void*>(o.m.i8_tiles), o.m.data, owner_role == VB_ROLE_WQ ? c->qkv_rows : o.m.rows, o.m.cols));
         VB_CUDA(cudaStreamSynchronize(c->stream));
     }
     return VB_OK;
@@ -1202,6 +1252,8 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
         return VB_OK;
     }
     if (!strcmp(name, "decode_gemm_i8")) { gemm_i8_enabled = value != 0; return VB_OK; }
+    if (!strcmp(name, "i8_tiles")) { gemm_i8_tiles = value != 0; return VB_OK; }
+    if (!strcmp(name, "i8_half_ring")) { gemm_i8_half_ring = value != 0; return VB_OK; }
     if (!strcmp(name, "tc_resident_gb")) { c->tc_resident_gb = (uint32_t)value; return VB_OK; }
     if (!strcmp(name, "prefill_two_per_sm")) { gemm_tc_two_per_sm = value != 0; return VB_OK; }
     if (!strcmp(name, "decode_split_k")) { gemm_tc_split_k = value != 0; return VB_OK; }

@@ -86,6 +86,10 @@ struct I8Params {
     uint32_t* counters;         // [tile], zero between launches
     uint32_t stages;
     unsigned long long* trace;  // time stamps of this launch (vb_trace_read), or null
+    // tile-major copies of the weights in shared-memory order (null: tiled TMA from the canonical matrices): a tile is one
+    // contiguous 16 KB bulk copy -- sequential DRAM pages instead of 128 rows of 128 bytes a whole matrix row apart
+    const unsigned char* w_tiles;
+    const unsigned char* w2_tiles;
 };
 
 template <bool DUAL>
@@ -134,8 +138,14 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const uint32_t full = bars + kb * 8, st = base + kb * STAGE_BYTES;
             mbar_expect_tx(full, STAGE_BYTES);
             const int kx = (kb_first + kb) * I8_BK;
-            tma_2d(st, &map_w, kx, row0, full);
-            if (DUAL) tma_2d(st + I8_W_BYTES, &map_w2, kx, row0, full);
+            if (p.w_tiles) {
+                const size_t toff = ((size_t)blockIdx.y * nk_all + kb_first + kb) * I8_W_BYTES;
+                tma_load_1d(st, p.w_tiles + toff, I8_W_BYTES, full);
+                if (DUAL) tma_load_1d(st + I8_W_BYTES, p.w2_tiles + toff, I8_W_BYTES, full);
+            } else {
+                tma_2d(st, &map_w, kx, row0, full);
+                if (DUAL) tma_2d(st + I8_W_BYTES, &map_w2, kx, row0, full);
+            }
         }
         pdl_wait();
         trace_mark(p.trace, 1);
@@ -147,8 +157,14 @@ k_gemm_i8(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const uint32_t full = bars + s * 8, st = base + s * STAGE_BYTES;
             mbar_expect_tx(full, STAGE_BYTES);
             const int kx = (kb_first + kb) * I8_BK;
-            tma_2d(st, &map_w, kx, row0, full);
-            if (DUAL) tma_2d(st + I8_W_BYTES, &map_w2, kx, row0, full);
+            if (p.w_tiles) {
+                const size_t toff = ((size_t)blockIdx.y * nk_all + kb_first + kb) * I8_W_BYTES;
+                tma_load_1d(st, p.w_tiles + toff, I8_W_BYTES, full);
+                if (DUAL) tma_load_1d(st + I8_W_BYTES, p.w2_tiles + toff, I8_W_BYTES, full);
+            } else {
+                tma_2d(st, &map_w, kx, row0, full);
+                if (DUAL) tma_2d(st + I8_W_BYTES, &map_w2, kx, row0, full);
+            }
             tma_2d(st + W_TILES * I8_W_BYTES, &map_x, kx, 0, full);
         }
     } else if (warp == 1 && lane == 0) {
@@ -447,6 +463,22 @@ k_rows_to_i8_regs(int8_t* __restrict__ planes, float* __restrict__ inv_scale, co
     }
 }
 
+// dst tile (row tile rt, k block kb) at ((rt * n_kb) + kb) * 16 KB: byte b of the 16-byte piece c of row r at
+// r * 128 + ((c ^ (r & 7)) << 4) + b -- what a tiled TMA copy with the 128-byte swizzle would have written; rows past the
+// matrix are zeros.  One thread per 16-byte piece.
+__global__ void __launch_bounds__(256)
+k_tile_i8_umma(uint4* __restrict__ dst, const int8_t* __restrict__ src, uint32_t rows, uint32_t K, uint32_t n_kb, uint64_t n_pieces) {
+    const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n_pieces) return;
+    const uint32_t c = (uint32_t)(i & 7), r = (uint32_t)((i >> 3) & 127);
+    const uint64_t tile = i >> 10;
+    const uint32_t kb = (uint32_t)(tile % n_kb), rt = (uint32_t)(tile / n_kb);
+    const uint32_t row = rt * 128 + r;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < rows) v = *reinterpret_cast<const uint4*>(src + (size_t)row * K + (size_t)kb * 128 + c * 16);
+    dst[tile * 1024 + r * 8 + (c ^ (r & 7))] = v;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -479,6 +511,8 @@ constexpr uint64_t I8_COUNTER_BYTES = 64 * 1024, I8_PART_BYTES = 4 * 1024 * 1024
 
 }  // namespace
 
+bool gemm_i8_half_ring = true;  // vb_set_option("i8_half_ring", 0): every block of k_gemm_i8 takes a whole SM's shared memory
+bool gemm_i8_tiles = true;  // vb_set_option("i8_tiles", 0): weight tiles by tiled TMA from the canonical matrices instead of the tile-major copies
 bool gemm_i8_enabled = true;  // vb_set_option("decode_gemm_i8", 0): decode batches over int8 weights go through the fp16 copies again
 
 cudaError_t gemm_i8_init() {
@@ -498,6 +532,17 @@ bool gemm_i8_supported(const GemvArgs& a) {
                                      ((uintptr_t)a.w2.data & 15) != 0))
         return false;
     return a.push.links == nullptr;
+}
+
+uint64_t gemm_i8_tiles_bytes(uint32_t rows, uint32_t K) {
+    return K % I8_BK ? 0 : (uint64_t)((rows + I8_BM - 1) / I8_BM) * (K / I8_BK) * I8_W_BYTES;
+}
+cudaError_t gemm_i8_make_tiles(const LaunchCfg& lc, void* dst, const void* src_i8, uint32_t rows, uint32_t K) {
+    if (K % I8_BK != 0 || ((uintptr_t)dst & 15) != 0 || ((uintptr_t)src_i8 & 15) != 0) return cudaErrorInvalidValue;
+    const uint32_t n_kb = K / I8_BK;
+    const uint64_t n_pieces = gemm_i8_tiles_bytes(rows, K) / 16;
+    return launch(lc, k_tile_i8_umma, dim3((unsigned)((n_pieces + 255) / 256)), dim3(256), 0, reinterpret_cast<uint4*>(dst),
+                  reinterpret_cast<const int8_t*>(src_i8), rows, K, n_kb, n_pieces);
 }
 
 // workspace head: tile counters (zero before the first call) and partial tiles, then the planes of x and their scales
@@ -546,11 +591,20 @@ cudaError_t gemm_i8(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
         splits = std::min(std::min(148u / tiles, 8u), std::max(nk / 8u, 1u));
         if ((uint64_t)splits * tiles * 128 * 32 * 4 > I8_PART_BYTES || tiles * 4 > I8_COUNTER_BYTES) splits = 1;
     }
-    p.stages = (uint32_t)(192 * 1024 / ((dual ? 2 : 1) * I8_W_BYTES + I8_X_BYTES));
+    // single products with more tiles than SMs (the lm_head: 1188): half the shared memory of an SM per block (4 stages),
+    // two blocks per SM, so that one block's weights are on the way while the other is in its epilogue: 123 -> 94 us.
+    // One-wave products measured ~1 us slower that way and keep the whole ring, as does gate/up (two weight tiles per stage).
+    const uint32_t stage_bytes = (dual ? 2 : 1) * I8_W_BYTES + I8_X_BYTES;
+    p.stages = (uint32_t)(192 * 1024 / stage_bytes);
+    if (!dual && gemm_i8_half_ring && tiles * splits > 148) p.stages = 4;
+    const size_t smem = (size_t)p.stages * stage_bytes + 1024 + 256;
     p.trace = a.trace;
+    const bool use_tiles = gemm_i8_tiles && a.w.i8_tiles && (!dual || a.w2.i8_tiles) && K % I8_BK == 0;
+    p.w_tiles = use_tiles ? reinterpret_cast<const unsigned char*>(a.w.i8_tiles) : nullptr;
+    p.w2_tiles = (use_tiles && dual) ? reinterpret_cast<const unsigned char*>(a.w2.i8_tiles) : p.w_tiles;
     const dim3 grid(1, tiles, splits);
-    if (dual) return launch(lc, k_gemm_i8<true>, grid, dim3(128), I8_SMEM, mw, mw2, mx, p);
-    return launch(lc, k_gemm_i8<false>, grid, dim3(128), I8_SMEM, mw, mw2, mx, p);
+    if (dual) return launch(lc, k_gemm_i8<true>, grid, dim3(128), smem, mw, mw2, mx, p);
+    return launch(lc, k_gemm_i8<false>, grid, dim3(128), smem, mw, mw2, mx, p);
 }
 
 }  // namespace vb

@@ -56,6 +56,10 @@ struct WMat {
     // f16_lo: what that copy's rounding dropped, as a second fp16 matrix (prefill chunks multiply hi + lo)
     const void* f16 = nullptr;
     const void* f16_lo = nullptr;
+    // int8 per-channel weights for the integer tensor-core decode batches (vb_gemm_i8.cu): the matrix cut into
+    // [128 rows][128 bytes of K] tiles, each stored as the 16 KB it occupies in shared memory (128-byte swizzle applied),
+    // tiles ordered [row tile][k block]: one contiguous bulk copy per tile; null: tiled TMA from the canonical copy
+    const void* i8_tiles = nullptr;
 };
 
 inline uint64_t wmat_data_bytes(int32_t fmt, uint64_t rows, uint64_t cols) {

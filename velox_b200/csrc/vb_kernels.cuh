@@ -138,6 +138,8 @@ cudaError_t gemm_tc(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uin
 // vb_gemm_i8.cu: decode batches (<= 32 rows) over int8 per-channel weights on the integer tensor cores, weights read
 // where they lie (one byte per weight), exact arithmetic; workspace head (gemm_i8_workspace_zero_bytes) zero before first use
 extern bool gemm_i8_enabled;
+extern bool gemm_i8_tiles;
+extern bool gemm_i8_half_ring;
 bool gemm_i8_supported(const GemvArgs& a);
 // absorbed multi-head latent attention on tcgen05 (vb_mla_tc.cu); `extra` = status word + bf16 copy of q, 16-byte aligned
 extern bool mla_use_tc;
@@ -145,6 +147,9 @@ uint64_t mla_tc_extra_scratch_bytes(uint32_t batch, uint32_t n_heads);
 cudaError_t mla_decode_tc(const LaunchCfg& lc, const float* q, const void* cache, const uint32_t* ctx_len, float* partial, void* extra,
                           uint32_t batch, uint32_t n_heads, uint32_t n_splits, uint32_t split_tokens, uint64_t cache_stride, float scale);
 uint64_t gemm_i8_workspace_bytes(uint32_t in_dim);
+// int8 [rows][K] -> tile-major copy in shared-memory order (WMat::i8_tiles); K a multiple of 128
+uint64_t gemm_i8_tiles_bytes(uint32_t rows, uint32_t K);
+cudaError_t gemm_i8_make_tiles(const LaunchCfg& lc, void* dst, const void* src_i8, uint32_t rows, uint32_t K);
 inline uint64_t gemm_i8_workspace_zero_bytes() { return 64 * 1024; }
 cudaError_t gemm_i8(const LaunchCfg& lc, const GemvArgs& a, void* workspace, uint64_t workspace_bytes, bool counters_zeroed);
 
