@@ -226,6 +226,8 @@ int32_t vb_trace_read(vb_ctx* ctx, uint64_t* out, uint32_t max_records, uint32_t
  *   "tc_resident_gb" budget in GB for resident fp16 copies of the layer matrices used by those GEMMs (40; 0: convert
  *                    per call into the workspace)
  *   "pdl"            1: programmatic dependent launch between the kernels of a step
+ *   "attn_tcgen05"   1: the decode attention of head_dim-128 models runs its two products as tcgen05.mma (tokens as the M dimension,
+ *                    S^T and O^T in tensor memory); same results, measured slower than the mma.sync form (default 0)
  *   "attn_splits"    slices of the context per (sequence, KV head) in the decode attention (1..8; default: one per 32 tokens
  *                    of max_seq_len up to 8, fewer when the batch alone fills the GPU)
  *   "trace"          1: device time stamps per kernel (vb_trace_read)

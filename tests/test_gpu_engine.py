@@ -89,6 +89,30 @@ def test_smollm_135m_prompt128_32_steps():
     assert err <= LOGIT_TOL
 
 
+@pytest.mark.parametrize("g", [4, 7])
+def test_decode_attention_tcgen05_form_matches_checker(g):
+    """Option "attn_tcgen05": both attention products as tcgen05.mma (head_dim 128, tokens as the M dimension) over a context
+    that takes several 128-token chunks per split, group sizes that fill and do not fill the eight head columns."""
+    spec = LLAMA3_8B_INT4.scaled(name="hd128-g%d-int4-small" % g, d_model=512, n_layers=2, n_q_heads=g, n_kv_heads=1, head_dim=128,
+                                 ffn_dim=1408, vocab=4096)
+    n_prompt, n_new = 700, 10
+    max_seq = n_prompt + n_new + 1
+    ora, _ = H.build_oracle(spec, 41, max_seq)
+    eng = H.build_engine(spec, 41, max_seq)
+    eng.set_option("attn_tcgen05", 1)
+    eng.set_option("attn_splits", 2)
+    prompt = H.prompt_tokens(spec, 41, n_prompt)
+    try:
+        want = ora.generate_greedy(prompt, n_new)
+        got = eng.generate_greedy(prompt, n_new)
+        err = float(np.max(np.abs(eng.logits() - ora.logits)))
+    finally:
+        eng.set_option("attn_tcgen05", 0)
+        eng.close()
+    assert err <= LOGIT_TOL, "logits max-abs %g" % err
+    assert np.array_equal(got, want)
+
+
 @pytest.mark.parametrize("mma", [1, 0])
 def test_long_context_crosses_chunk_refills(mma):
     """A context of ~1400 tokens: every split of the attention kernel walks more than two staged chunks (the

@@ -146,8 +146,51 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// ---- tcgen05 helpers of the head_dim-128 path (tokens are the M dimension) ---------------------------------------------
+// instruction descriptors, kind::f16 with fp16 operands (format 0), fp32 accumulate, M 128 (8 << 24), N 16 (2 << 17);
+// bit 15: A is MN-major (V is stored [token][dimension]: the dimensions are M, the tokens K)
+constexpr uint32_t AT_IDESC_S = (1u << 4) | (2u << 17) | (8u << 24);
+constexpr uint32_t AT_IDESC_O = (1u << 4) | (1u << 15) | (2u << 17) | (8u << 24);
+__device__ __forceinline__ uint64_t at_desc_k_sw128(uint32_t addr) {  // K-major, rows of 128 bytes, 8-row groups 1024 bytes apart
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t at_desc_mn_sw128(uint32_t addr, uint32_t lbo) {  // MN-major: 64 elements of M per 128-byte row, next 64 `lbo` bytes on
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint64_t at_desc_k_plain(uint32_t addr, uint32_t lbo, uint32_t sbo) {  // K-major core matrices of 8 rows x 16 bytes
+    return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+}
+__device__ __forceinline__ void at_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_ld16(uint32_t taddr, float r[16]) {
+    uint32_t u[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
+                   "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) r[i] = __uint_as_float(u[i]);
+}
+__device__ __forceinline__ void at_st16(uint32_t taddr, const float r[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(__float_as_uint(r[0])), "r"(__float_as_uint(r[1])), "r"(__float_as_uint(r[2])), "r"(__float_as_uint(r[3])),
+                   "r"(__float_as_uint(r[4])), "r"(__float_as_uint(r[5])), "r"(__float_as_uint(r[6])), "r"(__float_as_uint(r[7])),
+                   "r"(__float_as_uint(r[8])), "r"(__float_as_uint(r[9])), "r"(__float_as_uint(r[10])), "r"(__float_as_uint(r[11])),
+                   "r"(__float_as_uint(r[12])), "r"(__float_as_uint(r[13])), "r"(__float_as_uint(r[14])), "r"(__float_as_uint(r[15]))
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory plan of one block (dynamic): K/V staging for two chunks of CH tokens, the warp-merge buffer.
-template <typename KVT, int EPL, int GM, bool MMA>
+template <typename KVT, int EPL, int GM, int MMA>
 struct AttnSmem {
     static constexpr int D = EPL * 32;
     // staged row stride in elements: the tensor-core path pads rows by 16 bytes so that the 8 rows of an
@@ -165,10 +208,11 @@ struct AttnSmem {
     static constexpr int CH = CH_FIT > CH_CAP ? CH_CAP : CH_FIT;
     static constexpr size_t kv_bytes = (size_t)2 * 2 * CH * RS * sizeof(KVT);  // [buffer][K|V][CH][RS]
     static constexpr size_t acc_bytes = (size_t)ATTN_WARPS * GM * D * sizeof(float);
-    static constexpr size_t total = kv_bytes + acc_bytes + (MMA ? 1024 : 0);  // tensor-core path: staging aligned to 1024 bytes
+    // tensor-core paths: staging aligned to 1024 bytes; tcgen05 path: + the Q and P operands (4 KB each)
+    static constexpr size_t total = kv_bytes + acc_bytes + (MMA ? 1024 : 0) + (MMA == 2 ? 8192 : 0);
 };
 
-template <typename KVT, int EPL, int GM, bool MMA>
+template <typename KVT, int EPL, int GM, int MMA>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_constant__ AttnKArgs ka) {
     const AttnArgs& a = ka.a;
     using SM = AttnSmem<KVT, EPL, GM, MMA>;
@@ -187,6 +231,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
     __shared__ __align__(8) unsigned long long kv_bar[2];  // one transaction barrier per staging buffer
     __shared__ int32_t blk_s[ATTN_SPEC_BLOCKS];             // the sequence's block-table row (short tables only)
     __shared__ __align__(16) KVT new_kv[2][D];  // the appended token's K and V (fused mode)
+    __shared__ __align__(8) unsigned long long tc_bar[2];  // tcgen05 path: S ready, P . V done (one completion per chunk each)
+    __shared__ uint32_t tc_tmem_slot;
+    __shared__ float tc_red[4][8];                          // per-warp maxima / sums of the 128 token rows
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     unsigned char* dyn_base = MMA ? dyn_smem + ((1024u - (smem_u32(dyn_smem) & 1023u)) & 1023u) : dyn_smem;
     KVT* kv_s = reinterpret_cast<KVT*>(dyn_base);
@@ -194,6 +241,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
     // tensor-core path: until the warps' partials are written there (after the last chunk's barrier), the same bytes hold
     // the low halves of Q (q - fp16(q)) as B fragments, the same for every warp: [k step][lane], 16 * D bytes
     uint2* qlo_s = reinterpret_cast<uint2*>(part_acc);
+    // tcgen05 path: the B operands, [q_hi (8 heads) | q_lo (8 heads)] as 16 rows x 128 dimensions (two 64-column halves, 128-byte
+    // swizzle) and [p_hi | p_lo] as 16 rows x 128 tokens (core matrices of 8 rows x 16 bytes)
+    unsigned char* qop = dyn_base + SM::kv_bytes + SM::acc_bytes;
+    unsigned char* pop = qop + 4096;
 
     trace_mark(a.trace, 0);
     pdl_launch_dependents();
@@ -228,6 +279,10 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
     constexpr int MT = D / 16;
     float o_t[MMA ? MT : 1][4];
     float m2[2] = {-INFINITY, -INFINITY}, l2[2] = {0.0f, 0.0f};
+    // tcgen05 path: running maximum in use and this thread's share of the sums, per head (threads 0..127 = token rows)
+    float tc_m[MMA == 2 ? 8 : 1], tc_l[MMA == 2 ? 8 : 1];
+#pragma unroll
+    for (int h = 0; h < (MMA == 2 ? 8 : 1); ++h) { tc_m[h] = -INFINITY; tc_l[h] = 0.0f; }
 #pragma unroll
     for (int i = 0; i < (MMA ? MT : 1); ++i) { o_t[i][0] = 0.0f; o_t[i][1] = 0.0f; o_t[i][2] = 0.0f; o_t[i][3] = 0.0f; }
     float m[GM], l[GM], acc[GM][EPL];
@@ -306,10 +361,20 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&kv_bar[0]), 1);
         mbar_init(smem_u32(&kv_bar[1]), 1);
+        if constexpr (MMA == 2) { mbar_init(smem_u32(&tc_bar[0]), 1); mbar_init(smem_u32(&tc_bar[1]), 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if constexpr (MMA == 2) {
+        if (warp == 1) {  // 32 columns of tensor memory: S^T (16) and O^T (16)
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tc_tmem_slot)), "r"(32) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        at_fence_before();
     }
     if (spec_table) blk_s[threadIdx.x] = my_blk;
     __syncthreads();  // barriers initialised, block table in place
+    uint32_t tmem = 0;
+    if constexpr (MMA == 2) { at_fence_after(); tmem = tc_tmem_slot; }
     if (early) {
         // the requests for the first two chunks, spread over the block (one copy per thread or fewer)
         if (n_ch > 0) stage_chunk(0, 0, 0);
@@ -413,8 +478,23 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
 #pragma unroll
             for (int e = 0; e < EPL; ++e) qr[g][e] = MMA ? 0.0f : q_s[g][lane * EPL + e];
         // Q^T as B fragments (k = head dimension, n = query head), fp16
-        uint32_t qb[MMA ? MT : 1][2];
-        if constexpr (MMA) {
+        uint32_t qb[MMA == 1 ? MT : 1][2];
+        if constexpr (MMA == 2) {
+            // the B operand of S^T = K . Q^T: rows 0..7 = fp16(q) of the group's heads, rows 8..15 = q - fp16(q): the split of Q
+            // costs no extra instruction (N = 16 is the smallest tile anyway)
+            for (uint32_t i = threadIdx.x; i < 16 * (D / 2); i += blockDim.x) {
+                const uint32_t n = i / (D / 2), d = 2 * (i % (D / 2)), g = n & 7;
+                float v0 = 0.0f, v1 = 0.0f;
+                if (g < (uint32_t)GM) {
+                    v0 = q_s[g][d]; v1 = q_s[g][d + 1];
+                    if (n >= 8) { v0 -= half_round(v0); v1 -= half_round(v1); }
+                }
+                *reinterpret_cast<uint32_t*>(qop + (d >> 6) * 2048 + n * 128 + ((((d & 63) >> 3) ^ (n & 7)) << 4) + (d & 7) * 2) = pack_half2(v0, v1);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+        }
+        if constexpr (MMA == 1) {
             const uint32_t n = lane >> 2, k0 = 2 * (lane & 3);
 #pragma unroll
             for (int ks = 0; ks < MT; ++ks) {
@@ -458,6 +538,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
                                 reinterpret_cast<const uint4*>(new_kv[kv])[piece];
                         }
                     }
+                    if constexpr (MMA == 2) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // read by the tensor core
                     __syncthreads();
                 }
             } else if (appender && c0 <= pos && pos < c0 + CH) {
@@ -468,7 +549,85 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
                 }
                 __syncthreads();
             }
-            if constexpr (MMA) {
+            if constexpr (MMA == 2) {
+                const uint32_t n_valid = c_hi - c0, n_landed = (n_valid + 15u) & ~15u;
+                // ---- S^T[128 tokens x 16] = K . [q_hi | q_lo]^T : D / 16 instructions from one thread --------------------------
+                const uint32_t s_bar = smem_u32(&tc_bar[0]), o_bar = smem_u32(&tc_bar[1]);
+                if (threadIdx.x == 0) {
+                    at_fence_after();
+                    const uint32_t kbase = smem_u32(kb), qbase = smem_u32(qop);
+#pragma unroll
+                    for (int ks = 0; ks < MT; ++ks)
+                        at_mma(tmem, at_desc_k_sw128(kbase + (ks >> 2) * (CH * 128u) + (ks & 3) * 32u),
+                               at_desc_k_sw128(qbase + (ks >> 2) * 2048u + (ks & 3) * 32u), AT_IDESC_S, ks != 0 ? 1u : 0u);
+                    at_commit(s_bar);
+                }
+                if (warp < 4) {
+                    // ---- softmax: thread = token row = tensor-memory lane ------------------------------------------------------
+                    const uint32_t lane_addr = (warp * 32u) << 16, tok = threadIdx.x;
+                    const bool ok = __all_sync(0xFFFFFFFFu, mbar_wait(s_bar, c & 1));
+                    if (!ok && a.err && lane == 0) atomicOr(a.err, 0x800u);
+                    at_fence_after();
+                    float sv[16];
+                    at_ld16(tmem + lane_addr, sv);
+                    const bool valid = tok < n_valid;
+                    float s8[8], mx[8];
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) { s8[h] = valid ? (sv[h] + sv[8 + h]) * ka.scale : -INFINITY; mx[h] = s8[h]; }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                        for (int h = 0; h < 8; ++h) mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xFFFFFFFFu, mx[h], off));
+#pragma unroll
+                    for (int h = 0; h < 8; ++h)
+                        if (lane == (uint32_t)h) tc_red[warp][h] = mx[h];   // (every lane holds all eight maxima)
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    float alpha[8];
+                    bool moved = false;
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) {
+                        const float cm = fmaxf(fmaxf(tc_red[0][h], tc_red[1][h]), fmaxf(tc_red[2][h], tc_red[3][h]));
+                        const float mn = fmaxf(tc_m[h], cm);  // finite: every chunk has a live token
+                        alpha[h] = (tc_m[h] == -INFINITY) ? 0.0f : __expf(tc_m[h] - mn);
+                        moved = moved || (mn != tc_m[h]);
+                        tc_m[h] = mn;
+                    }
+                    // [p_hi | p_lo] as the K-major B operand of O^T = V^T . P^T: row n, token k at (n / 8) * 2048 + (k / 8) * 128 +
+                    // (n % 8) * 16 + (k % 8) * 2
+                    unsigned char* prow = pop + (tok >> 3) * 128 + (tok & 7) * 2;
+#pragma unroll
+                    for (int h = 0; h < 8; ++h) {
+                        const float pv_ = valid ? __expf(s8[h] - tc_m[h]) : 0.0f;
+                        tc_l[h] = fmaf(tc_l[h], alpha[h], pv_);
+                        const __half ph = __float2half_rn(pv_);
+                        *reinterpret_cast<__half*>(prow + h * 16) = ph;
+                        *reinterpret_cast<__half*>(prow + 2048 + h * 16) = __float2half_rn(pv_ - __half2float(ph));
+                    }
+                    if (c > 0 && moved) {
+                        // the maximum in use moved (the same decision in every thread): scale O^T, this thread = dimension `tok`
+                        float o[16];
+                        at_ld16(tmem + lane_addr + 16, o);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) o[j] *= alpha[j & 7];
+                        at_st16(tmem + lane_addr + 16, o);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    at_fence_before();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                }
+                if (threadIdx.x == 0) {
+                    // ---- O^T[128 dimensions x 16] += V^T . [p_hi | p_lo]^T : one instruction per 16 tokens ------------------------
+                    at_fence_after();
+                    const uint32_t vbase = smem_u32(kb) + HV * (CH * 128u), pbase = smem_u32(pop);
+                    for (uint32_t kk = 0; kk < n_landed / 16u; ++kk)
+                        at_mma(tmem + 16, at_desc_mn_sw128(vbase + kk * 2048u, CH * 128u), at_desc_k_plain(pbase + kk * 256u, 128u, 2048u),
+                               AT_IDESC_O, (c | kk) != 0 ? 1u : 0u);
+                    at_commit(o_bar);
+                }
+                // the staging buffer, the P operand and S^T are free again once that product is done
+                if (!mbar_wait(o_bar, c & 1) && a.err) atomicOr(a.err, 0x1000u);
+                at_fence_after();
+            } else if constexpr (MMA) {
                 const uint32_t n_tiles = (c_hi - c0 + 15) / 16;
                 const uint32_t mi = lane >> 3, r8 = lane & 7;
                 for (uint32_t tile = warp; tile < n_tiles; tile += ATTN_WARPS) {
@@ -582,7 +741,46 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) k_attn_split(const __grid_con
     }
 
     // ---- merge the warps into this block's partial (m, l, unnormalised acc) ...
-    if constexpr (MMA) {
+    if constexpr (MMA == 2) {
+        // the whole block's result sits in tensor memory: it becomes "warp 0's" partial, the other warps contribute nothing
+        for (uint32_t i = threadIdx.x; i < (ATTN_WARPS - 1) * GM * D; i += blockDim.x) part_acc[(size_t)GM * D + i] = 0.0f;
+        if (threadIdx.x < (ATTN_WARPS - 1) * GM) { part_ml[1 + threadIdx.x / GM][threadIdx.x % GM][0] = -INFINITY; part_ml[1 + threadIdx.x / GM][threadIdx.x % GM][1] = 0.0f; }
+        if (warp < 4) {
+            float o[16];
+            if (has_tokens) {
+                at_fence_after();
+                at_ld16(tmem + ((warp * 32u) << 16) + 16, o);   // O^T: this thread's dimension, columns = [hi | lo] heads
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) o[j] = 0.0f;
+            }
+#pragma unroll
+            for (int h = 0; h < GM; ++h) part_acc[(size_t)h * D + threadIdx.x] = o[h] + o[8 + h];
+            // sums of the probabilities: every thread holds those of its own token rows
+            float ls[8];
+#pragma unroll
+            for (int h = 0; h < 8; ++h) ls[h] = has_tokens ? tc_l[h] : 0.0f;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int h = 0; h < 8; ++h) ls[h] += __shfl_xor_sync(0xFFFFFFFFu, ls[h], off);
+#pragma unroll
+            for (int h = 0; h < 8; ++h)
+                if (lane == (uint32_t)h) tc_red[warp][h] = ls[h];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x < (uint32_t)GM) {
+                const uint32_t h = threadIdx.x;
+                part_ml[0][h][0] = has_tokens ? tc_m[h] : -INFINITY;
+                part_ml[0][h][1] = (tc_red[0][h] + tc_red[1][h]) + (tc_red[2][h] + tc_red[3][h]);
+            }
+            at_fence_before();
+        }
+        __syncthreads();
+        if (warp == 1) {
+            at_fence_after();
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(32) : "memory");
+        }
+    } else if constexpr (MMA) {
         // the 8 lanes that share lane & 3 hold partial sums of the same two heads
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
@@ -676,9 +874,15 @@ uint32_t attn_pick_splits(uint32_t max_seq) {
     return s < 1 ? 1 : s;
 }
 
+// head_dim 128 on the tensor-core path as tcgen05.mma (option "attn_tcgen05"): tokens are the M dimension, [q_hi | q_lo] and
+// [p_hi | p_lo] the N = 16 columns (the hi/lo halves cost no instruction), S^T and O^T in tensor memory.  It gives the same
+// results and 24 instead of 256 tensor-core instructions per 128-token chunk, but a chunk is then one serial chain of
+// hand-overs (commit -> barrier -> tcgen05.ld -> cross-warp maximum -> P through shared memory and a proxy fence -> commit):
+// measured 1.39 instead of 1.29 ms per token at batch 1 and 4.0 instead of 3.27 ms per step at batch 32.  Off by default.
+bool attn_use_tcgen05 = false;
 bool attn_use_mma = true;  // fp16 caches with head_dim <= 256: QK^T and PV on the tensor cores (option "attn_mma")
 
-template <typename KVT, int EPL, int GM, bool MMA>
+template <typename KVT, int EPL, int GM, int MMA>
 static cudaError_t launch_split_g(const LaunchCfg& lc, AttnKArgs ka) {
     ka.g_chunks = (ka.G + GM - 1) / GM;
     const size_t smem = AttnSmem<KVT, EPL, GM, MMA>::total;
@@ -707,19 +911,27 @@ static cudaError_t launch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
     if constexpr (sizeof(KVT) == 2 && EPL >= 2 && EPL <= 8) {
         // tensor-core path: paged pool of 16-token blocks reachable through its tensor map
         if (attn_use_mma && ka.a.kv_map && ka.a.block_table && ka.a.block_tokens == 16) {
-            if (ka.G == 1) return launch_split_g<KVT, EPL, 1, true>(lc, ka);
-            if (ka.G == 2) return launch_split_g<KVT, EPL, 2, true>(lc, ka);
-            if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, true>(lc, ka);
-            return launch_split_g<KVT, EPL, 8, true>(lc, ka);
+            if constexpr (EPL == 4) {
+                if (attn_use_tcgen05) {  // head_dim 128: both products as tcgen05.mma with the tokens as the M dimension
+                    if (ka.G == 1) return launch_split_g<KVT, EPL, 1, 2>(lc, ka);
+                    if (ka.G == 2) return launch_split_g<KVT, EPL, 2, 2>(lc, ka);
+                    if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, 2>(lc, ka);
+                    return launch_split_g<KVT, EPL, 8, 2>(lc, ka);
+                }
+            }
+            if (ka.G == 1) return launch_split_g<KVT, EPL, 1, 1>(lc, ka);
+            if (ka.G == 2) return launch_split_g<KVT, EPL, 2, 1>(lc, ka);
+            if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, 1>(lc, ka);
+            return launch_split_g<KVT, EPL, 8, 1>(lc, ka);
         }
     }
     if constexpr (EPL >= 8) {
-        return launch_split_g<KVT, EPL, 1, false>(lc, ka);  // wide heads: one query head per block keeps registers in bounds
+        return launch_split_g<KVT, EPL, 1, 0>(lc, ka);  // wide heads: one query head per block keeps registers in bounds
     } else {
-        if (ka.G == 1) return launch_split_g<KVT, EPL, 1, false>(lc, ka);
-        if (ka.G == 2) return launch_split_g<KVT, EPL, 2, false>(lc, ka);
-        if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, false>(lc, ka);
-        return launch_split_g<KVT, EPL, 8, false>(lc, ka);
+        if (ka.G == 1) return launch_split_g<KVT, EPL, 1, 0>(lc, ka);
+        if (ka.G == 2) return launch_split_g<KVT, EPL, 2, 0>(lc, ka);
+        if (ka.G <= 4) return launch_split_g<KVT, EPL, 4, 0>(lc, ka);
+        return launch_split_g<KVT, EPL, 8, 0>(lc, ka);
     }
 }
 
@@ -737,12 +949,17 @@ static cudaError_t dispatch_split(const LaunchCfg& lc, const AttnKArgs& ka) {
 
 template <typename KVT, int EPL, int GM>
 static cudaError_t opt_in_one() {
-    cudaError_t e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)AttnSmem<KVT, EPL, GM, false>::total);
+    cudaError_t e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AttnSmem<KVT, EPL, GM, 0>::total);
     if constexpr (sizeof(KVT) == 2 && EPL >= 2 && EPL <= 8) {
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)AttnSmem<KVT, EPL, GM, true>::total);
+            e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)AttnSmem<KVT, EPL, GM, 1>::total);
+        if constexpr (EPL == 4) {
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(k_attn_split<KVT, EPL, GM, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)AttnSmem<KVT, EPL, GM, 2>::total);
+        }
     }
     return e;
 }

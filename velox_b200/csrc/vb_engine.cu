@@ -1324,6 +1324,7 @@ int32_t vb_set_option(vb_ctx* c, const char* name, int64_t value) {
     if (!strcmp(name, "gemv_imma")) { imma_enabled = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_multirow")) { imma_multirow = value != 0; return VB_OK; }
     if (!strcmp(name, "attn_mma")) { attn_use_mma = value != 0; return VB_OK; }
+    if (!strcmp(name, "attn_tcgen05")) { attn_use_tcgen05 = value != 0; return VB_OK; }
     if (!strcmp(name, "gemv_tma")) { fast_use_tma = value != 0; return VB_OK; }
     set_error("vb_set_option: unknown option '%s'", name);
     return VB_ERR_INVALID;

@@ -99,6 +99,7 @@ cudaError_t tile_q4_swiglu(const LaunchCfg& lc, void* tiled, const void* canon, 
                            int which);
 extern bool fast_use_tma;
 extern bool attn_use_mma;
+extern bool attn_use_tcgen05;
 cudaError_t fast_error_word(uint32_t** out);
 cudaError_t fast_error_word_host(uint32_t** out);
 cudaError_t tile_q4(const LaunchCfg& lc, void* tiled, void* tiled_scales, const void* canon, const void* canon_scales,
