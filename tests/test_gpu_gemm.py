@@ -68,6 +68,30 @@ def test_matmul_rows_parity(vb, oracle, dev, fmt, shape):
         assert np.max(np.abs(got[r] - want)) <= 3e-3 * scale
 
 
+def test_matmul_rows_inputs_beyond_fp16_range(vb, oracle, dev):
+    """Rows of x with values around 1e5 (un-normalised activations of a real checkpoint can get there): the chunk path carries
+    them as fp16 hi + lo halves (exact up to 2 x 65504), the decode-batch path saturates; neither produces infinities."""
+    in_dim, out_dim = 512, 256
+    c = oracle.FMT_Q4G32
+    w = oracle.fill_normal(out_dim * in_dim, 21, 1, 0.02).reshape(out_dim, in_dim)
+    data, scales = oracle.quantize(w, c)
+    for n_rows in (64, 8):
+        x = oracle.fill_normal(n_rows * in_dim, 21, 2, 1.0).reshape(n_rows, in_dim)
+        x[1, 7], x[1, 300], x[n_rows - 1, 0] = 1.0e5, -9.5e4, 1.2e5
+        got = run_rows(vb, dev, data, scales, c, x, in_dim, out_dim)
+        assert np.all(np.isfinite(got))
+        if n_rows > 32:  # hi + lo halves hold these values exactly: the product agrees with the fp32 reference
+            for r in (1, n_rows - 1, 5):
+                want = oracle.matvec(x[r], data, scales, c, in_dim, out_dim)
+                assert np.max(np.abs(got[r] - want)) <= 1e-3 * max(1.0, float(np.max(np.abs(want))))
+        else:            # one fp16 half: the outliers are clamped to 65504, the other rows are untouched
+            want = oracle.matvec(x[5], data, scales, c, in_dim, out_dim)
+            assert np.max(np.abs(got[5] - want)) <= 3e-3 * np.sqrt(in_dim) * 0.02
+            xc = np.clip(x[1], -65504.0, 65504.0)
+            want = oracle.matvec(xc, data, scales, c, in_dim, out_dim)
+            assert np.max(np.abs(got[1] - want)) <= 2e-3 * float(np.max(np.abs(want)))
+
+
 def test_matmul_rows_linearity_at_full_size(vb, oracle, dev):
     """Llama-3-8B down-projection shape, 512 rows: (x1 + x2) W = x1 W + x2 W up to rounding, and a spot check of rows."""
     in_dim, out_dim, n_rows = 14336, 4096, 512

@@ -346,11 +346,15 @@ k_rows_to_f16(__half* __restrict__ dst, __half* __restrict__ dst_lo, const float
             }
             v.x = (v.x * inv) * w.x; v.y = (v.y * inv) * w.y; v.z = (v.z * inv) * w.z; v.w = (v.w * inv) * w.w;
         }
-        const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
+        // un-normalised inputs (attention output, SiLU(gate) * up) may exceed fp16's range: the cast saturates instead of
+        // producing infinities; with the hi + lo split the low half carries what the high half could not (exact up to 2 x 65504)
+        constexpr float H_MAX = 65504.0f;
+        auto sat = [](float f) { return fminf(fmaxf(f, -H_MAX), H_MAX); };
+        const __half2 h01 = __floats2half2_rn(sat(v.x), sat(v.y)), h23 = __floats2half2_rn(sat(v.z), sat(v.w));
         out2[k] = make_uint2(*reinterpret_cast<const uint32_t*>(&h01), *reinterpret_cast<const uint32_t*>(&h23));
         if (dst_lo) {
             const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-            const __half2 l01 = __floats2half2_rn(v.x - f01.x, v.y - f01.y), l23 = __floats2half2_rn(v.z - f23.x, v.w - f23.y);
+            const __half2 l01 = __floats2half2_rn(sat(v.x - f01.x), sat(v.y - f01.y)), l23 = __floats2half2_rn(sat(v.z - f23.x), sat(v.w - f23.y));
             reinterpret_cast<uint2*>(dst_lo + (size_t)r * K)[k] = make_uint2(*reinterpret_cast<const uint32_t*>(&l01), *reinterpret_cast<const uint32_t*>(&l23));
         }
     }
