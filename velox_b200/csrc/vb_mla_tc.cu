@@ -28,7 +28,12 @@
 // Tried on the way (same workload, 64 sequences of 1024..8192 tokens): 32-token tiles with two slots and P in shared
 // memory 0.49 ms; Q in tensor memory as the A operand with a four-way split of the output columns and a five-slot
 // ring 0.66 ms (the S product is no faster from tensor memory and is computed four times); one issuer 0.49, two 0.44,
-// three 0.44; P in tensor memory 0.41 ms.  The mma.sync kernel of vb_mla_decode.cu takes 0.65 ms.
+// three 0.44; P in tensor memory 0.41 ms; two softmax groups of four warps taking alternate tiles (the maximum in use
+// handed from tile to tile through shared memory) 0.436 ms: the softmax chain is not what bounds a tile.  What does:
+// each of the 36 S instructions of a tile reads its 128 x 16 slice of Q (4 KB) from shared memory at 128 bytes a
+// clock, 1152 clocks (0.6 us) per tile whatever the tile's width, so the cost per token halves only with tiles twice
+// as wide, and the tile buffers that 147 KB of Q leave room for hold 64 rows in all.
+// The mma.sync kernel of vb_mla_decode.cu takes 0.65 ms.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
