@@ -250,7 +250,7 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
     prompt_lens = [prompt_len] * batch
     if workload == BS32_WORKLOAD and not args.same_prompt_len:
         prompt_lens = [int(x) for x in np.random.default_rng(SEED).integers(256, 2049, size=batch)]
-    max_seq = max(prompt_lens) + warmup + 2 * steps + 16
+    max_seq = max(prompt_lens) + warmup + 2 * steps + 16 + 512   # (512: room to keep the GPU busy for the clock sampler)
 
     def barrier():
         if not solo:
@@ -365,14 +365,19 @@ def measure(args, R: Ranks, workload: str, steps: int, warmup: int, prompt_len: 
     ms_per_step = ms / steps
     value = groups * batch * 1e3 / ms_per_step
 
-    if sampler.rows == []:
-        # very short runs: keep the GPU busy until the sampler has something to report
-        t_end = time.perf_counter() + 1.0
-        spare = max_seq - max(eng.state(slot)[1] for slot in range(batch)) - 1
-        while not sampler.rows and time.perf_counter() < t_end and spare >= 8:
-            eng.decode(8)
-            eng.sync()
-            spare -= 8
+    # short runs: keep replaying the same step (untimed) until the sampler has three readings under load, two seconds at
+    # most.  Ranks that work together decide together (a sharded step is a collective: every rank replays the same number).
+    t_end = time.perf_counter() + 2.0
+    spare = max_seq - max(eng.state(slot)[1] for slot in range(batch)) - 1
+    while spare >= 8:
+        more = 1.0 if (len(sampler.rows) < 3 and time.perf_counter() < t_end) else 0.0
+        if not solo:
+            more = R.max(more)
+        if more == 0.0:
+            break
+        eng.decode(8)
+        eng.sync()
+        spare -= 8
     clocks = sampler.stop()
 
     peak, peak_kind = load_peaks()
